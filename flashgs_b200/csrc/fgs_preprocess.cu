@@ -1,0 +1,446 @@
+// Preprocess + key duplication for sm_100a.
+//
+// One kernel does what flashgs::preprocess does (csrc/cuda_rasterizer/preprocess.cu:243-418):
+// near/opacity cull, projection, EWA 2D covariance, conic, exact AABB of the 1/256
+// iso-ellipse, exact ellipse-vs-tile test, (tile|depth) key emission, degree-3 SH colour
+// and the feature records the blend stage reads.
+//
+// Design (B200): a block of 256 threads owns 256 consecutive Gaussians.
+//   1. position / opacity / covariance of the block are fetched with 16-byte loads into
+//      shared memory (the [P,3] and [P,6] rows are 12 and 24 bytes, so per-thread loads
+//      could not be vectorised); each thread then projects its own Gaussian.
+//   2. The tile rectangles of the block's Gaussians are laid end to end ("slots") with a
+//      block-wide exclusive scan, and all 256 threads walk the slot space together: a
+//      thread finds the Gaussian a slot belongs to by binary search in the scan and runs
+//      the exact tile test for that one tile. A splat covering thousands of tiles is thus
+//      spread over the whole block instead of serialising a warp, and 1-tile splats fill
+//      all lanes.
+//   3. Pair offsets: per chunk of 1024 slots the per-warp hit counts are scanned by one
+//      warp, which issues ONE atomicAdd on the global pair counter for the whole chunk
+//      (a warp-aggregated prefix); every warp then stores a contiguous run of keys.
+//   4. Gaussians with at least one hit fetch their 192-byte SH record with 16-byte loads
+//      and write the three feature records.
+//
+// The float expressions keep the operation order of the reference so that the device
+// compiler's FMA contraction sees the same expression trees: the tile lists depend on
+// float comparisons and (int) truncations of these values.
+
+#include "fgs_common.cuh"
+
+#include <cstring>
+
+namespace fgs {
+namespace {
+
+constexpr int PRE_THREADS = 256;
+constexpr int PRE_WARPS = PRE_THREADS / 32;
+constexpr int PRE_K = 4;  // slot iterations per offset chunk (PRE_K * PRE_WARPS == 32 counts, one warp scans them)
+static_assert(PRE_K * PRE_WARPS == 32, "one warp scans the chunk's per-warp counts");
+
+constexpr float kLog2e = 1.4426950216293334961f;
+constexpr float kLn2 = 0.69314718055f;
+
+__device__ __forceinline__ float approx_sqrt(float x) { float y; asm volatile("sqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float approx_rsqrt(float x) { float y; asm volatile("rsqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float approx_lg2(float x) { float y; asm volatile("lg2.approx.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float max_f32(float a, float b) { float d; asm volatile("max.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b)); return d; }
+
+// preprocess.cu:64-67 -- the literals are doubles, so the arithmetic is done in fp64
+__device__ __forceinline__ float ndc_to_pix(float v, int S) { return ((v + 1.0) * S - 1.0) * 0.5; }
+
+struct f3 { float x, y, z; };
+
+// preprocess.cu:69-77
+__device__ __forceinline__ f3 xform4x3(const f3& p, const float* m)
+{
+    f3 t = {
+        m[0] * p.x + m[4] * p.y + m[8] * p.z + m[12],
+        m[1] * p.x + m[5] * p.y + m[9] * p.z + m[13],
+        m[2] * p.x + m[6] * p.y + m[10] * p.z + m[14],
+    };
+    return t;
+}
+
+// Column-major 3x3 product in GLM's operation order (csrc/glm/detail/type_mat3x3.inl:486-519):
+// r[c][q] = a[0][q]*b[c][0] + a[1][q]*b[c][1] + a[2][q]*b[c][2]
+__device__ __forceinline__ void mul3(const float (&a)[3][3], const float (&b)[3][3], float (&r)[3][3])
+{
+#pragma unroll
+    for (int c = 0; c < 3; c++)
+#pragma unroll
+        for (int q = 0; q < 3; q++)
+            r[c][q] = a[0][q] * b[c][0] + a[1][q] * b[c][1] + a[2][q] * b[c][2];
+}
+
+// preprocess.cu:103-143
+__device__ __forceinline__ f3 cov2d(const f3& p, const PreCam& cam, const float* cov3)
+{
+    f3 t = xform4x3(p, cam.view);
+    const float limx = 1.3f * cam.tan_fovx;
+    const float limy = 1.3f * cam.tan_fovy;
+    const float txtz = t.x / t.z;
+    const float tytz = t.y / t.z;
+    t.x = fminf(limx, fmaxf(-limx, txtz)) * t.z;
+    t.y = fminf(limy, fmaxf(-limy, tytz)) * t.z;
+
+    const float J[3][3] = {
+        { cam.focal_x / t.z, 0.0f, -(cam.focal_x * t.x) / (t.z * t.z) },
+        { 0.0f, cam.focal_y / t.z, -(cam.focal_y * t.y) / (t.z * t.z) },
+        { 0.0f, 0.0f, 0.0f } };
+    const float* v = cam.view;
+    const float Wm[3][3] = { { v[0], v[4], v[8] }, { v[1], v[5], v[9] }, { v[2], v[6], v[10] } };
+    float T[3][3];
+    mul3(Wm, J, T);
+    const float Vt[3][3] = {   // transpose of the symmetric Vrk, spelled out as GLM's transpose does
+        { cov3[0], cov3[1], cov3[2] }, { cov3[1], cov3[3], cov3[4] }, { cov3[2], cov3[4], cov3[5] } };
+    const float Tt[3][3] = { { T[0][0], T[1][0], T[2][0] }, { T[0][1], T[1][1], T[2][1] }, { T[0][2], T[1][2], T[2][2] } };
+    float A[3][3], C[3][3];
+    mul3(Tt, Vt, A);
+    mul3(A, T, C);
+    C[0][0] += 0.3f;
+    C[1][1] += 0.3f;
+    return { C[0][0], C[0][1], C[1][1] };
+}
+
+// preprocess.cu:187-194
+__device__ __forceinline__ bool segment_hits_ellipse(float a, float b, float c, float d, float l, float r)
+{
+    float delta = b * b - 4.0f * a * c;
+    float t1 = (l - d) * (2.0f * a) + b;
+    float t2 = (r - d) * (2.0f * a) + b;
+    return delta >= 0.0f && (t1 <= 0.0f || t1 * t1 <= delta) && (t2 >= 0.0f || t2 * t2 <= delta);
+}
+
+// preprocess.cu:196-241: centre inside the tile's pixel box, or the iso-ellipse crosses the
+// nearest vertical edge, or the nearest horizontal edge.
+__device__ __forceinline__ bool tile_hit(int tx, int ty, int bx, int by, float cx_pix, float cy_pix,
+                                         float conx, float cony, float conz, float power)
+{
+    const int minx = tx * bx, miny = ty * by;
+    const int maxx = minx + bx - 1, maxy = miny + by - 1;
+    if (cx_pix >= minx && cx_pix <= maxx && cy_pix >= miny && cy_pix <= maxy) return true;
+
+    float a, b, c, dx, dy;
+    const float w = 2.0f * power;
+    if (cx_pix * 2.0f < minx + maxx) dx = cx_pix - minx; else dx = cx_pix - maxx;
+    a = conz;
+    b = -2.0f * cony * dx;
+    c = conx * dx * dx - w;
+    if (segment_hits_ellipse(a, b, c, cy_pix, miny, maxy)) return true;
+
+    if (cy_pix * 2.0f < miny + maxy) dy = cy_pix - miny; else dy = cy_pix - maxy;
+    a = conx;
+    b = -2.0f * cony * dy;
+    c = conz * dy * dy - w;
+    return segment_hits_ellipse(a, b, c, cx_pix, minx, maxx);
+}
+
+// preprocess.cu:145-185; sh holds the 16 coefficients as [coef][rgb]
+
+__device__ __forceinline__ void sh_color(const float (&sh)[48], const f3& p, const float* campos, float& r, float& g, float& bl)
+{
+    const float SH_C0 = 0.28209479177387814f, SH_C1 = 0.4886025119029199f;
+    const float C2[5] = { 1.0925484305920792f, -1.0925484305920792f, 0.31539156525252005f, -1.0925484305920792f, 0.5462742152960396f };
+    const float C3[7] = { -0.5900435899266435f, 2.890611442640554f, -0.4570457994644658f, 0.3731763325901154f,
+                          -0.4570457994644658f, 1.445305721320277f, -0.5900435899266435f };
+    float dx = p.x - campos[0], dy = p.y - campos[1], dz = p.z - campos[2];
+    const float l2 = dx * dx + dy * dy + dz * dz;
+    const float rs = approx_rsqrt(l2);
+    const float x = dx * rs, y = dy * rs, z = dz * rs;
+    const float xx = x * x, yy = y * y, zz = z * z;
+    const float xy = x * y, yz = y * z, xz = x * z;
+    float res[3];
+#pragma unroll
+    for (int ch = 0; ch < 3; ch++) {
+        float v = SH_C0 * sh[ch] + 0.5f;
+        v = v - SH_C1 * y * sh[3 + ch] + SH_C1 * z * sh[6 + ch] - SH_C1 * x * sh[9 + ch];
+        v = v +
+            C2[0] * xy * sh[12 + ch] +
+            C2[1] * yz * sh[15 + ch] +
+            C2[2] * (2.0f * zz - xx - yy) * sh[18 + ch] +
+            C2[3] * xz * sh[21 + ch] +
+            C2[4] * (xx - yy) * sh[24 + ch];
+        v = v +
+            C3[0] * y * (3.0f * xx - yy) * sh[27 + ch] +
+            C3[1] * xy * z * sh[30 + ch] +
+            C3[2] * y * (4.0f * zz - xx - yy) * sh[33 + ch] +
+            C3[3] * z * (2.0f * zz - 3.0f * xx - 3.0f * yy) * sh[36 + ch] +
+            C3[4] * x * (4.0f * zz - xx - yy) * sh[39 + ch] +
+            C3[5] * z * (xx - yy) * sh[42 + ch] +
+            C3[6] * x * (xx - 3.0f * yy) * sh[45 + ch];
+        res[ch] = max_f32(v, 0.0f);
+    }
+    r = res[0]; g = res[1]; bl = res[2];
+}
+
+// Cooperative copy of `nfloats` floats starting at a 16-byte aligned global address into
+// shared memory: whole float4s first, then the ragged tail one float at a time.
+template <bool VEC>
+__device__ __forceinline__ void stage_floats(float* dst, const float* src, int nfloats)
+{
+    if (VEC) {
+        const int nv = nfloats >> 2;
+        for (int i = threadIdx.x; i < nv; i += PRE_THREADS)
+            reinterpret_cast<float4*>(dst)[i] = __ldg(reinterpret_cast<const float4*>(src) + i);
+        for (int i = (nv << 2) + threadIdx.x; i < nfloats; i += PRE_THREADS) dst[i] = __ldg(src + i);
+    } else {
+        for (int i = threadIdx.x; i < nfloats; i += PRE_THREADS) dst[i] = __ldg(src + i);
+    }
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(PRE_THREADS)
+preprocess_kernel(int P,
+                  const float* __restrict__ positions, const float* __restrict__ opacities,
+                  const float* __restrict__ cov3ds, const float* __restrict__ shs,
+                  const __grid_constant__ PreCam cam,
+                  float2* __restrict__ points_xy, float4* __restrict__ rgb_depth, float4* __restrict__ conic_opacity,
+                  uint64_t* __restrict__ keys, uint32_t* __restrict__ values, long long capacity,
+                  int* __restrict__ curr_offset, int* __restrict__ status)
+{
+    __shared__ __align__(16) float s_pos[PRE_THREADS * 3];
+    __shared__ __align__(16) float s_cov[PRE_THREADS * 6];
+    __shared__ __align__(16) float s_opa[PRE_THREADS];
+    __shared__ float2 s_xy[PRE_THREADS];
+    __shared__ float4 s_con[PRE_THREADS];      // conic.x, conic.y, conic.z, power
+    __shared__ int4 s_rect[PRE_THREADS];       // min_x, min_y, width, float_bits(depth)
+    __shared__ int s_prefix[PRE_THREADS + 1];  // exclusive scan of rectangle areas
+    __shared__ int s_vis[PRE_THREADS];
+    __shared__ int s_wcnt[32];
+    __shared__ int s_woff[32];
+    __shared__ int s_wsum[PRE_WARPS];
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int base = blockIdx.x * PRE_THREADS;
+    const int n_here = min(PRE_THREADS, P - base);
+
+    stage_floats<VEC>(s_pos, positions + (size_t)base * 3, n_here * 3);
+    stage_floats<VEC>(s_cov, cov3ds + (size_t)base * 6, n_here * 6);
+    stage_floats<VEC>(s_opa, opacities + base, n_here);
+    s_vis[tid] = 0;
+    __syncthreads();
+
+    // ---- per-Gaussian projection (preprocess.cu:282-316) ----
+    bool point_valid = false;
+    f3 p_orig = { 0.f, 0.f, 0.f };
+    float depth = 0.f, log2_opacity = 0.f, power = 0.f;
+    float2 point_xy = { 0.f, 0.f };
+    f3 conic = { 0.f, 0.f, 0.f };
+    int minx = 0, miny = 0, maxx = 0, maxy = 0;
+    if (tid < n_here) {
+        do {
+            p_orig = { s_pos[3 * tid], s_pos[3 * tid + 1], s_pos[3 * tid + 2] };
+            const f3 p_view = xform4x3(p_orig, cam.view);
+            depth = p_view.z;
+            if (p_view.z <= 0.2f) break;
+            const float opacity = s_opa[tid];
+            if (255.0f * opacity < 1.0f) break;
+
+            const float* pm = cam.proj;
+            const float hx = pm[0] * p_orig.x + pm[4] * p_orig.y + pm[8] * p_orig.z + pm[12];
+            const float hy = pm[1] * p_orig.x + pm[5] * p_orig.y + pm[9] * p_orig.z + pm[13];
+            const float hw = pm[3] * p_orig.x + pm[7] * p_orig.y + pm[11] * p_orig.z + pm[15];
+            const float p_w = 1.0f / (hw + 0.0000001f);
+            const float projx = hx * p_w, projy = hy * p_w;
+
+            const f3 cov = cov2d(p_orig, cam, s_cov + 6 * tid);
+            const float det = (cov.x * cov.z - cov.y * cov.y);
+            const float det_inv = 1.f / det;
+            conic = { cov.z * det_inv, -cov.y * det_inv, cov.x * det_inv };
+
+            log2_opacity = approx_lg2(opacity);
+            power = kLn2 * 8.0f + kLn2 * log2_opacity;
+            const int width = (int)(1.414214f * approx_sqrt(cov.x * power) + 1.0f);
+            const int height = (int)(1.414214f * approx_sqrt(cov.z * power) + 1.0f);
+
+            point_xy = { ndc_to_pix(projx, cam.W), ndc_to_pix(projy, cam.H) };
+            // getRect, preprocess.cu:90-100, then the strip clamp on rows
+            minx = min(cam.grid_x, max(0, (int)((point_xy.x - width) / (float)cam.block_x)));
+            miny = min(cam.grid_y, max(0, (int)((point_xy.y - height) / (float)cam.block_y)));
+            maxx = min(cam.grid_x, max(0, (int)((point_xy.x + width) / (float)cam.block_x) + 1));
+            maxy = min(cam.grid_y, max(0, (int)((point_xy.y + height) / (float)cam.block_y) + 1));
+            miny = max(miny, cam.row_begin);
+            maxy = min(maxy, cam.row_end);
+            point_valid = (maxx > minx) && (maxy > miny);
+        } while (false);
+    }
+
+    const int rect_w = point_valid ? (maxx - minx) : 0;
+    const int area = point_valid ? rect_w * (maxy - miny) : 0;
+    s_xy[tid] = point_xy;
+    s_con[tid] = make_float4(conic.x, conic.y, conic.z, power);
+    s_rect[tid] = make_int4(minx, miny, rect_w, __float_as_int(depth));
+
+    // ---- block-wide exclusive scan of the rectangle areas ----
+    int incl = area;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(FULL_MASK, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_wsum[warp] = incl;
+    __syncthreads();
+    int wbase = 0;
+#pragma unroll
+    for (int w = 0; w < PRE_WARPS; w++) wbase += (w < warp) ? s_wsum[w] : 0;
+    s_prefix[tid] = wbase + incl - area;
+    if (tid == PRE_THREADS - 1) s_prefix[PRE_THREADS] = wbase + incl;
+    __syncthreads();
+    const int total = s_prefix[PRE_THREADS];
+
+    // ---- walk the slot space: one (Gaussian, tile) test per thread per step ----
+    const unsigned lt = lanemask_lt();
+    for (int c0 = 0; c0 < total; c0 += PRE_THREADS * PRE_K) {
+        unsigned hit_mask[PRE_K];
+        uint32_t tile_id[PRE_K];
+        int owner[PRE_K];
+#pragma unroll
+        for (int k = 0; k < PRE_K; k++) {
+            const int slot = c0 + k * PRE_THREADS + tid;
+            bool hit = false;
+            tile_id[k] = 0; owner[k] = 0;
+            if (slot < total) {
+                int lo = 0, hi = PRE_THREADS;   // largest g with s_prefix[g] <= slot
+#pragma unroll
+                for (int s = 0; s < 8; s++) {
+                    const int mid = (lo + hi) >> 1;
+                    if (s_prefix[mid] <= slot) lo = mid; else hi = mid;
+                }
+                const int g = lo;
+                const int4 rc = s_rect[g];
+                const int t = slot - s_prefix[g];
+                const int ry = t / rc.z;
+                const int tx = rc.x + (t - ry * rc.z);
+                const int ty = rc.y + ry;
+                const float2 c = s_xy[g];
+                const float4 q = s_con[g];
+                hit = tile_hit(tx, ty, cam.block_x, cam.block_y, c.x, c.y, q.x, q.y, q.z, q.w);
+                tile_id[k] = (uint32_t)(ty * cam.grid_x + tx);
+                owner[k] = g;
+                if (hit) s_vis[g] = 1;
+            }
+            hit_mask[k] = __ballot_sync(FULL_MASK, hit);
+            if (lane == 0) s_wcnt[k * PRE_WARPS + warp] = __popc(hit_mask[k]);
+        }
+        __syncthreads();
+        if (warp == 0) {
+            const int c = s_wcnt[lane];
+            int inc = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(FULL_MASK, inc, o);
+                if (lane >= o) inc += v;
+            }
+            const int chunk_total = __shfl_sync(FULL_MASK, inc, 31);
+            int chunk_base = 0;
+            if (lane == 0 && chunk_total > 0) chunk_base = atomicAdd(curr_offset, chunk_total);
+            chunk_base = __shfl_sync(FULL_MASK, chunk_base, 0);
+            s_woff[lane] = chunk_base + inc - c;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < PRE_K; k++) {
+            if (hit_mask[k] & (1u << lane)) {
+                const long long o = (long long)s_woff[k * PRE_WARPS + warp] + __popc(hit_mask[k] & lt);
+                if (o >= 0 && o < capacity) {
+                    const int g = owner[k];
+                    keys[o] = ((uint64_t)tile_id[k] << 32) | (uint32_t)s_rect[g].w;
+                    values[o] = (uint32_t)(base + g);
+                } else {
+                    atomicOr(status, FGS_ERR_PAIR_OVERFLOW);
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- features of visible Gaussians (preprocess.cu:411-417) ----
+    if (tid < n_here && s_vis[tid]) {
+        const int idx = base + tid;
+        float sh[48];
+        if (VEC) {
+            const float4* s4 = reinterpret_cast<const float4*>(shs + (size_t)idx * 48);
+#pragma unroll
+            for (int i = 0; i < 12; i++) {
+                const float4 v = __ldg(s4 + i);
+                sh[4 * i] = v.x; sh[4 * i + 1] = v.y; sh[4 * i + 2] = v.z; sh[4 * i + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 48; i++) sh[i] = __ldg(shs + (size_t)idx * 48 + i);
+        }
+        float r, g, b;
+        sh_color(sh, p_orig, cam.cam, r, g, b);
+        points_xy[idx] = point_xy;
+        conic_opacity[idx] = make_float4((-0.5f * kLog2e) * conic.x, -kLog2e * conic.y, (-0.5f * kLog2e) * conic.z, log2_opacity);
+        rgb_depth[idx] = make_float4(r, g, b, depth);
+    }
+}
+
+} // namespace
+
+// Host matrices in the reference's operation order; see fgs_view_proj_matrices().
+void host_view_proj(int width, int height, const float* pos, const float* rot, float fx, float fy,
+                    float zFar, float zNear, float* view, float* proj);
+
+} // namespace fgs
+
+extern "C" int fgs_preprocess_strip(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                                    int width, int height, int block_x, int block_y,
+                                    const float* cam_position, const float* cam_rotation,
+                                    float focal_x, float focal_y, float zFar, float zNear,
+                                    int tile_row_begin, int tile_row_end,
+                                    float* points_xy, float* rgb_depth, float* conic_opacity,
+                                    uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                                    int* curr_offset, void* stream)
+{
+    using namespace fgs;
+    if (P < 0 || width <= 0 || height <= 0 || block_x <= 0 || block_y <= 0 || pair_capacity < 0) return FGS_ERR_BAD_ARG;
+    if (!cam_position || !cam_rotation || !curr_offset) return FGS_ERR_BAD_ARG;
+    if (P == 0) return FGS_OK;
+    if (!positions || !shs || !opacities || !cov3ds || !points_xy || !rgb_depth || !conic_opacity ||
+        !keys_unsorted || !values_unsorted)
+        return FGS_ERR_BAD_ARG;
+    int* status = device_status_ptr();
+    if (!status) return FGS_ERR_CUDA;
+
+    PreCam cam;
+    host_view_proj(width, height, cam_position, cam_rotation, focal_x, focal_y, zFar, zNear, cam.view, cam.proj);
+    std::memcpy(cam.cam, cam_position, 3 * sizeof(float));
+    cam.tan_fovx = width / (2.0f * focal_x);    // preprocess.cu:465-466
+    cam.tan_fovy = height / (2.0f * focal_y);
+    cam.focal_x = focal_x; cam.focal_y = focal_y;
+    cam.W = width; cam.H = height; cam.block_x = block_x; cam.block_y = block_y;
+    cam.grid_x = (width + block_x - 1) / block_x;
+    cam.grid_y = (height + block_y - 1) / block_y;
+    cam.row_begin = tile_row_begin < 0 ? 0 : tile_row_begin;
+    cam.row_end = (tile_row_end < 0 || tile_row_end > cam.grid_y) ? cam.grid_y : tile_row_end;
+
+    const bool vec = aligned16(positions) && aligned16(shs) && aligned16(opacities) && aligned16(cov3ds);
+    const int blocks = (P + PRE_THREADS - 1) / PRE_THREADS;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (vec)
+        preprocess_kernel<true><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,
+            reinterpret_cast<float2*>(points_xy), reinterpret_cast<float4*>(rgb_depth), reinterpret_cast<float4*>(conic_opacity),
+            keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status);
+    else
+        preprocess_kernel<false><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,
+            reinterpret_cast<float2*>(points_xy), reinterpret_cast<float4*>(rgb_depth), reinterpret_cast<float4*>(conic_opacity),
+            keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status);
+    return launch_status();
+}
+
+extern "C" int fgs_preprocess(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                              int width, int height, int block_x, int block_y,
+                              const float* cam_position, const float* cam_rotation,
+                              float focal_x, float focal_y, float zFar, float zNear,
+                              float* points_xy, float* rgb_depth, float* conic_opacity,
+                              uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                              int* curr_offset, void* stream)
+{
+    return fgs_preprocess_strip(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y,
+                                cam_position, cam_rotation, focal_x, focal_y, zFar, zNear, 0, -1,
+                                points_xy, rgb_depth, conic_opacity, keys_unsorted, values_unsorted, pair_capacity,
+                                curr_offset, stream);
+}

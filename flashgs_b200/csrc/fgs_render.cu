@@ -1,0 +1,323 @@
+// Tile ranges and per-tile front-to-back alpha blending for sm_100a.
+//
+// Replaces flashgs::render_16x16 / 32x16 / 32x32 (csrc/cuda_rasterizer/render.cu:549-608):
+// the memset + identifyTileRanges pair (render.cu:9-31,557) and renderCUDA (render.cu:199-547).
+//
+// Tile ranges: one thread per tile finds the first and one-past-last position of its tile id
+// in the sorted key list by binary search (about 2*log2(R) cached reads per tile instead of a
+// pass over all R keys plus a memset); tiles without pairs get (0,0) as in the reference.
+//
+// Blend: one warp per tile, laid out 8x4 over the tile; a thread owns a TX x TY block of pixels
+// (2x4 for 16x16 tiles). The sorted splat list of the tile is consumed in batches of 32: lane l
+// reads the l-th index of the batch (one coalesced 128-byte read) and gathers that splat's
+// three feature records straight into shared memory with cp.async (8 + 16 + 16 bytes), two
+// batches in flight, so that the gather of batch b+1 and the index read of batch b+2 overlap
+// the arithmetic of batch b. All lanes then read each splat from shared memory as a broadcast.
+// The exponent of a splat at pixel (x, y) is split into per-column terms (computed TX times),
+// a per-row term (TY times) and two FMAs per pixel; alpha = ex2.approx.ftz(exponent).
+//
+// Stop rule, identical to the reference's (render.cu:315,394-407,486-487): splats are consumed
+// two at a time and after each pair a warp vote ends the tile once every pixel of the tile
+// (also those outside the image) has T < 1e-4; pixels already below the threshold keep
+// accumulating until then. There is no alpha clamp and no minimum-alpha skip (render.cu:40-52).
+//
+// Output: the tile's 8-bit RGB rows are assembled in shared memory and leave as 16-byte stores
+// when the image width is a multiple of the tile width; otherwise as guarded byte stores. Nothing
+// outside the image is written.
+
+#include "fgs_common.cuh"
+
+namespace fgs {
+namespace {
+
+constexpr int BLEND_WARPS = 4;      // tiles per block
+constexpr int BATCH = 32;           // splats per staged batch (one per lane)
+constexpr int STAGES = 2;
+
+__global__ void tile_ranges_kernel(const uint64_t* __restrict__ keys, int n, int num_tiles, int2* __restrict__ ranges)
+{
+    const int tile = blockIdx.x * blockDim.x + threadIdx.x;
+    if (tile >= num_tiles) return;
+    // first index whose tile id is >= t
+    auto lower = [&](uint32_t t) {
+        int lo = 0, hi = n;
+        while (lo < hi) {
+            const int mid = (int)(((unsigned)lo + (unsigned)hi) >> 1);
+            if ((uint32_t)(__ldg(keys + mid) >> 32) < t) lo = mid + 1; else hi = mid;
+        }
+        return lo;
+    };
+    const int first = lower((uint32_t)tile);
+    const int last = lower((uint32_t)tile + 1u);
+    ranges[tile] = (last > first) ? make_int2(first, last) : make_int2(0, 0);
+}
+
+__device__ __forceinline__ float ex2_approx_ftz(float x)
+{
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void cp_async_8(void* smem, const void* gmem)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// render.cu:54-57
+__device__ __forceinline__ uint8_t encode_u8(float x) { return (uint8_t)fminf(fmaxf(0.0f, x * 255.0f), 255.0f); }
+
+struct BlendStage {
+    float2 xy[BATCH];
+    float4 con[BATCH];    // conic_opacity record
+    float4 rgbd[BATCH];   // rgb_depth record
+};
+
+template <int BX, int BY, bool EXTRA>
+__global__ void __launch_bounds__(BLEND_WARPS * 32)
+blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point_list,
+             int width, int height, int grid_x, int row_begin, int num_strip_tiles,
+             const float2* __restrict__ points_xy, const float4* __restrict__ rgb_depth,
+             const float4* __restrict__ conic_opacity,
+             float bg_r, float bg_g, float bg_b, int vector_store,
+             uint8_t* __restrict__ out_color, float* __restrict__ out_rgb, float* __restrict__ out_alpha,
+             float* __restrict__ out_depth, int* __restrict__ consumed)
+{
+    constexpr int TX = BX / 8, TY = BY / 4;
+    __shared__ __align__(16) BlendStage s_stage[BLEND_WARPS][STAGES];
+    __shared__ __align__(16) uint8_t s_out[BLEND_WARPS][BY][BX * 3];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int strip_tile = blockIdx.x * BLEND_WARPS + warp;
+    if (strip_tile >= num_strip_tiles) return;          // whole warp leaves; no block-wide barrier is used
+    const int tile_y = row_begin + strip_tile / grid_x;
+    const int tile_x = strip_tile - (strip_tile / grid_x) * grid_x;
+    const int tile = tile_y * grid_x + tile_x;
+    const int2 range = ranges[tile];
+    const int n = range.y - range.x;
+    BlendStage* stage = s_stage[warp];
+
+    const int lx = lane & 7, ly = lane >> 3;
+    const int px0 = tile_x * BX + lx * TX, py0 = tile_y * BY + ly * TY;
+    float pxf[TX], pyf[TY];
+#pragma unroll
+    for (int j = 0; j < TX; j++) pxf[j] = (float)(px0 + j);
+#pragma unroll
+    for (int i = 0; i < TY; i++) pyf[i] = (float)(py0 + i);
+
+    float T[TY][TX], Cr[TY][TX], Cg[TY][TX], Cb[TY][TX], D[TY][TX];
+#pragma unroll
+    for (int i = 0; i < TY; i++)
+#pragma unroll
+        for (int j = 0; j < TX; j++) { T[i][j] = 1.0f; Cr[i][j] = Cg[i][j] = Cb[i][j] = 0.0f; D[i][j] = 0.0f; }
+
+    int used = 0;
+    if (n > 0) {
+        const uint32_t* list = point_list + range.x;
+        const int batches = (n + BATCH - 1) / BATCH;
+        auto gather = [&](int b, uint32_t idx) {
+            if (b * BATCH + lane < n) {
+                BlendStage& s = stage[b % STAGES];
+                cp_async_8(&s.xy[lane], points_xy + idx);
+                cp_async_16(&s.con[lane], conic_opacity + idx);
+                cp_async_16(&s.rgbd[lane], rgb_depth + idx);
+            }
+            cp_async_commit();
+        };
+        uint32_t idx_next = (lane < n) ? __ldg(list + lane) : 0u;
+        gather(0, idx_next);
+        idx_next = (BATCH + lane < n) ? __ldg(list + BATCH + lane) : 0u;
+
+        bool stop = false;
+        for (int b = 0; b < batches && !stop; b++) {
+            if (b + 1 < batches) {
+                gather(b + 1, idx_next);
+                idx_next = ((b + 2) * BATCH + lane < n) ? __ldg(list + (b + 2) * BATCH + lane) : 0u;
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncwarp();
+            const BlendStage& s = stage[b % STAGES];
+            const int cnt = min(BATCH, n - b * BATCH);
+            for (int k = 0; k < cnt; k += 2) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    if (k + h < cnt) {
+                        const float2 xy = s.xy[k + h];
+                        const float4 co = s.con[k + h];
+                        const float4 rd = s.rgbd[k + h];
+                        float A[TX], B[TX];
+#pragma unroll
+                        for (int j = 0; j < TX; j++) {
+                            const float dx = xy.x - pxf[j];
+                            A[j] = fmaf(co.x * dx, dx, co.w);
+                            B[j] = co.y * dx;
+                        }
+#pragma unroll
+                        for (int i = 0; i < TY; i++) {
+                            const float dy = xy.y - pyf[i];
+#pragma unroll
+                            for (int j = 0; j < TX; j++) {
+                                const float t = fmaf(co.z, dy, B[j]);
+                                const float power = fmaf(t, dy, A[j]);
+                                const float alpha = ex2_approx_ftz(power);
+                                const float aT = alpha * T[i][j];
+                                Cr[i][j] = fmaf(rd.x, aT, Cr[i][j]);
+                                Cg[i][j] = fmaf(rd.y, aT, Cg[i][j]);
+                                Cb[i][j] = fmaf(rd.z, aT, Cb[i][j]);
+                                if (EXTRA) D[i][j] = fmaf(rd.w, aT, D[i][j]);
+                                T[i][j] -= aT;
+                            }
+                        }
+                    }
+                }
+                bool done = true;
+#pragma unroll
+                for (int i = 0; i < TY; i++)
+#pragma unroll
+                    for (int j = 0; j < TX; j++) done = done && (T[i][j] < 0.0001f);
+                if (__all_sync(FULL_MASK, done)) { stop = true; used = b * BATCH + min(k + 2, cnt); break; }
+            }
+            __syncwarp();
+        }
+        if (!stop) used = n;
+        cp_async_wait<0>();
+    }
+    if (EXTRA && consumed && lane == 0) consumed[tile] = used;
+
+    // ---- write-out (render.cu:59-73; background-only tiles: render.cu:530-546, here bounds-checked) ----
+    uint8_t (*so)[BX * 3] = s_out[warp];
+#pragma unroll
+    for (int i = 0; i < TY; i++)
+#pragma unroll
+        for (int j = 0; j < TX; j++) {
+            const float Traw = T[i][j];
+            const float Tq = (n > 0 && Traw < 0.0001f) ? 0.0f : Traw;
+            const float r = Cr[i][j] + Tq * bg_r, g = Cg[i][j] + Tq * bg_g, bl = Cb[i][j] + Tq * bg_b;
+            const int cx = lx * TX + j, cy = ly * TY + i;
+            so[cy][cx * 3 + 0] = encode_u8(r);
+            so[cy][cx * 3 + 1] = encode_u8(g);
+            so[cy][cx * 3 + 2] = encode_u8(bl);
+            if (EXTRA) {
+                const int X = px0 + j, Y = py0 + i;
+                if (X < width && Y < height) {
+                    const size_t pix = (size_t)Y * width + X;
+                    if (out_rgb) { out_rgb[3 * pix] = r; out_rgb[3 * pix + 1] = g; out_rgb[3 * pix + 2] = bl; }
+                    if (out_alpha) out_alpha[pix] = 1.0f - Traw;
+                    if (out_depth) out_depth[pix] = D[i][j];
+                }
+            }
+        }
+    if (out_color == nullptr) return;
+    __syncwarp();
+    const int X0 = tile_x * BX, Y0 = tile_y * BY;
+    if (vector_store) {
+        constexpr int CHUNKS_PER_ROW = BX * 3 / 16;
+        for (int c = lane; c < BY * CHUNKS_PER_ROW; c += 32) {
+            const int row = c / CHUNKS_PER_ROW, part = c - row * CHUNKS_PER_ROW;
+            if (Y0 + row < height) {
+                const uint4 v = *reinterpret_cast<const uint4*>(&so[row][part * 16]);
+                *reinterpret_cast<uint4*>(out_color + ((size_t)(Y0 + row) * width + X0) * 3 + part * 16) = v;
+            }
+        }
+    } else {
+        for (int c = lane; c < BY * BX * 3; c += 32) {
+            const int row = c / (BX * 3), col = c - row * (BX * 3);
+            const int X = X0 + col / 3;
+            if (Y0 + row < height && X < width)
+                out_color[((size_t)(Y0 + row) * width + X) * 3 + (col - (col / 3) * 3)] = so[row][col];
+        }
+    }
+}
+
+template <int BX, int BY>
+int launch_render(int num_rendered, int width, int height,
+                  const float* points_xy, const float* rgb_depth, const float* conic_opacity,
+                  const uint64_t* keys_sorted, const uint32_t* values_sorted, int* ranges, const float* bg,
+                  int row_begin, int row_end,
+                  uint8_t* out_color, float* out_rgb, float* out_alpha, float* out_depth, int* consumed, cudaStream_t st)
+{
+    const int grid_x = (width + BX - 1) / BX, grid_y = (height + BY - 1) / BY;
+    const int num_tiles = grid_x * grid_y;
+    if (row_begin < 0) row_begin = 0;
+    if (row_end < 0 || row_end > grid_y) row_end = grid_y;
+    tile_ranges_kernel<<<(num_tiles + 255) / 256, 256, 0, st>>>(keys_sorted, num_rendered, num_tiles,
+                                                               reinterpret_cast<int2*>(ranges));
+    if (row_end <= row_begin) return launch_status();
+    const int strip_tiles = (row_end - row_begin) * grid_x;
+    const int blocks = (strip_tiles + BLEND_WARPS - 1) / BLEND_WARPS;
+    const int vec = (out_color != nullptr) && (width % BX == 0) && aligned16(out_color);
+    const bool extra = out_rgb || out_alpha || out_depth || consumed;
+    if (extra)
+        blend_kernel<BX, BY, true><<<blocks, BLEND_WARPS * 32, 0, st>>>(
+            reinterpret_cast<const int2*>(ranges), values_sorted, width, height, grid_x, row_begin, strip_tiles,
+            reinterpret_cast<const float2*>(points_xy), reinterpret_cast<const float4*>(rgb_depth),
+            reinterpret_cast<const float4*>(conic_opacity), bg[0], bg[1], bg[2], vec,
+            out_color, out_rgb, out_alpha, out_depth, consumed);
+    else
+        blend_kernel<BX, BY, false><<<blocks, BLEND_WARPS * 32, 0, st>>>(
+            reinterpret_cast<const int2*>(ranges), values_sorted, width, height, grid_x, row_begin, strip_tiles,
+            reinterpret_cast<const float2*>(points_xy), reinterpret_cast<const float4*>(rgb_depth),
+            reinterpret_cast<const float4*>(conic_opacity), bg[0], bg[1], bg[2], vec,
+            out_color, nullptr, nullptr, nullptr, nullptr);
+    return launch_status();
+}
+
+} // namespace
+} // namespace fgs
+
+extern "C" int fgs_tile_ranges(int num_rendered, int num_tiles, const uint64_t* keys_sorted, int* ranges, void* stream)
+{
+    if (num_rendered < 0 || num_tiles <= 0 || !ranges || (num_rendered > 0 && !keys_sorted)) return FGS_ERR_BAD_ARG;
+    fgs::tile_ranges_kernel<<<(num_tiles + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        keys_sorted, num_rendered, num_tiles, reinterpret_cast<int2*>(ranges));
+    return fgs::launch_status();
+}
+
+extern "C" int fgs_render_ex(int block_x, int block_y, int num_rendered, int width, int height,
+                             const float* points_xy, const float* rgb_depth, const float* conic_opacity,
+                             const uint64_t* keys_sorted, const uint32_t* values_sorted,
+                             int* ranges, const float* bg_color,
+                             int tile_row_begin, int tile_row_end,
+                             uint8_t* out_color, float* out_rgb, float* out_alpha, float* out_depth, int* consumed,
+                             void* stream)
+{
+    using namespace fgs;
+    if (num_rendered < 0 || width <= 0 || height <= 0 || !ranges || !bg_color) return FGS_ERR_BAD_ARG;
+    if (!out_color && !out_rgb && !out_alpha && !out_depth && !consumed) return FGS_ERR_BAD_ARG;
+    if (num_rendered > 0 && (!points_xy || !rgb_depth || !conic_opacity || !keys_sorted || !values_sorted)) return FGS_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define FGS_RENDER_CASE(BX, BY)                                                                                        \
+    if (block_x == BX && block_y == BY)                                                                                \
+        return launch_render<BX, BY>(num_rendered, width, height, points_xy, rgb_depth, conic_opacity, keys_sorted,     \
+                                     values_sorted, ranges, bg_color, tile_row_begin, tile_row_end, out_color, out_rgb, \
+                                     out_alpha, out_depth, consumed, st);
+    FGS_RENDER_CASE(16, 16)
+    FGS_RENDER_CASE(32, 16)
+    FGS_RENDER_CASE(32, 32)
+#undef FGS_RENDER_CASE
+    return FGS_ERR_BAD_ARG;
+}
+
+#define FGS_RENDER_ENTRY(NAME, BX, BY)                                                                               \
+    extern "C" int NAME(int num_rendered, int width, int height, const float* points_xy, const float* rgb_depth,     \
+                        const float* conic_opacity, const uint64_t* keys_sorted, const uint32_t* values_sorted,      \
+                        int* ranges, const float* bg_color, uint8_t* out_color, void* stream)                        \
+    {                                                                                                                \
+        if (!out_color) return FGS_ERR_BAD_ARG;                                                                      \
+        return fgs_render_ex(BX, BY, num_rendered, width, height, points_xy, rgb_depth, conic_opacity, keys_sorted,  \
+                             values_sorted, ranges, bg_color, 0, -1, out_color, nullptr, nullptr, nullptr, nullptr,  \
+                             stream);                                                                                \
+    }
+FGS_RENDER_ENTRY(fgs_render_16x16, 16, 16)
+FGS_RENDER_ENTRY(fgs_render_32x16, 32, 16)
+FGS_RENDER_ENTRY(fgs_render_32x32, 32, 32)
+#undef FGS_RENDER_ENTRY

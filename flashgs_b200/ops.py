@@ -1,0 +1,197 @@
+"""Operator API of the reference, backed by the sm_100a library.
+
+Same function names, positional arguments and argument meaning as the module the
+reference binds with pybind11 (``flash_gaussian_splatting.ops``,
+csrc/pybind.cpp:122-271): PyTorch tensors in, results written into caller-owned
+tensors. Each function is a thin shim that hands raw pointers to the C ABI of
+``libflashgs_b200.so``; camera position/rotation and the background colour are
+read on the host and therefore must be CPU tensors (csrc/pybind.cpp:131-143,177),
+everything else must live on the current CUDA device.
+
+Differences from the reference, all on the strict side:
+  * a non-zero status of the C ABI raises ``RuntimeError`` (the reference checks
+    no launch at all);
+  * output tensors must be contiguous (the reference would silently write into a
+    temporary, csrc/pybind.cpp:145-148);
+  * the render ops never write outside the image (the reference does for empty
+    tiles on a partial last tile row, csrc/cuda_rasterizer/render.cu:530-546).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import FlashGSError  # noqa: F401  (re-exported)
+
+_L = _lib.load()
+
+
+def _stream() -> int:
+    # The reference always launches on the legacy default stream (its bindings pass no
+    # stream); torch's current stream is that stream unless the caller changed it.
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(t: torch.Tensor, name: str, dtype=None) -> int:
+    if not t.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor" % name)
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError("%s must have dtype %s, got %s" % (name, dtype, t.dtype))
+    return t.data_ptr()
+
+
+def _in(t: torch.Tensor, name: str, dtype) -> torch.Tensor:
+    if not t.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor" % name)
+    if t.dtype != dtype:
+        raise RuntimeError("%s must have dtype %s, got %s" % (name, dtype, t.dtype))
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _out(t: torch.Tensor, name: str, dtype) -> torch.Tensor:
+    if not t.is_contiguous():
+        raise RuntimeError("%s is written in place and must be contiguous" % name)
+    return _in(t, name, dtype)
+
+
+def _host(t: torch.Tensor, name: str, n: int) -> torch.Tensor:
+    if t.is_cuda:
+        raise RuntimeError("%s is read on the host and must be a CPU tensor" % name)
+    t = t.to(torch.float32).contiguous()
+    if t.numel() < n:
+        raise RuntimeError("%s needs %d elements" % (name, n))
+    return t
+
+
+def loadPly(path: str):
+    """Scene loading is not part of the per-frame path; see ``flashgs_b200.ply.load_ply``."""
+    from .ply import load_ply
+    return load_ply(path)
+
+
+def preprocess(orig_points, shs, opacities, cov3Ds, width, height, block_x, block_y,
+               position, rotation, focal_x, focal_y, zFar, zNear,
+               points_xy, rgb_depth, conic_opacity,
+               gaussian_keys_unsorted, gaussian_values_unsorted, curr_offset,
+               tile_row_begin: int = 0, tile_row_end: int = -1) -> None:
+    """csrc/pybind.cpp:122-150. The two trailing keyword arguments restrict the pairs to a strip of tile rows."""
+    f32 = torch.float32
+    pts = _in(orig_points, "orig_points", f32)
+    sh = _in(shs, "shs", f32)
+    op = _in(opacities, "opacities", f32)
+    cov = _in(cov3Ds, "cov3Ds", f32)
+    pos = _host(position, "position", 3)
+    rot = _host(rotation, "rotation", 9)
+    xy = _out(points_xy, "points_xy", f32)
+    rd = _out(rgb_depth, "rgb_depth", f32)
+    co = _out(conic_opacity, "conic_opacity", f32)
+    keys = _out(gaussian_keys_unsorted, "gaussian_keys_unsorted", torch.int64)
+    vals = _out(gaussian_values_unsorted, "gaussian_values_unsorted", torch.int32)
+    off = _out(curr_offset, "curr_offset", torch.int32)
+    P = int(op.size(0))
+    cap = min(int(keys.numel()), int(vals.numel()))
+    st = _L.fgs_preprocess_strip(P, pts.data_ptr(), sh.data_ptr(), op.data_ptr(), cov.data_ptr(),
+                                 int(width), int(height), int(block_x), int(block_y),
+                                 pos.data_ptr(), rot.data_ptr(),
+                                 float(focal_x), float(focal_y), float(zFar), float(zNear),
+                                 int(tile_row_begin), int(tile_row_end),
+                                 xy.data_ptr(), rd.data_ptr(), co.data_ptr(),
+                                 keys.data_ptr(), vals.data_ptr(), cap, off.data_ptr(), _stream())
+    _lib.check("preprocess", st)
+
+
+def get_sort_buffer_size(num_rendered: int) -> int:
+    """csrc/pybind.cpp:165-168."""
+    return int(_L.fgs_sort_temp_bytes(int(num_rendered)))
+
+
+def sort_gaussian(num_rendered, width, height, block_x, block_y, list_sorting_space,
+                  gaussian_keys_unsorted, gaussian_values_unsorted,
+                  gaussian_keys_sorted, gaussian_values_sorted) -> None:
+    """csrc/pybind.cpp:152-163."""
+    n = int(num_rendered)
+    ki = _in(gaussian_keys_unsorted, "gaussian_keys_unsorted", torch.int64)
+    vi = _in(gaussian_values_unsorted, "gaussian_values_unsorted", torch.int32)
+    ko = _out(gaussian_keys_sorted, "gaussian_keys_sorted", torch.int64)
+    vo = _out(gaussian_values_sorted, "gaussian_values_sorted", torch.int32)
+    if n > min(ki.numel(), vi.numel(), ko.numel(), vo.numel()):
+        raise RuntimeError("sort_gaussian: num_rendered (%d) exceeds the pair buffers" % n)
+    tmp = list_sorting_space
+    if not tmp.is_cuda or not tmp.is_contiguous():
+        raise RuntimeError("list_sorting_space must be a contiguous CUDA tensor")
+    st = _L.fgs_sort_pairs(n, int(width), int(height), int(block_x), int(block_y),
+                           tmp.data_ptr(), tmp.numel() * tmp.element_size(),
+                           ki.data_ptr(), vi.data_ptr(), ko.data_ptr(), vo.data_ptr(), _stream())
+    _lib.check("sort_gaussian", st)
+
+
+def _render(fn_name, block_x, block_y, num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
+            gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color):
+    f32 = torch.float32
+    xy = _in(points_xy, "points_xy", f32)
+    rd = _in(rgb_depth, "rgb_depth", f32)
+    co = _in(conic_opacity, "conic_opacity", f32)
+    ks = _in(gaussian_keys_sorted, "gaussian_keys_sorted", torch.int64)
+    vs = _in(gaussian_values_sorted, "gaussian_values_sorted", torch.int32)
+    rg = _out(ranges, "ranges", torch.int32)
+    bg = _host(bg_color, "bg_color", 3)
+    if not out_color.is_cuda or not out_color.is_contiguous() or out_color.element_size() != 1:
+        raise RuntimeError("out_color must be a contiguous CUDA int8/uint8 tensor")
+    tiles = ((int(width) + block_x - 1) // block_x) * ((int(height) + block_y - 1) // block_y)
+    if rg.numel() < 2 * tiles:
+        raise RuntimeError("ranges holds %d tiles, the image has %d" % (rg.numel() // 2, tiles))
+    if out_color.numel() < int(width) * int(height) * 3:
+        raise RuntimeError("out_color is smaller than height*width*3")
+    st = getattr(_L, fn_name)(int(num_rendered), int(width), int(height),
+                              xy.data_ptr(), rd.data_ptr(), co.data_ptr(), ks.data_ptr(), vs.data_ptr(),
+                              rg.data_ptr(), bg.data_ptr(), out_color.data_ptr(), _stream())
+    _lib.check(fn_name, st)
+
+
+def render_16x16(num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
+                 gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color) -> None:
+    """csrc/pybind.cpp:170-188."""
+    _render("fgs_render_16x16", 16, 16, num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
+            gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color)
+
+
+def render_32x16(num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
+                 gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color) -> None:
+    """csrc/pybind.cpp:190-208."""
+    _render("fgs_render_32x16", 32, 16, num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
+            gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color)
+
+
+def render_32x32(num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
+                 gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color) -> None:
+    """csrc/pybind.cpp:210-228."""
+    _render("fgs_render_32x32", 32, 32, num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
+            gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color)
+
+
+def render_ex(block_x, block_y, num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
+              gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color,
+              out_color=None, out_rgb=None, out_alpha=None, out_depth=None, consumed=None,
+              tile_row_begin: int = 0, tile_row_end: int = -1) -> None:
+    """General render call (no reference counterpart): strips of tile rows and optional float outputs."""
+    f32 = torch.float32
+    bg = _host(bg_color, "bg_color", 3)
+    ptr = lambda t: 0 if t is None else t.data_ptr()  # noqa: E731
+    for t, nm, dt in ((out_rgb, "out_rgb", f32), (out_alpha, "out_alpha", f32), (out_depth, "out_depth", f32),
+                      (consumed, "consumed", torch.int32)):
+        if t is not None:
+            _out(t, nm, dt)
+    st = _L.fgs_render_ex(int(block_x), int(block_y), int(num_rendered), int(width), int(height),
+                          _in(points_xy, "points_xy", f32).data_ptr(), _in(rgb_depth, "rgb_depth", f32).data_ptr(),
+                          _in(conic_opacity, "conic_opacity", f32).data_ptr(),
+                          _in(gaussian_keys_sorted, "gaussian_keys_sorted", torch.int64).data_ptr(),
+                          _in(gaussian_values_sorted, "gaussian_values_sorted", torch.int32).data_ptr(),
+                          _out(ranges, "ranges", torch.int32).data_ptr(), bg.data_ptr(),
+                          int(tile_row_begin), int(tile_row_end),
+                          ptr(out_color), ptr(out_rgb), ptr(out_alpha), ptr(out_depth), ptr(consumed), _stream())
+    _lib.check("render_ex", st)
+
+
+def device_status(reset: bool = True) -> int:
+    """OR of the error bits raised by kernels on the current device since the last reset (synchronises)."""
+    return int(_L.fgs_device_status(1 if reset else 0, _stream()))

@@ -1,0 +1,116 @@
+"""Statically allocated rasterizer: the host-side frame loop of the reference's example.
+
+Mirrors ``Scene`` / ``Rasterizer.forward`` of the reference (example.py:10-27, 45-94):
+all scratch (pair buffers, sort space, tile ranges, feature records) is allocated once,
+and a frame is ``preprocess -> read the pair count -> sort_gaussian -> render_16x16``
+through the operator API. The operator module is a parameter so that the same loop can
+drive any implementation of that API.
+
+Additions that the reference does not have:
+  * ``rows=(begin, end)`` renders only a strip of tile rows (one frame split across GPUs);
+  * the output image can be a caller-owned, reused buffer instead of a fresh
+    ``torch.zeros`` per frame (example.py:89).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops as _ops
+from .scenes import Camera, Scene, tile_grid
+
+
+class DeviceScene:
+    """Gaussian buffers on the device (example.py:10-27)."""
+
+    def __init__(self, scene: Scene, device):
+        self.device = torch.device(device)
+        self.num_vertex = scene.num_vertex
+        self.position = torch.from_numpy(scene.position).to(self.device)
+        self.shs = torch.from_numpy(scene.shs).to(self.device)
+        self.opacity = torch.from_numpy(scene.opacity).to(self.device)
+        self.cov3d = torch.from_numpy(scene.cov3d).to(self.device)
+
+
+class TorchCamera:
+    """Camera with CPU tensors for position / rotation, as example.py:30-41 builds it."""
+
+    def __init__(self, cam: Camera):
+        self.id, self.img_name = cam.id, cam.img_name
+        self.width, self.height = cam.width, cam.height
+        self.position = torch.from_numpy(cam.position.copy())
+        self.rotation = torch.from_numpy(cam.rotation.copy())
+        self.focal_x, self.focal_y = cam.focal_x, cam.focal_y
+        self.zFar, self.zNear = cam.zFar, cam.zNear
+
+
+class Rasterizer:
+    def __init__(self, scene: DeviceScene, MAX_NUM_RENDERED: int, MAX_NUM_TILES: int, ops=_ops, block=(16, 16)):
+        dev = scene.device
+        self.ops = ops
+        self.block = block
+        z = lambda n, dt: torch.zeros(n, device=dev, dtype=dt)  # noqa: E731
+        self.gaussian_keys_unsorted = z(MAX_NUM_RENDERED, torch.int64)
+        self.gaussian_values_unsorted = z(MAX_NUM_RENDERED, torch.int32)
+        self.gaussian_keys_sorted = z(MAX_NUM_RENDERED, torch.int64)
+        self.gaussian_values_sorted = z(MAX_NUM_RENDERED, torch.int32)
+        self.MAX_NUM_RENDERED = MAX_NUM_RENDERED
+        self.MAX_NUM_TILES = MAX_NUM_TILES
+        self.SORT_BUFFER_SIZE = ops.get_sort_buffer_size(MAX_NUM_RENDERED)
+        self.list_sorting_space = z(self.SORT_BUFFER_SIZE, torch.int8)
+        self.ranges = z((MAX_NUM_TILES, 2), torch.int32)
+        self.curr_offset = z(1, torch.int32)
+        self.points_xy = z((scene.num_vertex, 2), torch.float32)
+        self.rgb_depth = z((scene.num_vertex, 4), torch.float32)
+        self.conic_opacity = z((scene.num_vertex, 4), torch.float32)
+        self.num_rendered = 0
+        self._render = {(16, 16): "render_16x16", (32, 16): "render_32x16", (32, 32): "render_32x32"}[tuple(block)]
+
+    def forward(self, scene: DeviceScene, camera, bg_color, out_color=None, rows=None):
+        """One frame (example.py:67-94). Returns the int8 [H,W,3] image tensor."""
+        ops, (bx, by) = self.ops, self.block
+        self.curr_offset.fill_(0)
+        extra = {} if rows is None else dict(tile_row_begin=rows[0], tile_row_end=rows[1])
+        ops.preprocess(scene.position, scene.shs, scene.opacity, scene.cov3d,
+                       camera.width, camera.height, bx, by,
+                       camera.position, camera.rotation,
+                       camera.focal_x, camera.focal_y, camera.zFar, camera.zNear,
+                       self.points_xy, self.rgb_depth, self.conic_opacity,
+                       self.gaussian_keys_unsorted, self.gaussian_values_unsorted,
+                       self.curr_offset, **extra)
+        num_rendered = int(self.curr_offset.cpu()[0])
+        if num_rendered >= self.MAX_NUM_RENDERED:
+            raise RuntimeError("Too many k-v pairs! (%d >= %d)" % (num_rendered, self.MAX_NUM_RENDERED))
+        self.num_rendered = num_rendered
+        ops.sort_gaussian(num_rendered, camera.width, camera.height, bx, by,
+                          self.list_sorting_space,
+                          self.gaussian_keys_unsorted, self.gaussian_values_unsorted,
+                          self.gaussian_keys_sorted, self.gaussian_values_sorted)
+        if out_color is None:
+            out_color = torch.zeros((camera.height, camera.width, 3), device=scene.device, dtype=torch.int8)
+        if rows is None:
+            getattr(ops, self._render)(num_rendered, camera.width, camera.height,
+                                       self.points_xy, self.rgb_depth, self.conic_opacity,
+                                       self.gaussian_keys_sorted, self.gaussian_values_sorted,
+                                       self.ranges, bg_color, out_color)
+        else:
+            ops.render_ex(bx, by, num_rendered, camera.width, camera.height,
+                          self.points_xy, self.rgb_depth, self.conic_opacity,
+                          self.gaussian_keys_sorted, self.gaussian_values_sorted,
+                          self.ranges, bg_color, out_color=out_color,
+                          tile_row_begin=rows[0], tile_row_end=rows[1])
+        return out_color
+
+
+def strip_rows(grid_y: int, world_size: int, rank: int):
+    """Tile rows [begin, end) of ``rank`` when ``grid_y`` rows are dealt out as evenly as possible."""
+    base, rem = divmod(grid_y, world_size)
+    begin = rank * base + min(rank, rem)
+    return begin, begin + base + (1 if rank < rem else 0)
+
+
+def save_ppm(image: torch.Tensor, path: str) -> None:
+    """Binary PPM writer (example.py:97-102)."""
+    image = image.cpu()
+    assert image.dim() >= 3 and image.size(2) == 3
+    with open(path, "wb") as f:
+        f.write(b"P6\n" + f"{image.size(1)} {image.size(0)}\n255\n".encode() + image.numpy().tobytes())

@@ -1,0 +1,171 @@
+/*
+ * flashgs_b200 -- C ABI of the B200 (sm_100a) forward 3D Gaussian Splatting raster path.
+ *
+ * The entry points below are what a binding of the reference's operator API
+ * (namespace flashgs, csrc/ops.h:32-65, bound to Python in csrc/pybind.cpp:233-271)
+ * needs: plain pointers and sizes, no C++ or torch types. Unless stated otherwise
+ * every pointer is a DEVICE pointer on the current CUDA device, every buffer is
+ * owned by the caller, nothing is allocated and no state is kept between calls,
+ * all work is enqueued on `stream` (a cudaStream_t passed as void*, NULL = the
+ * legacy default stream, which is what the reference's bindings always use) and
+ * the call returns without waiting for the GPU.
+ *
+ * Every function returns FGS_OK (0) or one of the FGS_ERR_* codes. Failures
+ * detected on the device (pair buffer overflow, a look-back wait that ran out of
+ * its poll budget) are recorded in a per-device status word that
+ * fgs_device_status() reads.
+ */
+#ifndef FLASHGS_B200_H
+#define FLASHGS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FGS_OK 0
+#define FGS_ERR_BAD_ARG 1          /* null pointer, non-positive size, unsupported tile shape */
+#define FGS_ERR_CUDA 2             /* a CUDA runtime call or kernel launch failed */
+#define FGS_ERR_PAIR_OVERFLOW 4    /* more (tile, Gaussian) pairs than the pair buffers hold */
+#define FGS_ERR_LOOKBACK_TIMEOUT 8 /* a bounded device-side wait gave up */
+#define FGS_ERR_TEMP_TOO_SMALL 16  /* sort scratch smaller than fgs_sort_temp_bytes() */
+
+/* Version of this ABI; bumped when a signature changes. */
+int fgs_abi_version(void);
+
+/* Human-readable name of a status code (static storage). */
+const char* fgs_status_string(int status);
+
+/*
+ * Reads (and, if `reset` is non-zero, clears) the device status word of the
+ * current device: an OR of the FGS_ERR_* codes raised by kernels since the last
+ * reset. Synchronises `stream`. Returns a negative value if the read itself failed.
+ */
+int fgs_device_status(int reset, void* stream);
+
+/*
+ * Host-only helper: the 4x4 view and view-projection matrices (column-major,
+ * 16 floats each) the preprocess stage uses. Replaces getViewMatrix /
+ * getProjectionMatrix (csrc/cuda_rasterizer/preprocess.cu:420-448).
+ * `cam_position` (3 floats) and `cam_rotation` (9 floats, camera-to-world,
+ * row-major) are HOST pointers.
+ */
+int fgs_view_proj_matrices(int width, int height, const float* cam_position, const float* cam_rotation,
+                           float focal_x, float focal_y, float zFar, float zNear,
+                           float* view16, float* proj16);
+
+/*
+ * Cull, project, shade and duplicate. Replaces flashgs::preprocess
+ * (csrc/ops.h:32-39, csrc/cuda_rasterizer/preprocess.cu:243-418,452-488).
+ *
+ *   positions [P,3], shs [P,48] ([coef][rgb]), opacities [P], cov3ds [P,6]   inputs, fp32
+ *   cam_position [3], cam_rotation [9]                                       HOST pointers
+ *   points_xy [P,2], rgb_depth [P,4], conic_opacity [P,4]                    outputs, written only for
+ *                                                                            Gaussians that emit a pair
+ *   keys_unsorted [pair_capacity] = (tile_id << 32) | float_bits(depth)
+ *   values_unsorted [pair_capacity] = Gaussian index
+ *   curr_offset [1]   in/out pair counter; the caller zeroes it before the call
+ *                     (example.py:69); it keeps counting past pair_capacity while
+ *                     stores beyond the capacity are dropped and
+ *                     FGS_ERR_PAIR_OVERFLOW is raised in the device status word.
+ *
+ * The order of pairs is unspecified (as in the reference, where it is the arrival
+ * order of atomics).
+ */
+int fgs_preprocess(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                   int width, int height, int block_x, int block_y,
+                   const float* cam_position, const float* cam_rotation,
+                   float focal_x, float focal_y, float zFar, float zNear,
+                   float* points_xy, float* rgb_depth, float* conic_opacity,
+                   uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                   int* curr_offset, void* stream);
+
+/*
+ * Same as fgs_preprocess, restricted to tile rows [tile_row_begin, tile_row_end):
+ * pairs are emitted only for tiles of those rows, with GLOBAL tile ids, so that the
+ * union of the strips' pair sets equals the whole-frame pair set. Used to split one
+ * frame into horizontal strips across GPUs. No counterpart in the reference, which
+ * is single-GPU (csrc/cuda_rasterizer/preprocess.cu:314 is the rule that drops
+ * Gaussians whose clamped tile rectangle is empty; the strip clamp reuses it).
+ */
+int fgs_preprocess_strip(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                         int width, int height, int block_x, int block_y,
+                         const float* cam_position, const float* cam_rotation,
+                         float focal_x, float focal_y, float zFar, float zNear,
+                         int tile_row_begin, int tile_row_end,
+                         float* points_xy, float* rgb_depth, float* conic_opacity,
+                         uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                         int* curr_offset, void* stream);
+
+/*
+ * Scratch bytes fgs_sort_pairs needs for up to `num_rendered` pairs. Replaces
+ * flashgs::get_sort_buffer_size (csrc/ops.h:47, csrc/cuda_rasterizer/sort.cu:46-54). Host-only.
+ */
+size_t fgs_sort_temp_bytes(int64_t num_rendered);
+
+/*
+ * Stable radix sort of (key, value) pairs on key bits [0, 32 + bit_length(#tiles)).
+ * Replaces flashgs::sort_gaussian (csrc/ops.h:41-45, csrc/cuda_rasterizer/sort.cu:28-44).
+ * Inputs are left intact; outputs go to keys_sorted / values_sorted; `temp` must be
+ * 16-byte aligned and at least fgs_sort_temp_bytes(num_rendered) bytes.
+ */
+int fgs_sort_pairs(int num_rendered, int width, int height, int block_x, int block_y,
+                   void* temp, size_t temp_bytes,
+                   const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                   uint64_t* keys_sorted, uint32_t* values_sorted, void* stream);
+
+/*
+ * Tile ranges + front-to-back alpha blending into an 8-bit RGB image.
+ * Replace flashgs::render_16x16 / render_32x16 / render_32x32
+ * (csrc/ops.h:49-65, csrc/cuda_rasterizer/render.cu:549-608).
+ *
+ *   ranges [tiles,2] int32   scratch/out: [first, one-past-last) index of each tile in the
+ *                            sorted list, (0,0) for tiles without pairs
+ *   bg_color [3]             HOST pointer
+ *   out_color [H,W,3] uint8  every pixel of the image is written; nothing outside it is
+ */
+int fgs_render_16x16(int num_rendered, int width, int height,
+                     const float* points_xy, const float* rgb_depth, const float* conic_opacity,
+                     const uint64_t* keys_sorted, const uint32_t* values_sorted,
+                     int* ranges, const float* bg_color, uint8_t* out_color, void* stream);
+int fgs_render_32x16(int num_rendered, int width, int height,
+                     const float* points_xy, const float* rgb_depth, const float* conic_opacity,
+                     const uint64_t* keys_sorted, const uint32_t* values_sorted,
+                     int* ranges, const float* bg_color, uint8_t* out_color, void* stream);
+int fgs_render_32x32(int num_rendered, int width, int height,
+                     const float* points_xy, const float* rgb_depth, const float* conic_opacity,
+                     const uint64_t* keys_sorted, const uint32_t* values_sorted,
+                     int* ranges, const float* bg_color, uint8_t* out_color, void* stream);
+
+/*
+ * General form of the render entry points: any of the three tile shapes, an
+ * optional restriction to tile rows [tile_row_begin, tile_row_end) (only those
+ * rows of the image are written; pass 0 and -1 for the whole frame), and optional
+ * float outputs that the reference does not have (any of them may be NULL):
+ *   out_rgb [H,W,3]  = C + T*bg before quantisation
+ *   out_alpha [H,W]  = 1 - T
+ *   out_depth [H,W]  = sum of depth_i * alpha_i * T_i
+ *   consumed [tiles] = number of splats blended per tile (the reference's stop rule,
+ *                      csrc/cuda_rasterizer/render.cu:315,394-407)
+ * out_color may be NULL when only float outputs are wanted.
+ */
+int fgs_render_ex(int block_x, int block_y, int num_rendered, int width, int height,
+                  const float* points_xy, const float* rgb_depth, const float* conic_opacity,
+                  const uint64_t* keys_sorted, const uint32_t* values_sorted,
+                  int* ranges, const float* bg_color,
+                  int tile_row_begin, int tile_row_end,
+                  uint8_t* out_color, float* out_rgb, float* out_alpha, float* out_depth, int* consumed,
+                  void* stream);
+
+/*
+ * Tile ranges only (the first half of the render entry points). Replaces
+ * identifyTileRanges plus the memset before it (csrc/cuda_rasterizer/render.cu:9-31,557).
+ */
+int fgs_tile_ranges(int num_rendered, int num_tiles, const uint64_t* keys_sorted, int* ranges, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHGS_B200_H */
