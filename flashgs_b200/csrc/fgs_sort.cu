@@ -267,12 +267,15 @@ extern "C" size_t fgs_sort_temp_bytes(int64_t num_rendered)
     return fgs::make_layout(num_rendered).total;
 }
 
-extern "C" int fgs_sort_pairs(int num_rendered, int width, int height, int block_x, int block_y,
-                              void* temp, size_t temp_bytes,
-                              const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
-                              uint64_t* keys_sorted, uint32_t* values_sorted, void* stream)
+namespace fgs {
+// `events`, when given, receives passes + 2 recorded events: before the histogram kernel, after it,
+// and after every onesweep pass; `passes_out` receives the pass count.
+static int sort_pairs_impl(int num_rendered, int width, int height, int block_x, int block_y,
+                           void* temp, size_t temp_bytes,
+                           const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                           uint64_t* keys_sorted, uint32_t* values_sorted, void* stream,
+                           cudaEvent_t* events, int* passes_out)
 {
-    using namespace fgs;
     if (num_rendered < 0 || num_rendered >= (1 << 30) || width <= 0 || height <= 0 || block_x <= 0 || block_y <= 0)
         return FGS_ERR_BAD_ARG;
     if (num_rendered == 0) return FGS_OK;
@@ -309,8 +312,11 @@ extern "C" int fgs_sort_pairs(int num_rendered, int width, int height, int block
     const size_t clear_bytes = L.status_off + (size_t)passes * L.parts * RADIX * 4;
     if (cudaMemsetAsync(base, 0, clear_bytes, st) != cudaSuccess) return FGS_ERR_CUDA;
 
+    if (passes_out) *passes_out = passes;
+    if (events) cudaEventRecord(events[0], st);
     int hist_blocks = L.parts < 148 * 8 ? L.parts : 148 * 8;
     histogram_kernel<<<hist_blocks, SORT_THREADS, 0, st>>>(keys_unsorted, n, passes, end_bit, hist);
+    if (events) cudaEventRecord(events[1], st);
 
     const uint64_t* src_k = keys_unsorted;
     const uint32_t* src_v = values_unsorted;
@@ -326,6 +332,42 @@ extern "C" int fgs_sort_pairs(int num_rendered, int width, int height, int block
                                                          dev_status, g_debug_skip_publish_part);
         src_k = dst_k;
         src_v = dst_v;
+        if (events) cudaEventRecord(events[2 + p], st);
     }
     return launch_status();
+}
+} // namespace fgs
+
+extern "C" int fgs_sort_pairs(int num_rendered, int width, int height, int block_x, int block_y,
+                              void* temp, size_t temp_bytes,
+                              const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                              uint64_t* keys_sorted, uint32_t* values_sorted, void* stream)
+{
+    return fgs::sort_pairs_impl(num_rendered, width, height, block_x, block_y, temp, temp_bytes, keys_unsorted,
+                                values_unsorted, keys_sorted, values_sorted, stream, nullptr, nullptr);
+}
+
+extern "C" int fgs_sort_pairs_profile(int num_rendered, int width, int height, int block_x, int block_y,
+                                      void* temp, size_t temp_bytes,
+                                      const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                                      uint64_t* keys_sorted, uint32_t* values_sorted, void* stream,
+                                      float* launch_ms, int launch_ms_len, int* num_launches)
+{
+    using namespace fgs;
+    if (!launch_ms || !num_launches || launch_ms_len < MAX_PASSES + 1) return FGS_ERR_BAD_ARG;
+    cudaEvent_t ev[MAX_PASSES + 2];
+    for (auto& e : ev)
+        if (cudaEventCreate(&e) != cudaSuccess) return FGS_ERR_CUDA;
+    int passes = 0;
+    int st = sort_pairs_impl(num_rendered, width, height, block_x, block_y, temp, temp_bytes, keys_unsorted,
+                             values_unsorted, keys_sorted, values_sorted, stream, ev, &passes);
+    *num_launches = 0;
+    if (st == FGS_OK && num_rendered > 0) {
+        if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) st = FGS_ERR_CUDA;
+        for (int i = 0; st == FGS_OK && i < passes + 1; i++)
+            if (cudaEventElapsedTime(&launch_ms[i], ev[i], ev[i + 1]) != cudaSuccess) st = FGS_ERR_CUDA;
+        if (st == FGS_OK) *num_launches = passes + 1;
+    }
+    for (auto& e : ev) cudaEventDestroy(e);
+    return st;
 }

@@ -117,6 +117,19 @@ int fgs_sort_pairs(int num_rendered, int width, int height, int block_x, int blo
                    uint64_t* keys_sorted, uint32_t* values_sorted, void* stream);
 
 /*
+ * fgs_sort_pairs with CUDA events recorded around each of its kernel launches; waits for the
+ * stream and fills launch_ms[0] (histogram kernel) and launch_ms[1..] (one onesweep pass each);
+ * *num_launches receives how many entries were filled (0 when num_rendered is 0). launch_ms must
+ * hold at least 9 floats. A measurement aid for benchmarks: it creates and destroys events and
+ * blocks the host, so it is not for the frame loop. No counterpart in the reference.
+ */
+int fgs_sort_pairs_profile(int num_rendered, int width, int height, int block_x, int block_y,
+                           void* temp, size_t temp_bytes,
+                           const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                           uint64_t* keys_sorted, uint32_t* values_sorted, void* stream,
+                           float* launch_ms, int launch_ms_len, int* num_launches);
+
+/*
  * Tile ranges + front-to-back alpha blending into an 8-bit RGB image.
  * Replace flashgs::render_16x16 / render_32x16 / render_32x32
  * (csrc/ops.h:49-65, csrc/cuda_rasterizer/render.cu:549-608).

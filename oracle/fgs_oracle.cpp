@@ -25,6 +25,7 @@
 #include <cstdint>
 #include <cstring>
 #include <numeric>
+#include <parallel/algorithm>
 #include <vector>
 #ifdef _OPENMP
 #include <omp.h>
@@ -334,7 +335,9 @@ void fgso_sort(int64_t n, int width, int height, int block_x, int block_y,
     const uint64_t mask = end_bit >= 64 ? ~0ull : ((1ull << end_bit) - 1);
     std::vector<int64_t> idx((size_t)n);
     std::iota(idx.begin(), idx.end(), 0);
-    std::stable_sort(idx.begin(), idx.end(), [&](int64_t a, int64_t b) { return (keys_in[a] & mask) < (keys_in[b] & mask); });
+    // multi-threaded merge sort; stable like the reference's radix sort
+    __gnu_parallel::stable_sort(idx.begin(), idx.end(), [&](int64_t a, int64_t b) { return (keys_in[a] & mask) < (keys_in[b] & mask); });
+#pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; i++) { keys_out[i] = keys_in[idx[i]]; vals_out[i] = vals_in[idx[i]]; }
 }
 

@@ -1,0 +1,80 @@
+"""Host-side logic of the multi-GPU strip split, exercised with two CPU ranks over gloo.
+
+Each rank "renders" its strip with the CPU oracle (the renderer is injected; the product
+code under test is the partition and gather logic of flashgs_b200.parallel).
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from flashgs_b200 import parallel, scenes
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out_path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import oracle
+        w, sc, cams = scenes.make_workload("C1", 6000)
+        cam = cams[0]
+        gy = scenes.tile_grid(cam.width, cam.height)[1]
+        rows = [parallel.strip_rows(gy, world, r) for r in range(world)]
+        mine = oracle.render_frame(sc, cam, rows=rows[rank], floats=False)
+        local = torch.from_numpy(mine["u8"])
+        # rows outside the strip must not matter: poison them
+        y0, y1 = parallel.strip_pixel_rows(rows[rank], 16, cam.height)
+        local[:y0] = 77
+        local[y1:] = 77
+        full = parallel.gather_strips(local, rows, 16, cam.height, dst=0)
+        counts = torch.tensor([mine["keys"].size], dtype=torch.int64)
+        dist.all_reduce(counts)
+        if rank == 0:
+            ref = oracle.render_frame(sc, cam, floats=False)
+            ok = bool((full.numpy() == ref["u8"]).all()) and int(counts[0]) == ref["keys"].size
+            with open(out_path, "w") as f:
+                f.write("ok" if ok else "mismatch")
+        else:
+            assert full is None
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_strip_gather(tmp_path, oracle_lib):
+    out = tmp_path / "result.txt"
+    mp.spawn(_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
+    assert out.read_text() == "ok"
+
+
+def test_strip_rows_cover_grid_exactly():
+    for gy in (1, 7, 50, 68, 135):
+        for world in (1, 2, 3, 4, 8):
+            rows = [parallel.strip_rows(gy, world, r) for r in range(world)]
+            assert rows[0][0] == 0 and rows[-1][1] == gy
+            assert all(rows[i][1] == rows[i + 1][0] for i in range(world - 1))
+            sizes = [b - a for a, b in rows]
+            assert max(sizes) - min(sizes) <= 1
+
+
+def test_balanced_strips_follow_cost():
+    cost = [1.0] * 10 + [9.0] * 10
+    rows = parallel.balanced_strip_rows(cost, 4)
+    assert rows[0][0] == 0 and rows[-1][1] == 20
+    assert all(rows[i][1] == rows[i + 1][0] for i in range(3))
+    sums = [sum(cost[a:b]) for a, b in rows]
+    assert max(sums) <= 1.5 * (sum(cost) / 4)
+    assert all(b > a for a, b in parallel.balanced_strip_rows([0.0] * 8, 8))
+    assert parallel.strip_pixel_rows((60, 68), 16, 1080) == (960, 1080)
