@@ -64,6 +64,8 @@ def load():
             fn.argtypes = args
         lib.fgs_debug_sort_skip_publish.restype = None
         lib.fgs_debug_sort_skip_publish.argtypes = [_i]
+        lib.fgs_debug_preprocess_no_column_cull.restype = None
+        lib.fgs_debug_preprocess_no_column_cull.argtypes = [_i]
         _lib = lib
     return _lib
 

@@ -30,6 +30,7 @@ struct PreCam {
     float cam[3];
     float tan_fovx, tan_fovy, focal_x, focal_y;
     int W, H, block_x, block_y, grid_x, grid_y, row_begin, row_end;
+    int cull_columns;   // 1: bound each row's column range in closed form before the exact tile test
 };
 
 __device__ __forceinline__ unsigned lane_id() { return threadIdx.x & 31u; }

@@ -9,15 +9,21 @@
 //   1. position / opacity / covariance of the block are fetched with 16-byte loads into
 //      shared memory (the [P,3] and [P,6] rows are 12 and 24 bytes, so per-thread loads
 //      could not be vectorised); each thread then projects its own Gaussian.
-//   2. The tile rectangles of the block's Gaussians are laid end to end ("slots") with a
-//      block-wide exclusive scan, and all 256 threads walk the slot space together: a
-//      thread finds the Gaussian a slot belongs to by binary search in the scan and runs
-//      the exact tile test for that one tile. A splat covering thousands of tiles is thus
-//      spread over the whole block instead of serialising a warp, and 1-tile splats fill
-//      all lanes.
-//   3. Pair offsets: per chunk of 1024 slots the per-warp hit counts are scanned by one
-//      warp, which issues ONE atomicAdd on the global pair counter for the whole chunk
-//      (a warp-aggregated prefix); every warp then stores a contiguous run of keys.
+//   2. Work items are (Gaussian, tile row, 32-tile window of that row). The items of the
+//      block's Gaussians are laid end to end with a block-wide exclusive scan and all 256
+//      threads walk the item space together; a thread finds the Gaussian an item belongs to
+//      by binary search in the scan. A splat covering thousands of tiles is thus spread over
+//      the whole block instead of serialising a warp.
+//      For its item a thread first bounds, in closed form and with generous margins, the
+//      column range in which the iso-ellipse can reach the row's band of pixels, and then
+//      runs the exact reference test only on the tiles of that range. For needle-like
+//      splats this skips most of the bounding rectangle; the margins are far wider than the
+//      float error of either computation, so the set of hits is the one the exact test
+//      alone would give (the parity tests compare it pair by pair).
+//   3. Pair offsets: per chunk of 1024 items the hit counts are scanned (warp shuffles, then
+//      one warp over the 32 per-warp totals), which issues ONE atomicAdd on the global pair
+//      counter for the whole chunk (a warp-aggregated prefix); every thread then stores the
+//      keys of its item's hits.
 //   4. Gaussians with at least one hit fetch their 192-byte SH record with 16-byte loads
 //      and write the three feature records.
 //
@@ -204,6 +210,7 @@ preprocess_kernel(int P,
     __shared__ float2 s_xy[PRE_THREADS];
     __shared__ float4 s_con[PRE_THREADS];      // conic.x, conic.y, conic.z, power
     __shared__ int4 s_rect[PRE_THREADS];       // min_x, min_y, width, float_bits(depth)
+    __shared__ float4 s_cull[PRE_THREADS];     // enlarged w, dx_max (< 0: no culling), dy_max, dy where x is largest
     __shared__ int s_prefix[PRE_THREADS + 1];  // exclusive scan of rectangle areas
     __shared__ int s_vis[PRE_THREADS];
     __shared__ int s_wcnt[32];
@@ -266,14 +273,33 @@ preprocess_kernel(int P,
         } while (false);
     }
 
+    // Work items of this Gaussian: one per (tile row, window of 32 tile columns).
     const int rect_w = point_valid ? (maxx - minx) : 0;
-    const int area = point_valid ? rect_w * (maxy - miny) : 0;
+    const int nseg = (rect_w + 31) >> 5;
+    const int items = point_valid ? nseg * (maxy - miny) : 0;
     s_xy[tid] = point_xy;
     s_con[tid] = make_float4(conic.x, conic.y, conic.z, power);
     s_rect[tid] = make_int4(minx, miny, rect_w, __float_as_int(depth));
+    {
+        // Closed-form extent of the (slightly enlarged) iso-ellipse A dx^2 + 2B dx dy + C dy^2 <= w:
+        // |dx| <= sqrt(C w / det), |dy| <= sqrt(A w / det); x is extreme at dy = -+ (B/C) dx_max.
+        // The enlargement grows with the conditioning A*C/det of the quadratic, which is what
+        // amplifies rounding in the exact test near tangency; ill-conditioned or degenerate
+        // conics are not culled at all (dx_max < 0 marks that).
+        const float A = conic.x, B = conic.y, C = conic.z;
+        const float det = A * C - B * B;
+        const float cond = (A * C) / det;
+        float4 cull = make_float4(0.f, -1.f, 0.f, 0.f);
+        if (cam.cull_columns && point_valid && det > 0.f && A > 0.f && C > 0.f && cond < 5000.f) {
+            const float w = 2.0f * power * (1.0f + 1e-3f + 2e-4f * cond);
+            const float dxmax = sqrtf(C * w / det);
+            cull = make_float4(w, dxmax, sqrtf(A * w / det), -(B / C) * dxmax);
+        }
+        s_cull[tid] = cull;
+    }
 
-    // ---- block-wide exclusive scan of the rectangle areas ----
-    int incl = area;
+    // ---- block-wide exclusive scan of the item counts ----
+    int incl = items;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         const int v = __shfl_up_sync(FULL_MASK, incl, o);
@@ -284,44 +310,83 @@ preprocess_kernel(int P,
     int wbase = 0;
 #pragma unroll
     for (int w = 0; w < PRE_WARPS; w++) wbase += (w < warp) ? s_wsum[w] : 0;
-    s_prefix[tid] = wbase + incl - area;
+    s_prefix[tid] = wbase + incl - items;
     if (tid == PRE_THREADS - 1) s_prefix[PRE_THREADS] = wbase + incl;
     __syncthreads();
     const int total = s_prefix[PRE_THREADS];
 
-    // ---- walk the slot space: one (Gaussian, tile) test per thread per step ----
-    const unsigned lt = lanemask_lt();
+    // ---- walk the item space: PRE_K items per thread per chunk ----
+    const float margin = 0.5f;   // pixels, on both the band and the column range
     for (int c0 = 0; c0 < total; c0 += PRE_THREADS * PRE_K) {
         unsigned hit_mask[PRE_K];
-        uint32_t tile_id[PRE_K];
+        int first_tile[PRE_K];    // tile id of bit 0 of hit_mask
         int owner[PRE_K];
+        int excl[PRE_K];          // exclusive prefix of the hit count inside the warp, per k
 #pragma unroll
         for (int k = 0; k < PRE_K; k++) {
-            const int slot = c0 + k * PRE_THREADS + tid;
-            bool hit = false;
-            tile_id[k] = 0; owner[k] = 0;
-            if (slot < total) {
-                int lo = 0, hi = PRE_THREADS;   // largest g with s_prefix[g] <= slot
+            const int item = c0 + k * PRE_THREADS + tid;
+            unsigned mask = 0;
+            first_tile[k] = 0; owner[k] = 0;
+            if (item < total) {
+                int lo = 0, hi = PRE_THREADS;   // largest g with s_prefix[g] <= item
 #pragma unroll
-                for (int s = 0; s < 8; s++) {
+                for (int st = 0; st < 8; st++) {
                     const int mid = (lo + hi) >> 1;
-                    if (s_prefix[mid] <= slot) lo = mid; else hi = mid;
+                    if (s_prefix[mid] <= item) lo = mid; else hi = mid;
                 }
                 const int g = lo;
                 const int4 rc = s_rect[g];
-                const int t = slot - s_prefix[g];
-                const int ry = t / rc.z;
-                const int tx = rc.x + (t - ry * rc.z);
-                const int ty = rc.y + ry;
+                const int t = item - s_prefix[g];
+                const int ns = (rc.z + 31) >> 5;
+                const int row = (ns == 1) ? t : t / ns;
+                const int seg = t - row * ns;
+                const int ty = rc.y + row;
+                int x_begin = rc.x + (seg << 5);
+                int x_end = min(rc.x + rc.z, x_begin + 32);
                 const float2 c = s_xy[g];
                 const float4 q = s_con[g];
-                hit = tile_hit(tx, ty, cam.block_x, cam.block_y, c.x, c.y, q.x, q.y, q.z, q.w);
-                tile_id[k] = (uint32_t)(ty * cam.grid_x + tx);
+                const float4 cu = s_cull[g];
+                if (cu.y >= 0.f) {
+                    // band of pixel rows of this tile row, relative to the centre, clipped to the ellipse's extent
+                    const float d_lo = fmaxf((float)(ty * cam.block_y) - c.y - margin, -cu.z);
+                    const float d_hi = fminf((float)(ty * cam.block_y + cam.block_y - 1) - c.y + margin, cu.z);
+                    if (d_lo > d_hi) {
+                        x_end = x_begin;
+                    } else {
+                        const float det = q.x * q.z - q.y * q.y;
+                        const float s_lo = sqrtf(fmaxf(0.f, q.x * cu.x - det * d_lo * d_lo));
+                        const float s_hi = sqrtf(fmaxf(0.f, q.x * cu.x - det * d_hi * d_hi));
+                        const float inv_a = 1.0f / q.x;
+                        const float xh = (cu.w >= d_lo && cu.w <= d_hi) ? cu.y
+                                         : fmaxf((-q.y * d_lo + s_lo) * inv_a, (-q.y * d_hi + s_hi) * inv_a);
+                        const float xl = (-cu.w >= d_lo && -cu.w <= d_hi) ? -cu.y
+                                         : fminf((-q.y * d_lo - s_lo) * inv_a, (-q.y * d_hi - s_hi) * inv_a);
+                        // tiles whose pixel box [tx*bx, tx*bx + bx - 1] meets [c.x + xl - margin, c.x + xh + margin]
+                        const float inv_bx = 1.0f / (float)cam.block_x;
+                        const float fl = ceilf((c.x + xl - margin - (float)(cam.block_x - 1)) * inv_bx);
+                        const float fr = floorf((c.x + xh + margin) * inv_bx);
+                        x_begin = max(x_begin, (int)fmaxf(fl, -1.0e6f));
+                        x_end = min(x_end, (int)fminf(fr, 1.0e6f) + 1);
+                    }
+                }
+                first_tile[k] = ty * cam.grid_x + rc.x + (seg << 5);
                 owner[k] = g;
-                if (hit) s_vis[g] = 1;
+                const int bit0 = rc.x + (seg << 5);
+                for (int tx = x_begin; tx < x_end; tx++)
+                    if (tile_hit(tx, ty, cam.block_x, cam.block_y, c.x, c.y, q.x, q.y, q.z, q.w))
+                        mask |= 1u << (tx - bit0);
+                if (mask) s_vis[g] = 1;
             }
-            hit_mask[k] = __ballot_sync(FULL_MASK, hit);
-            if (lane == 0) s_wcnt[k * PRE_WARPS + warp] = __popc(hit_mask[k]);
+            hit_mask[k] = mask;
+            const int cnt = __popc(mask);
+            int inc = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(FULL_MASK, inc, o);
+                if (lane >= o) inc += v;
+            }
+            excl[k] = inc - cnt;
+            if (lane == 31) s_wcnt[k * PRE_WARPS + warp] = inc;
         }
         __syncthreads();
         if (warp == 0) {
@@ -341,14 +406,22 @@ preprocess_kernel(int P,
         __syncthreads();
 #pragma unroll
         for (int k = 0; k < PRE_K; k++) {
-            if (hit_mask[k] & (1u << lane)) {
-                const long long o = (long long)s_woff[k * PRE_WARPS + warp] + __popc(hit_mask[k] & lt);
-                if (o >= 0 && o < capacity) {
-                    const int g = owner[k];
-                    keys[o] = ((uint64_t)tile_id[k] << 32) | (uint32_t)s_rect[g].w;
-                    values[o] = (uint32_t)(base + g);
-                } else {
-                    atomicOr(status, FGS_ERR_PAIR_OVERFLOW);
+            unsigned m = hit_mask[k];
+            if (m) {
+                long long o = (long long)s_woff[k * PRE_WARPS + warp] + excl[k];
+                const int g = owner[k];
+                const uint32_t depth_bits = (uint32_t)s_rect[g].w;
+                const uint32_t idx = (uint32_t)(base + g);
+                while (m) {
+                    const int bit = __ffs(m) - 1;
+                    m &= m - 1;
+                    if (o >= 0 && o < capacity) {
+                        keys[o] = ((uint64_t)(uint32_t)(first_tile[k] + bit) << 32) | depth_bits;
+                        values[o] = idx;
+                    } else {
+                        atomicOr(status, FGS_ERR_PAIR_OVERFLOW);
+                    }
+                    o++;
                 }
             }
         }
@@ -380,11 +453,18 @@ preprocess_kernel(int P,
 
 } // namespace
 
+int g_debug_no_column_cull = 0;
+
 // Host matrices in the reference's operation order; see fgs_view_proj_matrices().
 void host_view_proj(int width, int height, const float* pos, const float* rot, float fx, float fy,
                     float zFar, float zNear, float* view, float* proj);
 
 } // namespace fgs
+
+// Test hook: non-zero makes the next preprocess calls run the exact tile test on every tile of a
+// splat's bounding rectangle, as the reference does, instead of first narrowing each row's column
+// range. Both settings must produce the same pair set; the tests compare them.
+extern "C" void fgs_debug_preprocess_no_column_cull(int on) { fgs::g_debug_no_column_cull = on; }
 
 extern "C" int fgs_preprocess_strip(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
                                     int width, int height, int block_x, int block_y,
@@ -416,6 +496,7 @@ extern "C" int fgs_preprocess_strip(int P, const float* positions, const float* 
     cam.grid_y = (height + block_y - 1) / block_y;
     cam.row_begin = tile_row_begin < 0 ? 0 : tile_row_begin;
     cam.row_end = (tile_row_end < 0 || tile_row_end > cam.grid_y) ? cam.grid_y : tile_row_end;
+    cam.cull_columns = g_debug_no_column_cull ? 0 : 1;
 
     const bool vec = aligned16(positions) && aligned16(shs) && aligned16(opacities) && aligned16(cov3ds);
     const int blocks = (P + PRE_THREADS - 1) / PRE_THREADS;

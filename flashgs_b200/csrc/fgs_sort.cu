@@ -7,7 +7,7 @@
 // Structure:
 //   * one histogram kernel reads the keys once and counts every 8-bit digit of the live
 //     bits (ceil(end_bit / 8) digits; bits at or above end_bit are never looked at);
-//   * one "onesweep" kernel per digit: a block takes the next partition of 4096 pairs from a
+//   * one "onesweep" kernel per digit: a block (512 threads) takes the next partition of 4096 pairs from a
 //     ticket counter, ranks its keys by digit (warp match + per-warp counters, which keeps the
 //     sort stable), publishes its per-digit counts and obtains the counts of all earlier
 //     partitions by decoupled look-back, then moves keys and values through shared memory so
@@ -26,21 +26,24 @@
 namespace fgs {
 namespace {
 
-constexpr int SORT_THREADS = 256;
+constexpr int SORT_THREADS = 512;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
-constexpr int SORT_ITEMS = 16;                          // pairs per thread
+constexpr int SORT_ITEMS = 8;                           // pairs per thread
 constexpr int SORT_PART = SORT_THREADS * SORT_ITEMS;    // pairs per partition
 constexpr int RADIX_BITS = 8;
 constexpr int RADIX = 1 << RADIX_BITS;
 constexpr int MAX_PASSES = 8;
-static_assert(RADIX == SORT_THREADS, "one thread owns one digit value in the look-back");
+constexpr int HIST_THREADS = 256;
+static_assert(RADIX <= SORT_THREADS, "thread d < RADIX owns digit value d in the scans and the look-back");
 
 constexpr uint32_t FLAG_AGGREGATE = 1u << 30;           // this partition's count only
 constexpr uint32_t FLAG_INCLUSIVE = 2u << 30;           // count of this and all earlier partitions
 constexpr uint32_t FLAG_MASK = 3u << 30;
 constexpr uint32_t VALUE_MASK = ~FLAG_MASK;
 constexpr int LOOKBACK_MAX_POLLS = 1 << 20;             // x (100 ns sleep + one L2 read): gives up after about a second
-constexpr int SORT_SMEM_BYTES = SORT_PART * 12;         // staged keys + values of one partition
+constexpr int STAGE_BYTES = SORT_PART * 12;             // keys + values of one partition
+constexpr int SORT_SMEM_BYTES = 2 * STAGE_BYTES;        // two stages per block
+constexpr int MBAR_MAX_POLLS = 1 << 20;                 // tries of at most ~1 us each: a bulk copy gets about a second
 
 __device__ __forceinline__ uint32_t ld_relaxed(const uint32_t* p)
 {
@@ -75,168 +78,271 @@ inline SortLayout make_layout(int64_t n)
 }
 
 // ---- digit histograms of all passes in one read of the keys ----
-__global__ void __launch_bounds__(SORT_THREADS)
+__global__ void __launch_bounds__(HIST_THREADS)
 histogram_kernel(const uint64_t* __restrict__ keys, int n, int passes, int end_bit, uint32_t* __restrict__ hist)
 {
     __shared__ uint32_t s_hist[MAX_PASSES * RADIX];
-    for (int i = threadIdx.x; i < passes * RADIX; i += SORT_THREADS) s_hist[i] = 0;
+    for (int i = threadIdx.x; i < passes * RADIX; i += HIST_THREADS) s_hist[i] = 0;
     __syncthreads();
     const uint64_t live = end_bit >= 64 ? ~0ull : ((1ull << end_bit) - 1ull);
-    for (int64_t i = (int64_t)blockIdx.x * SORT_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * SORT_THREADS) {
+    for (int64_t i = (int64_t)blockIdx.x * HIST_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * HIST_THREADS) {
         const uint64_t k = __ldg(keys + i) & live;
         for (int p = 0; p < passes; p++)
             atomicAdd(&s_hist[p * RADIX + (uint32_t)((k >> (p * RADIX_BITS)) & (RADIX - 1))], 1u);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < passes * RADIX; i += SORT_THREADS) {
+    for (int i = threadIdx.x; i < passes * RADIX; i += HIST_THREADS) {
         const uint32_t c = s_hist[i];
         if (c) atomicAdd(hist + i, c);
     }
 }
 
 // ---- one onesweep pass ----
-__global__ void __launch_bounds__(SORT_THREADS)
+// ---- asynchronous bulk copies (TMA, 1-D, no multicast) and their mbarrier ----
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait for a phase of the barrier; false if the poll budget ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+{
+    const uint32_t addr = smem_u32(bar);
+    for (int i = 0; i < MBAR_MAX_POLLS; i++) {
+        uint32_t ok;
+        // the last operand caps how long one try may suspend the thread (nanoseconds)
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 1000;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// ---- one onesweep pass ----
+// Persistent blocks (two per SM). A block owns two shared-memory stages of one partition each
+// (4096 keys + 4096 values): while it ranks and scatters the partition in one stage, the bulk
+// copy of its next partition is already filling the other, so the HBM reads of a block never
+// stop. The stage that was just consumed into registers doubles as the buffer in which the
+// partition is reordered before it is written out.
+__global__ void __launch_bounds__(SORT_THREADS, 2)
 onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                 uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
-                int n, int shift, uint32_t digit_mask,
+                int n, int num_parts, int shift, uint32_t digit_mask, int use_bulk,
                 uint32_t* __restrict__ ticket, const uint32_t* __restrict__ hist,
                 uint32_t* __restrict__ status_words, int* __restrict__ dev_status, int skip_publish_part)
 {
-    extern __shared__ __align__(16) unsigned char s_dyn[];                 // SORT_SMEM_BYTES
-    uint64_t* s_keys = reinterpret_cast<uint64_t*>(s_dyn);                 // [SORT_PART]
-    uint32_t* s_vals = reinterpret_cast<uint32_t*>(s_dyn + SORT_PART * 8); // [SORT_PART]
-    __shared__ uint32_t s_whist[SORT_WARPS][RADIX];   // per-warp digit counts, then exclusive warp offsets
-    __shared__ uint32_t s_local_start[RADIX];          // start of each digit's run inside the partition
-    __shared__ int64_t s_global_delta[RADIX];          // global index of a digit's run minus its local start
-    __shared__ uint32_t s_scan[SORT_WARPS];
-    __shared__ uint32_t s_part;
+    extern __shared__ __align__(128) unsigned char s_dyn[];   // 2 stages x (keys 8*PART | values 4*PART)
+    __shared__ __align__(8) uint64_t s_bar[2];
+    __shared__ uint16_t s_whist[SORT_WARPS][RADIX];    // per-warp digit counts, then exclusive warp offsets
+    __shared__ uint32_t s_local_start[RADIX];           // start of each digit's run inside the partition
+    __shared__ int64_t s_global_delta[RADIX];           // global index of a digit's run minus its local start
+    __shared__ uint32_t s_digit_base[RADIX];            // exclusive scan of the global histogram
+    __shared__ uint32_t s_scan[RADIX / 32];
+    __shared__ uint32_t s_tickets[4];                   // partition of iteration i lives in s_tickets[i & 3]
     __shared__ int s_abort;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) { s_part = atomicAdd(ticket, 1u); s_abort = 0; }
-#pragma unroll
-    for (int w = 0; w < SORT_WARPS; w++) s_whist[w][tid] = 0;
-    __syncthreads();
-    const uint32_t part = s_part;
-    const int64_t part_base = (int64_t)part * SORT_PART;
-    const int valid = (int)min((int64_t)SORT_PART, (int64_t)n - part_base);
-    if (valid <= 0) return;   // tickets beyond the last partition (never happens with an exact grid)
-
-    // keys in warp-striped order: item i of lane l of warp w sits at w*512 + i*32 + l
-    uint64_t key[SORT_ITEMS];
-    const int wbase = warp * (32 * SORT_ITEMS);
-#pragma unroll
-    for (int i = 0; i < SORT_ITEMS; i++) {
-        const int local = wbase + i * 32 + lane;
-        key[i] = local < valid ? __ldg(keys_in + part_base + local) : ~0ull;
-    }
-
-    // rank within the warp, item by item, so equal digits keep their input order
-    uint32_t rank[SORT_ITEMS];
     const unsigned lt = lanemask_lt();
-#pragma unroll
-    for (int i = 0; i < SORT_ITEMS; i++) {
-        const uint32_t d = (uint32_t)(key[i] >> shift) & digit_mask;
-        const unsigned peers = __match_any_sync(FULL_MASK, d);
-        const int leader = __ffs(peers) - 1;
-        uint32_t pre = 0;
-        if (lane == leader) {
-            pre = s_whist[warp][d];
-            s_whist[warp][d] = pre + __popc(peers);
+    auto stage_keys = [&](int st) { return reinterpret_cast<uint64_t*>(s_dyn + (size_t)st * STAGE_BYTES); };
+    auto stage_vals = [&](int st) { return reinterpret_cast<uint32_t*>(s_dyn + (size_t)st * STAGE_BYTES + SORT_PART * 8); };
+    // Thread 0: start the bulk copy of a full partition into a stage (the ragged last partition and
+    // unaligned inputs are copied with plain loads by the whole block when the stage is consumed).
+    uint32_t pending = 0;   // thread 0: bit st = a bulk copy into stage st has been started and not yet waited for
+    auto prefetch = [&](int st, uint32_t part) {
+        if (use_bulk && part < (uint32_t)num_parts && (int64_t)(part + 1) * SORT_PART <= (int64_t)n) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(&s_bar[st], SORT_PART * 12);
+            bulk_load(stage_keys(st), keys_in + (size_t)part * SORT_PART, SORT_PART * 8, &s_bar[st]);
+            bulk_load(stage_vals(st), vals_in + (size_t)part * SORT_PART, SORT_PART * 4, &s_bar[st]);
+            pending |= 1u << st;
         }
-        pre = __shfl_sync(FULL_MASK, pre, leader);
-        rank[i] = pre + __popc(peers & lt);
+    };
+
+    if (tid == 0) {
+        mbar_init(&s_bar[0], 1);
+        mbar_init(&s_bar[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_abort = 0;
+        const uint32_t first = atomicAdd(ticket, 1u);
+        s_tickets[0] = first;
+        prefetch(0, first);
+        s_tickets[1] = atomicAdd(ticket, 1u);
+    }
+    // exclusive scan of the global histogram: where each digit's output region starts
+    if (tid < RADIX) {
+        const uint32_t g = hist[tid];
+        uint32_t inc = g;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t a = __shfl_up_sync(FULL_MASK, inc, o);
+            if (lane >= o) inc += a;
+        }
+        if (lane == 31) s_scan[warp] = inc;
         __syncwarp();
+        s_digit_base[tid] = inc - g;    // completed below
+    }
+    __syncthreads();
+    if (tid < RADIX) {
+        uint32_t off = 0;
+#pragma unroll
+        for (int w = 0; w < RADIX / 32; w++) off += (w < warp) ? s_scan[w] : 0;
+        s_digit_base[tid] += off;
     }
     __syncthreads();
 
-    // thread d: per-warp exclusive offsets and the block count of digit d
-    uint32_t count = 0;
-#pragma unroll
-    for (int w = 0; w < SORT_WARPS; w++) {
-        const uint32_t c = s_whist[w][tid];
-        s_whist[w][tid] = count;
-        count += c;
-    }
-    uint32_t* my_status = status_words + (size_t)part * RADIX + tid;
-    const bool publish = (int)part != skip_publish_part;
-    if (publish) st_relaxed(my_status, (part == 0 ? FLAG_INCLUSIVE : FLAG_AGGREGATE) | count);
+    uint32_t phase_bits = 0;   // bit st = parity to wait for on stage st
+    for (int it = 0;; it++) {
+        const int st = it & 1;
+        const uint32_t part = s_tickets[it & 3];
+        if (part >= (uint32_t)num_parts) break;
+        const int64_t part_base = (int64_t)part * SORT_PART;
+        const int valid = (int)min((int64_t)SORT_PART, (int64_t)n - part_base);
+        const bool bulk = use_bulk && valid == SORT_PART;
+        // Thread 0: start the copy of the next partition (its ticket was taken one iteration ago) into
+        // the other stage, and request the ticket after that; the ticket is only stored at the end of
+        // the iteration, so its round trip to the L2 never stalls the block.
+        uint32_t ticket_after_next = 0;
+        if (tid == 0) {
+            prefetch(st ^ 1, s_tickets[(it + 1) & 3]);
+            ticket_after_next = atomicAdd(ticket, 1u);
+        }
+        for (int i = tid; i < SORT_WARPS * RADIX / 2; i += SORT_THREADS) reinterpret_cast<uint32_t*>(&s_whist[0][0])[i] = 0;
 
-    // exclusive scans over the 256 digits: block counts -> local starts, global histogram -> digit bases
-    const uint32_t gcount = hist[tid];
-    uint32_t inc_l = count, inc_g = gcount;
+        uint64_t* sk = stage_keys(st);
+        uint32_t* sv = stage_vals(st);
+        uint64_t key[SORT_ITEMS];
+        uint32_t val[SORT_ITEMS];
+        const int wbase = warp * (32 * SORT_ITEMS);   // warp-striped: item i of lane l sits at wbase + i*32 + l
+        if (bulk) {
+            if (!mbar_wait(&s_bar[st], (phase_bits >> st) & 1u)) { atomicOr(dev_status, FGS_ERR_LOOKBACK_TIMEOUT); s_abort = 1; }
+            else pending &= ~(1u << st);
+            phase_bits ^= 1u << st;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t a = __shfl_up_sync(FULL_MASK, inc_l, o);
-        const uint32_t b = __shfl_up_sync(FULL_MASK, inc_g, o);
-        if (lane >= o) { inc_l += a; inc_g += b; }
-    }
-    if (lane == 31) { s_scan[warp] = inc_l; }
-    __syncthreads();
-    uint32_t off_l = 0;
+            for (int i = 0; i < SORT_ITEMS; i++) { key[i] = sk[wbase + i * 32 + lane]; val[i] = sv[wbase + i * 32 + lane]; }
+        } else {
 #pragma unroll
-    for (int w = 0; w < SORT_WARPS; w++) off_l += (w < warp) ? s_scan[w] : 0;
-    __syncthreads();
-    if (lane == 31) { s_scan[warp] = inc_g; }
-    __syncthreads();
-    uint32_t off_g = 0;
-#pragma unroll
-    for (int w = 0; w < SORT_WARPS; w++) off_g += (w < warp) ? s_scan[w] : 0;
-    const uint32_t local_start = off_l + inc_l - count;
-    const uint32_t digit_base = off_g + inc_g - gcount;
-    s_local_start[tid] = local_start;
-
-    // decoupled look-back over earlier partitions for digit `tid`
-    uint32_t earlier = 0;
-    if (part > 0) {
-        int64_t p = (int64_t)part - 1;
-        int polls = 0;
-        bool failed = false;
-        while (true) {
-            const uint32_t s = ld_relaxed(status_words + (size_t)p * RADIX + tid);
-            const uint32_t f = s & FLAG_MASK;
-            if (f == 0) {
-                if (++polls > LOOKBACK_MAX_POLLS) { failed = true; break; }
-                __nanosleep(100);
-                continue;
+            for (int i = 0; i < SORT_ITEMS; i++) {
+                const int local = wbase + i * 32 + lane;
+                key[i] = local < valid ? __ldg(keys_in + part_base + local) : ~0ull;
+                val[i] = local < valid ? __ldg(vals_in + part_base + local) : 0u;
             }
-            earlier += s & VALUE_MASK;
-            if (f == FLAG_INCLUSIVE) break;
-            p--;   // partition 0 always publishes FLAG_INCLUSIVE, so p never goes below 0
         }
-        if (failed) { atomicOr(dev_status, FGS_ERR_LOOKBACK_TIMEOUT); s_abort = 1; }
-        if (publish) st_relaxed(my_status, FLAG_INCLUSIVE | ((earlier + count) & VALUE_MASK));
-    }
-    s_global_delta[tid] = (int64_t)digit_base + (int64_t)earlier - (int64_t)local_start;
-    __syncthreads();
-    if (s_abort) return;
+        __syncthreads();   // s_whist zeroed, every thread holds its items
+        if (s_abort) break;
 
-    // place keys (and the matching values) at their partition-local sorted position
+        // rank within the warp, item by item, so equal digits keep their input order
+        uint32_t rank[SORT_ITEMS];
 #pragma unroll
-    for (int i = 0; i < SORT_ITEMS; i++) {
-        const uint32_t d = (uint32_t)(key[i] >> shift) & digit_mask;
-        const uint32_t pos = s_local_start[d] + s_whist[warp][d] + rank[i];
-        rank[i] = pos;
-        s_keys[pos] = key[i];
-    }
-#pragma unroll
-    for (int i = 0; i < SORT_ITEMS; i++) {
-        const int local = wbase + i * 32 + lane;
-        if (local < valid) s_vals[rank[i]] = __ldg(vals_in + part_base + local);
-    }
-    __syncthreads();
-
-    // runs of equal digits are contiguous in shared memory and in the destination
-#pragma unroll
-    for (int i = 0; i < SORT_ITEMS; i++) {
-        const int j = i * SORT_THREADS + tid;
-        if (j < valid) {
-            const uint64_t k = s_keys[j];
-            const uint32_t d = (uint32_t)(k >> shift) & digit_mask;
-            const int64_t dst = s_global_delta[d] + j;
-            keys_out[dst] = k;
-            vals_out[dst] = s_vals[j];
+        for (int i = 0; i < SORT_ITEMS; i++) {
+            const uint32_t d = (uint32_t)(key[i] >> shift) & digit_mask;
+            const unsigned peers = __match_any_sync(FULL_MASK, d);
+            const int leader = __ffs(peers) - 1;
+            uint32_t pre = 0;
+            if (lane == leader) {
+                pre = s_whist[warp][d];
+                s_whist[warp][d] = (uint16_t)(pre + __popc(peers));
+            }
+            pre = __shfl_sync(FULL_MASK, pre, leader);
+            rank[i] = pre + __popc(peers & lt);
+            __syncwarp();
         }
+        __syncthreads();
+
+        // threads 0..RADIX-1: thread d owns digit value d
+        uint32_t count = 0, inc_l = 0;
+        uint32_t* my_status = status_words + (size_t)part * RADIX + tid;
+        const bool publish = (int)part != skip_publish_part;
+        if (tid < RADIX) {
+#pragma unroll
+            for (int w = 0; w < SORT_WARPS; w++) {
+                const uint32_t c = s_whist[w][tid];
+                s_whist[w][tid] = (uint16_t)count;   // exclusive offset of warp w inside the digit's run
+                count += c;
+            }
+            if (publish) st_relaxed(my_status, (part == 0 ? FLAG_INCLUSIVE : FLAG_AGGREGATE) | count);
+            inc_l = count;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t a = __shfl_up_sync(FULL_MASK, inc_l, o);
+                if (lane >= o) inc_l += a;
+            }
+            if (lane == 31) s_scan[warp] = inc_l;
+        }
+        __syncthreads();
+        if (tid < RADIX) {
+            uint32_t off_l = 0;
+#pragma unroll
+            for (int w = 0; w < RADIX / 32; w++) off_l += (w < warp) ? s_scan[w] : 0;
+            const uint32_t local_start = off_l + inc_l - count;
+            s_local_start[tid] = local_start;
+
+            // decoupled look-back over earlier partitions for digit `tid`
+            uint32_t earlier = 0;
+            if (part > 0) {
+                int64_t p = (int64_t)part - 1;
+                int polls = 0;
+                bool failed = false;
+                while (true) {
+                    const uint32_t sw = ld_relaxed(status_words + (size_t)p * RADIX + tid);
+                    const uint32_t f = sw & FLAG_MASK;
+                    if (f == 0) {
+                        if (++polls > LOOKBACK_MAX_POLLS) { failed = true; break; }
+                        __nanosleep(100);
+                        continue;
+                    }
+                    earlier += sw & VALUE_MASK;
+                    if (f == FLAG_INCLUSIVE) break;
+                    p--;   // partition 0 always publishes FLAG_INCLUSIVE, so p never goes below 0
+                }
+                if (failed) { atomicOr(dev_status, FGS_ERR_LOOKBACK_TIMEOUT); s_abort = 1; }
+                if (publish) st_relaxed(my_status, FLAG_INCLUSIVE | ((earlier + count) & VALUE_MASK));
+            }
+            s_global_delta[tid] = (int64_t)s_digit_base[tid] + (int64_t)earlier - (int64_t)local_start;
+        }
+        __syncthreads();
+        if (s_abort) break;
+
+        // place keys and values at their partition-local sorted position (the stage is free: its
+        // contents live in registers)
+#pragma unroll
+        for (int i = 0; i < SORT_ITEMS; i++) {
+            const uint32_t d = (uint32_t)(key[i] >> shift) & digit_mask;
+            const uint32_t pos = s_local_start[d] + s_whist[warp][d] + rank[i];
+            sk[pos] = key[i];
+            sv[pos] = val[i];
+        }
+        __syncthreads();
+
+        // runs of equal digits are contiguous in shared memory and in the destination
+#pragma unroll
+        for (int i = 0; i < SORT_ITEMS; i++) {
+            const int j = i * SORT_THREADS + tid;
+            if (j < valid) {
+                const uint64_t k = sk[j];
+                const uint32_t d = (uint32_t)(k >> shift) & digit_mask;
+                const int64_t dst = s_global_delta[d] + j;
+                keys_out[dst] = k;
+                vals_out[dst] = sv[j];
+            }
+        }
+        if (tid == 0) s_tickets[(it + 2) & 3] = ticket_after_next;
+        __syncthreads();   // the stage may now be refilled by the copy started in the next iteration
+    }
+
+    // Leaving early (a wait gave up): a copy into the other stage may still be in flight; wait for it
+    // (bounded) so that nothing writes into shared memory after the block is gone.
+    if (tid == 0) {
+        for (int st = 0; st < 2; st++)
+            if (pending & (1u << st)) mbar_wait(&s_bar[st], (phase_bits >> st) & 1u);
     }
 }
 
@@ -301,9 +407,12 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     uint32_t* alt_vals = reinterpret_cast<uint32_t*>(base + L.alt_vals_off);
 
     static bool smem_opt_in[64];
+    static int sm_count[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FGS_ERR_CUDA;
     if (!smem_opt_in[dev]) {
+        if (cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count[dev] <= 0)
+            return FGS_ERR_CUDA;
         if (cudaFuncSetAttribute(onesweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SORT_SMEM_BYTES) != cudaSuccess)
             return FGS_ERR_CUDA;
         smem_opt_in[dev] = true;
@@ -315,19 +424,21 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     if (passes_out) *passes_out = passes;
     if (events) cudaEventRecord(events[0], st);
     int hist_blocks = L.parts < 148 * 8 ? L.parts : 148 * 8;
-    histogram_kernel<<<hist_blocks, SORT_THREADS, 0, st>>>(keys_unsorted, n, passes, end_bit, hist);
+    histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, passes, end_bit, hist);
     if (events) cudaEventRecord(events[1], st);
 
     const uint64_t* src_k = keys_unsorted;
     const uint32_t* src_v = values_unsorted;
+    const int grid_blocks = L.parts < 2 * sm_count[dev] ? L.parts : 2 * sm_count[dev];   // persistent: two blocks per SM
     for (int p = 0; p < passes; p++) {
         const bool to_out = ((passes - 1 - p) & 1) == 0;
         uint64_t* dst_k = to_out ? keys_sorted : alt_keys;
         uint32_t* dst_v = to_out ? values_sorted : alt_vals;
         const int shift = p * RADIX_BITS;
         const int bits = (end_bit - shift) < RADIX_BITS ? (end_bit - shift) : RADIX_BITS;
-        onesweep_kernel<<<L.parts, SORT_THREADS, SORT_SMEM_BYTES, st>>>(src_k, src_v, dst_k, dst_v, n, shift, (1u << bits) - 1u,
-                                                         tickets + p, hist + p * RADIX,
+        const int use_bulk = aligned16(src_k) && aligned16(src_v);
+        onesweep_kernel<<<grid_blocks, SORT_THREADS, SORT_SMEM_BYTES, st>>>(src_k, src_v, dst_k, dst_v, n, L.parts, shift,
+                                                         (1u << bits) - 1u, use_bulk, tickets + p, hist + p * RADIX,
                                                          status_words + (size_t)p * L.parts * RADIX,
                                                          dev_status, g_debug_skip_publish_part);
         src_k = dst_k;

@@ -156,6 +156,38 @@ def test_needle_splats_match_oracle(ops, oracle_lib):
     _check_against_oracle(f, o, cam, (16, 16))
 
 
+@pytest.mark.parametrize("name,n,size", [("C1", 100000, (800, 800)), ("C4", 300000, (1920, 1080)), ("C3", 200000, (1280, 720))])
+def test_column_culling_changes_nothing(ops, name, n, size):
+    """Narrowing each row's column range before the exact tile test must not change the pair set."""
+    from flashgs_b200 import _lib
+    L = _lib.load()
+    w = scenes.WORKLOADS[name]
+    sc = scenes.make_scene(n, w.clusters, w.log_scale, seed=11)
+    cam = scenes.look_at_camera(size[0], size[1], w.radius, w.hfov_deg, w.azimuth_deg, w.elevation_deg)
+    a = Frame(ops, sc, cam, floats=False)
+    L.fgs_debug_preprocess_no_column_cull(1)
+    try:
+        b = Frame(ops, sc, cam, floats=False)
+    finally:
+        L.fgs_debug_preprocess_no_column_cull(0)
+    assert a.R == b.R
+    ka, va = canonical_pairs(a.np("ku", a.R), a.np("vu", a.R))
+    kb, vb = canonical_pairs(b.np("ku", b.R), b.np("vu", b.R))
+    assert (ka == kb).all() and (va == vb).all()
+    # extreme needles and huge splats: axis ratios up to e^8, some covering the whole image
+    sc2 = scenes.make_scene(4000, 8, ((-0.5, 1.5), (-6.0, 1.0), (-6.0, 1.0)), seed=12)
+    a = Frame(ops, sc2, cam, floats=False, capacity=1 << 24)
+    L.fgs_debug_preprocess_no_column_cull(1)
+    try:
+        b = Frame(ops, sc2, cam, floats=False, capacity=1 << 24)
+    finally:
+        L.fgs_debug_preprocess_no_column_cull(0)
+    assert a.R == b.R and a.R > 100000
+    ka, va = canonical_pairs(a.np("ku", a.R), a.np("vu", a.R))
+    kb, vb = canonical_pairs(b.np("ku", b.R), b.np("vu", b.R))
+    assert (ka == kb).all() and (va == vb).all()
+
+
 def test_partial_tiles_and_no_write_outside_image(ops, oracle_lib):
     # 203 x 117: ragged in both directions, byte-store path; the bytes after the image must stay untouched
     cam = scenes.look_at_camera(203, 117, 15.0, 60.0, 34.0, 17.0)
