@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libflashgs_b200.so")
+LIB_PATH = os.environ.get("FLASHGS_B200_LIB") or os.path.join(HERE, "libflashgs_b200.so")
 
 OK, ERR_BAD_ARG, ERR_CUDA, ERR_PAIR_OVERFLOW, ERR_LOOKBACK_TIMEOUT, ERR_TEMP_TOO_SMALL = 0, 1, 2, 4, 8, 16
 

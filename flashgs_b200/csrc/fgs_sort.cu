@@ -26,9 +26,27 @@
 namespace fgs {
 namespace {
 
-constexpr int SORT_THREADS = 512;
+#ifndef FGS_SORT_THREADS
+#define FGS_SORT_THREADS 256
+#endif
+#ifndef FGS_SORT_ITEMS
+#define FGS_SORT_ITEMS 16
+#endif
+#ifndef FGS_LOOKBACK_SLEEP_NS
+#define FGS_LOOKBACK_SLEEP_NS 200
+#endif
+#ifndef FGS_SORT_STAGES
+#define FGS_SORT_STAGES 2      // 2: bulk-copy prefetch of the next partition; 1: plain loads, smaller footprint
+#endif
+#ifndef FGS_SORT_BLOCKS_PER_SM
+#define FGS_SORT_BLOCKS_PER_SM 2
+#endif
+#ifndef FGS_LOOKBACK_WINDOW
+#define FGS_LOOKBACK_WINDOW 8
+#endif
+constexpr int SORT_THREADS = FGS_SORT_THREADS;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
-constexpr int SORT_ITEMS = 8;                           // pairs per thread
+constexpr int SORT_ITEMS = FGS_SORT_ITEMS;               // pairs per thread
 constexpr int SORT_PART = SORT_THREADS * SORT_ITEMS;    // pairs per partition
 constexpr int RADIX_BITS = 8;
 constexpr int RADIX = 1 << RADIX_BITS;
@@ -40,9 +58,13 @@ constexpr uint32_t FLAG_AGGREGATE = 1u << 30;           // this partition's coun
 constexpr uint32_t FLAG_INCLUSIVE = 2u << 30;           // count of this and all earlier partitions
 constexpr uint32_t FLAG_MASK = 3u << 30;
 constexpr uint32_t VALUE_MASK = ~FLAG_MASK;
-constexpr int LOOKBACK_MAX_POLLS = 1 << 20;             // x (100 ns sleep + one L2 read): gives up after about a second
+constexpr int LOOKBACK_MAX_POLLS = 1 << 20;             // x (sleep + one L2 read): gives up after about a second
+constexpr int LOOKBACK_WINDOW = FGS_LOOKBACK_WINDOW;                      // earlier partitions inspected per round trip
 constexpr int STAGE_BYTES = SORT_PART * 12;             // keys + values of one partition
-constexpr int SORT_SMEM_BYTES = 2 * STAGE_BYTES;        // two stages per block
+constexpr int LOOKBACK_SLEEP_NS = FGS_LOOKBACK_SLEEP_NS;
+constexpr int SORT_STAGES = FGS_SORT_STAGES;
+constexpr int SORT_BLOCKS_PER_SM = FGS_SORT_BLOCKS_PER_SM;
+constexpr int SORT_SMEM_BYTES = SORT_STAGES * STAGE_BYTES;
 constexpr int MBAR_MAX_POLLS = 1 << 20;                 // tries of at most ~1 us each: a bulk copy gets about a second
 
 __device__ __forceinline__ uint32_t ld_relaxed(const uint32_t* p)
@@ -98,6 +120,20 @@ histogram_kernel(const uint64_t* __restrict__ keys, int n, int passes, int end_b
 }
 
 // ---- one onesweep pass ----
+// Lanes of the warp that hold the same 8-bit digit: one vote per bit (the match.any instruction gives the
+// same mask but measured several hundred cycles per call here; eight votes are an order of magnitude cheaper).
+__device__ __forceinline__ unsigned match_digit(uint32_t d)
+{
+    unsigned peers = FULL_MASK;
+#pragma unroll
+    for (int b = 0; b < RADIX_BITS; b++) {
+        const bool bit = (d >> b) & 1u;
+        const unsigned vote = __ballot_sync(FULL_MASK, bit);
+        peers &= bit ? vote : ~vote;
+    }
+    return peers;
+}
+
 // ---- asynchronous bulk copies (TMA, 1-D, no multicast) and their mbarrier ----
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
@@ -127,13 +163,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
     return false;
 }
 
+// Optional per-phase cycle accounting of the pass kernel (compile with -DFGS_SORT_TIMING): thread 0 of
+// every block adds the SM cycles it spent in each phase to g_phase_cycles; read with fgs_debug_sort_phase_cycles.
+#ifdef FGS_SORT_TIMING
+__device__ unsigned long long g_phase_cycles[8];
+#define FGS_T(i) do { if (tid == 0) { const long long now_ = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
+#else
+#define FGS_T(i) do { } while (0)
+#endif
+
 // ---- one onesweep pass ----
 // Persistent blocks (two per SM). A block owns two shared-memory stages of one partition each
 // (4096 keys + 4096 values): while it ranks and scatters the partition in one stage, the bulk
 // copy of its next partition is already filling the other, so the HBM reads of a block never
 // stop. The stage that was just consumed into registers doubles as the buffer in which the
 // partition is reordered before it is written out.
-__global__ void __launch_bounds__(SORT_THREADS, 2)
+__global__ void __launch_bounds__(SORT_THREADS, SORT_BLOCKS_PER_SM)
 onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                 uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
                 int n, int num_parts, int shift, uint32_t digit_mask, int use_bulk,
@@ -174,7 +219,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
         s_abort = 0;
         const uint32_t first = atomicAdd(ticket, 1u);
         s_tickets[0] = first;
-        prefetch(0, first);
+        if (SORT_STAGES == 2) prefetch(0, first);
         s_tickets[1] = atomicAdd(ticket, 1u);
     }
     // exclusive scan of the global histogram: where each digit's output region starts
@@ -200,19 +245,22 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
     __syncthreads();
 
     uint32_t phase_bits = 0;   // bit st = parity to wait for on stage st
+#ifdef FGS_SORT_TIMING
+    long long t_prev_ = clock64();
+#endif
     for (int it = 0;; it++) {
-        const int st = it & 1;
+        const int st = (SORT_STAGES == 2) ? (it & 1) : 0;
         const uint32_t part = s_tickets[it & 3];
         if (part >= (uint32_t)num_parts) break;
         const int64_t part_base = (int64_t)part * SORT_PART;
         const int valid = (int)min((int64_t)SORT_PART, (int64_t)n - part_base);
-        const bool bulk = use_bulk && valid == SORT_PART;
+        const bool bulk = SORT_STAGES == 2 && use_bulk && valid == SORT_PART;
         // Thread 0: start the copy of the next partition (its ticket was taken one iteration ago) into
         // the other stage, and request the ticket after that; the ticket is only stored at the end of
         // the iteration, so its round trip to the L2 never stalls the block.
         uint32_t ticket_after_next = 0;
         if (tid == 0) {
-            prefetch(st ^ 1, s_tickets[(it + 1) & 3]);
+            if (SORT_STAGES == 2) prefetch(st ^ 1, s_tickets[(it + 1) & 3]);
             ticket_after_next = atomicAdd(ticket, 1u);
         }
         for (int i = tid; i < SORT_WARPS * RADIX / 2; i += SORT_THREADS) reinterpret_cast<uint32_t*>(&s_whist[0][0])[i] = 0;
@@ -237,6 +285,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
             }
         }
         __syncthreads();   // s_whist zeroed, every thread holds its items
+        FGS_T(0);
         if (s_abort) break;
 
         // rank within the warp, item by item, so equal digits keep their input order
@@ -244,7 +293,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
 #pragma unroll
         for (int i = 0; i < SORT_ITEMS; i++) {
             const uint32_t d = (uint32_t)(key[i] >> shift) & digit_mask;
-            const unsigned peers = __match_any_sync(FULL_MASK, d);
+            const unsigned peers = match_digit(d);
             const int leader = __ffs(peers) - 1;
             uint32_t pre = 0;
             if (lane == leader) {
@@ -256,11 +305,18 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
             __syncwarp();
         }
         __syncthreads();
+        FGS_T(1);
 
         // threads 0..RADIX-1: thread d owns digit value d
         uint32_t count = 0, inc_l = 0;
         uint32_t* my_status = status_words + (size_t)part * RADIX + tid;
         const bool publish = (int)part != skip_publish_part;
+        // Look-back window: the status words of the LOOKBACK_WINDOW nearest earlier partitions are
+        // requested together, right after this partition's own count is published, and only looked at
+        // after the block has reordered its items in shared memory, so their latency is hidden and a
+        // look-back that has to cross several partitions costs one round trip, not one per partition.
+        uint32_t sw[LOOKBACK_WINDOW];
+        int64_t p0 = (int64_t)part - 1;
         if (tid < RADIX) {
 #pragma unroll
             for (int w = 0; w < SORT_WARPS; w++) {
@@ -269,6 +325,9 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
                 count += c;
             }
             if (publish) st_relaxed(my_status, (part == 0 ? FLAG_INCLUSIVE : FLAG_AGGREGATE) | count);
+#pragma unroll
+            for (int k = 0; k < LOOKBACK_WINDOW; k++)
+                sw[k] = (p0 - k >= 0) ? ld_relaxed(status_words + (size_t)(p0 - k) * RADIX + tid) : FLAG_INCLUSIVE;
             inc_l = count;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -278,38 +337,16 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
             if (lane == 31) s_scan[warp] = inc_l;
         }
         __syncthreads();
+        uint32_t local_start = 0;
         if (tid < RADIX) {
             uint32_t off_l = 0;
 #pragma unroll
             for (int w = 0; w < RADIX / 32; w++) off_l += (w < warp) ? s_scan[w] : 0;
-            const uint32_t local_start = off_l + inc_l - count;
+            local_start = off_l + inc_l - count;
             s_local_start[tid] = local_start;
-
-            // decoupled look-back over earlier partitions for digit `tid`
-            uint32_t earlier = 0;
-            if (part > 0) {
-                int64_t p = (int64_t)part - 1;
-                int polls = 0;
-                bool failed = false;
-                while (true) {
-                    const uint32_t sw = ld_relaxed(status_words + (size_t)p * RADIX + tid);
-                    const uint32_t f = sw & FLAG_MASK;
-                    if (f == 0) {
-                        if (++polls > LOOKBACK_MAX_POLLS) { failed = true; break; }
-                        __nanosleep(100);
-                        continue;
-                    }
-                    earlier += sw & VALUE_MASK;
-                    if (f == FLAG_INCLUSIVE) break;
-                    p--;   // partition 0 always publishes FLAG_INCLUSIVE, so p never goes below 0
-                }
-                if (failed) { atomicOr(dev_status, FGS_ERR_LOOKBACK_TIMEOUT); s_abort = 1; }
-                if (publish) st_relaxed(my_status, FLAG_INCLUSIVE | ((earlier + count) & VALUE_MASK));
-            }
-            s_global_delta[tid] = (int64_t)s_digit_base[tid] + (int64_t)earlier - (int64_t)local_start;
         }
         __syncthreads();
-        if (s_abort) break;
+        FGS_T(2);
 
         // place keys and values at their partition-local sorted position (the stage is free: its
         // contents live in registers)
@@ -320,7 +357,47 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
             sk[pos] = key[i];
             sv[pos] = val[i];
         }
+        FGS_T(3);
+
+        // decoupled look-back over earlier partitions for digit `tid`
+        if (tid < RADIX) {
+            uint32_t earlier = 0;
+            bool done = (part == 0), failed = false;
+            int polls = 0;
+            while (!done) {
+                int used = 0;   // window entries consumed, nearest partition first, while they are published
+#pragma unroll
+                for (int k = 0; k < LOOKBACK_WINDOW; k++) {
+                    if (!done && used == k) {
+                        const uint32_t f = sw[k] & FLAG_MASK;
+                        if (f != 0) {
+                            earlier += sw[k] & VALUE_MASK;
+                            used = k + 1;
+                            done = (f == FLAG_INCLUSIVE);   // partition 0 always publishes FLAG_INCLUSIVE
+                        }
+                    }
+                }
+                if (done) break;
+                if (used == 0) {
+                    // the nearest unread partition has not published yet: wait for that one word only (polling
+                    // whole windows from every block saturates the L2) and back off between polls
+                    if (++polls > LOOKBACK_MAX_POLLS) { failed = true; break; }
+                    __nanosleep(LOOKBACK_SLEEP_NS);
+                    sw[0] = ld_relaxed(status_words + (size_t)p0 * RADIX + tid);
+                    continue;
+                }
+                p0 -= used;
+#pragma unroll
+                for (int k = 0; k < LOOKBACK_WINDOW; k++)
+                    sw[k] = (p0 - k >= 0) ? ld_relaxed(status_words + (size_t)(p0 - k) * RADIX + tid) : FLAG_INCLUSIVE;
+            }
+            if (failed) { atomicOr(dev_status, FGS_ERR_LOOKBACK_TIMEOUT); s_abort = 1; }
+            if (publish && part > 0) st_relaxed(my_status, FLAG_INCLUSIVE | ((earlier + count) & VALUE_MASK));
+            s_global_delta[tid] = (int64_t)s_digit_base[tid] + (int64_t)earlier - (int64_t)local_start;
+        }
         __syncthreads();
+        FGS_T(4);
+        if (s_abort) break;
 
         // runs of equal digits are contiguous in shared memory and in the destination
 #pragma unroll
@@ -334,8 +411,10 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
                 vals_out[dst] = sv[j];
             }
         }
+        FGS_T(5);
         if (tid == 0) s_tickets[(it + 2) & 3] = ticket_after_next;
         __syncthreads();   // the stage may now be refilled by the copy started in the next iteration
+        FGS_T(6);
     }
 
     // Leaving early (a wait gave up): a copy into the other stage may still be in flight; wait for it
@@ -362,6 +441,15 @@ int g_debug_skip_publish_part = -1;
 
 } // namespace
 } // namespace fgs
+
+#ifdef FGS_SORT_TIMING
+extern "C" int fgs_debug_sort_phase_cycles(unsigned long long* out8, int reset)
+{
+    if (cudaMemcpyFromSymbol(out8, fgs::g_phase_cycles, sizeof(unsigned long long) * 8) != cudaSuccess) return FGS_ERR_CUDA;
+    if (reset) { unsigned long long z[8] = {0}; cudaMemcpyToSymbol(fgs::g_phase_cycles, z, sizeof z); }
+    return FGS_OK;
+}
+#endif
 
 // Test hook: the partition with this index does not publish its look-back words in the next
 // sorts (-1 = off). Later partitions then run out of their poll budget, which exercises the
@@ -429,7 +517,8 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
 
     const uint64_t* src_k = keys_unsorted;
     const uint32_t* src_v = values_unsorted;
-    const int grid_blocks = L.parts < 2 * sm_count[dev] ? L.parts : 2 * sm_count[dev];   // persistent: two blocks per SM
+    const int resident = SORT_BLOCKS_PER_SM * sm_count[dev];   // persistent blocks
+    const int grid_blocks = L.parts < resident ? L.parts : resident;
     for (int p = 0; p < passes; p++) {
         const bool to_out = ((passes - 1 - p) & 1) == 0;
         uint64_t* dst_k = to_out ? keys_sorted : alt_keys;

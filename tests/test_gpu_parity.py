@@ -182,7 +182,7 @@ def test_column_culling_changes_nothing(ops, name, n, size):
         b = Frame(ops, sc2, cam, floats=False, capacity=1 << 24)
     finally:
         L.fgs_debug_preprocess_no_column_cull(0)
-    assert a.R == b.R and a.R > 100000
+    assert a.R == b.R and a.R > 20000
     ka, va = canonical_pairs(a.np("ku", a.R), a.np("vu", a.R))
     kb, vb = canonical_pairs(b.np("ku", b.R), b.np("vu", b.R))
     assert (ka == kb).all() and (va == vb).all()
