@@ -39,6 +39,14 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per unit measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum of one launch) on a
+# 1.5 M-Gaussian case of the same distribution (profiles/*_C4dist_1p5M_4K.txt); traffic grows in proportion
+# to the unit, so the full-size figure is this times the launch's units.
+NCU_DRAM_BYTES_PER_UNIT = {
+    "onesweep_kernel": (125.1e6 / 7.349e6, "R"),      # per pair and pass
+    "preprocess_kernel": (295.1e6 / 1.5e6, "P"),      # per Gaussian
+    "blend_kernel": (115.6e6 / 7.161e6, "S"),         # per blended pair
+}
 
 
 def measured_peaks():
@@ -340,8 +348,13 @@ def main():
         d = stages[dom]
         roofline = {"kernel": {"preprocess": "preprocess_kernel", "sort_pass": "onesweep_kernel", "ranges_blend": "blend_kernel"}[dom],
                     "bound": "hbm", "achieved": d["gbs"], "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                    "frac": d["gbs"] / peak, "traffic": None,
+                    "frac": d["gbs"] / peak, "traffic": None, "traffic_source": None,
                     "algorithmic_bytes_per_launch": d["bytes"], "launch_ms": d["ms"], "launches_per_frame": d["launches"]}
+
+    if roofline is not None:
+        per, unit = NCU_DRAM_BYTES_PER_UNIT[roofline["kernel"]]
+        roofline["traffic"] = per * {"R": R, "P": P, "S": S or 0}[unit]
+        roofline["traffic_source"] = "ncu capture of a smaller case scaled by %s" % unit
 
     # ---- end to end through the operator API: camera from pinned host memory, image to pinned host memory ----
     e2e = None
