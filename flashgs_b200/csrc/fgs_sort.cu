@@ -35,12 +35,6 @@ namespace {
 #ifndef FGS_LOOKBACK_SLEEP_NS
 #define FGS_LOOKBACK_SLEEP_NS 200
 #endif
-#ifndef FGS_SORT_STAGES
-#define FGS_SORT_STAGES 2      // 2: bulk-copy prefetch of the next partition; 1: plain loads, smaller footprint
-#endif
-#ifndef FGS_SORT_BLOCKS_PER_SM
-#define FGS_SORT_BLOCKS_PER_SM 2
-#endif
 #ifndef FGS_LOOKBACK_WINDOW
 #define FGS_LOOKBACK_WINDOW 8
 #endif
@@ -62,9 +56,7 @@ constexpr int LOOKBACK_MAX_POLLS = 1 << 20;             // x (sleep + one L2 rea
 constexpr int LOOKBACK_WINDOW = FGS_LOOKBACK_WINDOW;                      // earlier partitions inspected per round trip
 constexpr int STAGE_BYTES = SORT_PART * 12;             // keys + values of one partition
 constexpr int LOOKBACK_SLEEP_NS = FGS_LOOKBACK_SLEEP_NS;
-constexpr int SORT_STAGES = FGS_SORT_STAGES;
-constexpr int SORT_BLOCKS_PER_SM = FGS_SORT_BLOCKS_PER_SM;
-constexpr int SORT_SMEM_BYTES = SORT_STAGES * STAGE_BYTES;
+constexpr int SORT_SMEM_BYTES = 2 * STAGE_BYTES;        // IN stage + OUT stage
 constexpr int MBAR_MAX_POLLS = 1 << 20;                 // tries of at most ~1 us each: a bulk copy gets about a second
 
 __device__ __forceinline__ uint32_t ld_relaxed(const uint32_t* p)
@@ -119,7 +111,6 @@ histogram_kernel(const uint64_t* __restrict__ keys, int n, int passes, int end_b
     }
 }
 
-// ---- one onesweep pass ----
 // Lanes of the warp that hold the same 8-bit digit: one vote per bit (the match.any instruction gives the
 // same mask but measured several hundred cycles per call here; eight votes are an order of magnitude cheaper).
 __device__ __forceinline__ unsigned match_digit(uint32_t d)
@@ -172,54 +163,74 @@ __device__ unsigned long long g_phase_cycles[8];
 #define FGS_T(i) do { } while (0)
 #endif
 
+
+// ---- named barriers between the warp roles of the pass kernel ----
+__device__ __forceinline__ void bar_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+__device__ __forceinline__ void bar_arrive(int id, int count) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+
+__device__ __forceinline__ uint4 ld_relaxed_v4(const uint32_t* p)
+{
+    uint4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_v4(uint32_t* p, uint4 v)
+{
+    asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 // ---- one onesweep pass ----
-// Persistent blocks (two per SM). A block owns two shared-memory stages of one partition each
-// (4096 keys + 4096 values): while it ranks and scatters the partition in one stage, the bulk
-// copy of its next partition is already filling the other, so the HBM reads of a block never
-// stop. The stage that was just consumed into registers doubles as the buffer in which the
-// partition is reordered before it is written out.
-__global__ void __launch_bounds__(SORT_THREADS, SORT_BLOCKS_PER_SM)
+// Persistent blocks (two per SM) of SORT_THREADS "sorting" threads plus LB_THREADS "look-back" threads.
+//
+// Sorting warps, per partition of SORT_PART pairs: wait for the bulk copy (TMA) that brought the partition
+// into the IN stage, pull it into registers and immediately start the copy of the next partition into the
+// same stage; rank by digit; hand the per-digit counts to the look-back warps; write out the PREVIOUS
+// partition, whose global digit offsets the look-back warps have produced meanwhile; reorder the current
+// partition into the OUT stage.
+// Look-back warps, per partition: publish the counts, walk back over earlier partitions' status words until
+// an inclusive prefix is found, publish this partition's inclusive prefix, hand the offsets back.
+// The look-back of partition i therefore runs while the sorting warps write out partition i-1 and rank
+// partition i+1: persistent blocks advance in lock-step, which makes the walk long (it crosses the partitions
+// of all blocks that started together), and this keeps that wait off the sorting warps' path.
+constexpr int LB_THREADS = 64;                              // each owns 4 digit values (16-byte status accesses)
+constexpr int PASS_THREADS = SORT_THREADS + LB_THREADS;
+constexpr int BAR_SORTERS = 1;                              // barrier ids; 0 is __syncthreads
+constexpr int BAR_COUNTS = 2;                               // +parity: counts of a partition are in shared memory
+constexpr int BAR_OFFSETS = 4;                              // +parity: global offsets of a partition are in shared memory
+constexpr uint32_t NO_TICKET = 0xFFFFFFFFu;
+static_assert(LB_THREADS * 4 == RADIX, "a look-back thread owns four digit values");
+
+__global__ void __launch_bounds__(PASS_THREADS, 2)
 onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                 uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
                 int n, int num_parts, int shift, uint32_t digit_mask, int use_bulk,
                 uint32_t* __restrict__ ticket, const uint32_t* __restrict__ hist,
                 uint32_t* __restrict__ status_words, int* __restrict__ dev_status, int skip_publish_part)
 {
-    extern __shared__ __align__(128) unsigned char s_dyn[];   // 2 stages x (keys 8*PART | values 4*PART)
-    __shared__ __align__(8) uint64_t s_bar[2];
-    __shared__ uint16_t s_whist[SORT_WARPS][RADIX];    // per-warp digit counts, then exclusive warp offsets
-    __shared__ uint32_t s_local_start[RADIX];           // start of each digit's run inside the partition
-    __shared__ int64_t s_global_delta[RADIX];           // global index of a digit's run minus its local start
-    __shared__ uint32_t s_digit_base[RADIX];            // exclusive scan of the global histogram
+    extern __shared__ __align__(128) unsigned char s_dyn[];   // IN stage | OUT stage, each keys 8*PART | values 4*PART
+    __shared__ __align__(8) uint64_t s_bar;                   // completion of the bulk copy into IN
+    __shared__ uint16_t s_whist[SORT_WARPS][RADIX];           // per-warp digit counts, then exclusive warp offsets
+    __shared__ __align__(16) uint32_t s_count[2][RADIX];      // block digit counts of a partition (by parity)
+    __shared__ __align__(16) uint32_t s_gstart[2][RADIX];     // global index where the partition's run of a digit starts
+    __shared__ uint32_t s_local_start[2][RADIX];              // where that run starts inside the reordered partition
+    __shared__ __align__(16) uint32_t s_digit_base[RADIX];    // exclusive scan of the global histogram
     __shared__ uint32_t s_scan[RADIX / 32];
-    __shared__ uint32_t s_tickets[4];                   // partition of iteration i lives in s_tickets[i & 3]
-    __shared__ int s_abort;
+    __shared__ uint32_t s_tickets[4];                         // partition of iteration i lives in s_tickets[i & 3]
+    __shared__ int s_copy_issued[2];                          // by iteration parity: IN is being filled by a bulk copy
+    __shared__ volatile int s_abort;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const unsigned lt = lanemask_lt();
-    auto stage_keys = [&](int st) { return reinterpret_cast<uint64_t*>(s_dyn + (size_t)st * STAGE_BYTES); };
-    auto stage_vals = [&](int st) { return reinterpret_cast<uint32_t*>(s_dyn + (size_t)st * STAGE_BYTES + SORT_PART * 8); };
-    // Thread 0: start the bulk copy of a full partition into a stage (the ragged last partition and
-    // unaligned inputs are copied with plain loads by the whole block when the stage is consumed).
-    uint32_t pending = 0;   // thread 0: bit st = a bulk copy into stage st has been started and not yet waited for
-    auto prefetch = [&](int st, uint32_t part) {
-        if (use_bulk && part < (uint32_t)num_parts && (int64_t)(part + 1) * SORT_PART <= (int64_t)n) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_expect_tx(&s_bar[st], SORT_PART * 12);
-            bulk_load(stage_keys(st), keys_in + (size_t)part * SORT_PART, SORT_PART * 8, &s_bar[st]);
-            bulk_load(stage_vals(st), vals_in + (size_t)part * SORT_PART, SORT_PART * 4, &s_bar[st]);
-            pending |= 1u << st;
-        }
-    };
+    uint64_t* in_keys = reinterpret_cast<uint64_t*>(s_dyn);
+    uint32_t* in_vals = reinterpret_cast<uint32_t*>(s_dyn + SORT_PART * 8);
+    uint64_t* out_keys = reinterpret_cast<uint64_t*>(s_dyn + STAGE_BYTES);
+    uint32_t* out_vals = reinterpret_cast<uint32_t*>(s_dyn + STAGE_BYTES + SORT_PART * 8);
+    auto full_part = [&](uint32_t part) { return part < (uint32_t)num_parts && (int64_t)(part + 1) * SORT_PART <= (int64_t)n; };
 
     if (tid == 0) {
-        mbar_init(&s_bar[0], 1);
-        mbar_init(&s_bar[1], 1);
+        mbar_init(&s_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_abort = 0;
-        const uint32_t first = atomicAdd(ticket, 1u);
-        s_tickets[0] = first;
-        if (SORT_STAGES == 2) prefetch(0, first);
+        s_tickets[0] = atomicAdd(ticket, 1u);
         s_tickets[1] = atomicAdd(ticket, 1u);
     }
     // exclusive scan of the global histogram: where each digit's output region starts
@@ -244,38 +255,125 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
     }
     __syncthreads();
 
-    uint32_t phase_bits = 0;   // bit st = parity to wait for on stage st
+    if (tid >= SORT_THREADS) {
+        // ======================= look-back warps =======================
+        const int t4 = (tid - SORT_THREADS) * 4;   // first of this thread's four digit values
+        for (int it = 0;; it++) {
+            const uint32_t part = s_tickets[it & 3];
+            if (part >= (uint32_t)num_parts) break;
+            const int b = it & 1;
+            bar_sync(BAR_COUNTS + b, PASS_THREADS);                  // counts of this partition are ready
+            const uint4 cnt = *reinterpret_cast<const uint4*>(&s_count[b][t4]);
+            uint32_t* my_status = status_words + (size_t)part * RADIX + t4;
+            const bool publish = (int)part != skip_publish_part;
+
+            uint32_t earlier[4] = { 0, 0, 0, 0 };
+            bool done[4] = { part == 0, part == 0, part == 0, part == 0 };
+            bool failed = false;
+            int64_t p0 = (int64_t)part - 1;     // nearest partition not yet accounted for
+            int polls = 0;
+            while (!(done[0] && done[1] && done[2] && done[3]) && !s_abort) {
+                uint4 sw[LOOKBACK_WINDOW];
+#pragma unroll
+                for (int k = 0; k < LOOKBACK_WINDOW; k++)
+                    sw[k] = (p0 - k >= 0) ? ld_relaxed_v4(status_words + (size_t)(p0 - k) * RADIX + t4)
+                                          : make_uint4(FLAG_INCLUSIVE, FLAG_INCLUSIVE, FLAG_INCLUSIVE, FLAG_INCLUSIVE);
+                int used = 0;   // window entries consumed, nearest partition first, while all four words are published
+#pragma unroll
+                for (int k = 0; k < LOOKBACK_WINDOW; k++) {
+                    const uint32_t w4[4] = { sw[k].x, sw[k].y, sw[k].z, sw[k].w };
+                    bool ready = used == k;
+#pragma unroll
+                    for (int q = 0; q < 4; q++) ready = ready && (done[q] || (w4[q] & FLAG_MASK) != 0);
+                    if (ready) {
+#pragma unroll
+                        for (int q = 0; q < 4; q++)
+                            if (!done[q]) { earlier[q] += w4[q] & VALUE_MASK; done[q] = (w4[q] & FLAG_MASK) == FLAG_INCLUSIVE; }
+                        used = k + 1;
+                    }
+                }
+                p0 -= used;
+#ifdef FGS_SORT_TIMING
+                if (t4 == 0) { atomicAdd(&g_phase_cycles[6], 1ull); if (used == 0) atomicAdd(&g_phase_cycles[7], 1ull); }
+#endif
+                if (used == 0) {    // the nearest partition has not published yet: back off before asking again
+                    if (++polls > LOOKBACK_MAX_POLLS) { failed = true; break; }
+                    __nanosleep(LOOKBACK_SLEEP_NS);
+                }
+            }
+            if (failed) { atomicOr(dev_status, FGS_ERR_LOOKBACK_TIMEOUT); s_abort = 1; }
+            if (publish && part > 0)
+                st_relaxed_v4(my_status, make_uint4(FLAG_INCLUSIVE | ((earlier[0] + cnt.x) & VALUE_MASK), FLAG_INCLUSIVE | ((earlier[1] + cnt.y) & VALUE_MASK),
+                                                    FLAG_INCLUSIVE | ((earlier[2] + cnt.z) & VALUE_MASK), FLAG_INCLUSIVE | ((earlier[3] + cnt.w) & VALUE_MASK)));
+            const uint4 base = *reinterpret_cast<const uint4*>(&s_digit_base[t4]);
+            *reinterpret_cast<uint4*>(&s_gstart[b][t4]) = make_uint4(base.x + earlier[0], base.y + earlier[1], base.z + earlier[2], base.w + earlier[3]);
+            bar_arrive(BAR_OFFSETS + b, PASS_THREADS);               // offsets of this partition are ready
+        }
+        return;
+    }
+
+    // ======================= sorting warps =======================
+    const unsigned lt = lanemask_lt();
+    uint32_t in_parity = 0;
+    bool copy_pending = false;      // thread 0: a bulk copy into IN has been started and not yet waited for
+    // Thread 0 only: start the bulk copy of the partition of iteration `iter` into IN, if it is a whole,
+    // 16-byte aligned partition; otherwise (ragged tail, unaligned input, after a failed wait) the sorting
+    // threads fetch it with plain loads when its turn comes.
+    auto prefetch = [&](int iter, uint32_t part) {
+        const bool issue = use_bulk && full_part(part) && !s_abort;
+        if (issue) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(&s_bar, SORT_PART * 12);
+            bulk_load(in_keys, keys_in + (size_t)part * SORT_PART, SORT_PART * 8, &s_bar);
+            bulk_load(in_vals, vals_in + (size_t)part * SORT_PART, SORT_PART * 4, &s_bar);
+            copy_pending = true;
+        }
+        s_copy_issued[iter & 1] = issue ? 1 : 0;
+    };
+    // write the reordered partition held in OUT to its digits' global runs
+    auto write_out = [&](int b, int valid, uint32_t* gstart, uint32_t* lstart) {
+        (void)b;
+#pragma unroll
+        for (int i = 0; i < SORT_ITEMS; i++) {
+            const int j = i * SORT_THREADS + tid;
+            if (j < valid) {
+                const uint64_t k = out_keys[j];
+                const uint32_t d = (uint32_t)(k >> shift) & digit_mask;
+                const uint32_t dst = gstart[d] + ((uint32_t)j - lstart[d]);
+                keys_out[dst] = k;
+                vals_out[dst] = out_vals[j];
+            }
+        }
+    };
+    if (tid == 0) prefetch(0, s_tickets[0]);
+    bar_sync(BAR_SORTERS, SORT_THREADS);
 #ifdef FGS_SORT_TIMING
     long long t_prev_ = clock64();
 #endif
-    for (int it = 0;; it++) {
-        const int st = (SORT_STAGES == 2) ? (it & 1) : 0;
+
+    int it = 0, prev_valid = 0;
+    for (;; it++) {
         const uint32_t part = s_tickets[it & 3];
         if (part >= (uint32_t)num_parts) break;
+        const int b = it & 1;
         const int64_t part_base = (int64_t)part * SORT_PART;
         const int valid = (int)min((int64_t)SORT_PART, (int64_t)n - part_base);
-        const bool bulk = SORT_STAGES == 2 && use_bulk && valid == SORT_PART;
-        // Thread 0: start the copy of the next partition (its ticket was taken one iteration ago) into
-        // the other stage, and request the ticket after that; the ticket is only stored at the end of
-        // the iteration, so its round trip to the L2 never stalls the block.
+        const bool bulk = s_copy_issued[b] != 0;
+        // Thread 0 requests the ticket after next now and stores it at the end of the iteration, so the
+        // round trip of the atomic never stalls the block.
         uint32_t ticket_after_next = 0;
-        if (tid == 0) {
-            if (SORT_STAGES == 2) prefetch(st ^ 1, s_tickets[(it + 1) & 3]);
-            ticket_after_next = atomicAdd(ticket, 1u);
-        }
+        if (tid == 0) ticket_after_next = atomicAdd(ticket, 1u);
         for (int i = tid; i < SORT_WARPS * RADIX / 2; i += SORT_THREADS) reinterpret_cast<uint32_t*>(&s_whist[0][0])[i] = 0;
 
-        uint64_t* sk = stage_keys(st);
-        uint32_t* sv = stage_vals(st);
         uint64_t key[SORT_ITEMS];
         uint32_t val[SORT_ITEMS];
         const int wbase = warp * (32 * SORT_ITEMS);   // warp-striped: item i of lane l sits at wbase + i*32 + l
         if (bulk) {
-            if (!mbar_wait(&s_bar[st], (phase_bits >> st) & 1u)) { atomicOr(dev_status, FGS_ERR_LOOKBACK_TIMEOUT); s_abort = 1; }
-            else pending &= ~(1u << st);
-            phase_bits ^= 1u << st;
+            if (!mbar_wait(&s_bar, in_parity)) { atomicOr(dev_status, FGS_ERR_LOOKBACK_TIMEOUT); s_abort = 1; }
+            else copy_pending = false;
+            in_parity ^= 1u;
 #pragma unroll
-            for (int i = 0; i < SORT_ITEMS; i++) { key[i] = sk[wbase + i * 32 + lane]; val[i] = sv[wbase + i * 32 + lane]; }
+            for (int i = 0; i < SORT_ITEMS; i++) { key[i] = in_keys[wbase + i * 32 + lane]; val[i] = in_vals[wbase + i * 32 + lane]; }
         } else {
 #pragma unroll
             for (int i = 0; i < SORT_ITEMS; i++) {
@@ -284,9 +382,9 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
                 val[i] = local < valid ? __ldg(vals_in + part_base + local) : 0u;
             }
         }
-        __syncthreads();   // s_whist zeroed, every thread holds its items
+        bar_sync(BAR_SORTERS, SORT_THREADS);   // s_whist zeroed; every thread holds its items, IN is free again
+        if (tid == 0) prefetch(it + 1, s_tickets[(it + 1) & 3]);
         FGS_T(0);
-        if (s_abort) break;
 
         // rank within the warp, item by item, so equal digits keep their input order
         uint32_t rank[SORT_ITEMS];
@@ -304,125 +402,70 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
             rank[i] = pre + __popc(peers & lt);
             __syncwarp();
         }
-        __syncthreads();
+        bar_sync(BAR_SORTERS, SORT_THREADS);
         FGS_T(1);
 
-        // threads 0..RADIX-1: thread d owns digit value d
-        uint32_t count = 0, inc_l = 0;
-        uint32_t* my_status = status_words + (size_t)part * RADIX + tid;
-        const bool publish = (int)part != skip_publish_part;
-        // Look-back window: the status words of the LOOKBACK_WINDOW nearest earlier partitions are
-        // requested together, right after this partition's own count is published, and only looked at
-        // after the block has reordered its items in shared memory, so their latency is hidden and a
-        // look-back that has to cross several partitions costs one round trip, not one per partition.
-        uint32_t sw[LOOKBACK_WINDOW];
-        int64_t p0 = (int64_t)part - 1;
-        if (tid < RADIX) {
+        // thread d owns digit value d: block count, exclusive warp offsets, start of the run inside the partition
+        uint32_t count = 0;
 #pragma unroll
-            for (int w = 0; w < SORT_WARPS; w++) {
-                const uint32_t c = s_whist[w][tid];
-                s_whist[w][tid] = (uint16_t)count;   // exclusive offset of warp w inside the digit's run
-                count += c;
-            }
-            if (publish) st_relaxed(my_status, (part == 0 ? FLAG_INCLUSIVE : FLAG_AGGREGATE) | count);
-#pragma unroll
-            for (int k = 0; k < LOOKBACK_WINDOW; k++)
-                sw[k] = (p0 - k >= 0) ? ld_relaxed(status_words + (size_t)(p0 - k) * RADIX + tid) : FLAG_INCLUSIVE;
-            inc_l = count;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t a = __shfl_up_sync(FULL_MASK, inc_l, o);
-                if (lane >= o) inc_l += a;
-            }
-            if (lane == 31) s_scan[warp] = inc_l;
+        for (int w = 0; w < SORT_WARPS; w++) {
+            const uint32_t c = s_whist[w][tid];
+            s_whist[w][tid] = (uint16_t)count;
+            count += c;
         }
-        __syncthreads();
-        uint32_t local_start = 0;
-        if (tid < RADIX) {
+        s_count[b][tid] = count;
+        // published by the sorting thread itself, at once: later partitions wait for exactly this word, and the
+        // look-back warps may still be busy with the previous partition
+        if ((int)part != skip_publish_part)
+            st_relaxed(status_words + (size_t)part * RADIX + tid, (part == 0 ? FLAG_INCLUSIVE : FLAG_AGGREGATE) | count);
+        uint32_t inc_l = count;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t a = __shfl_up_sync(FULL_MASK, inc_l, o);
+            if (lane >= o) inc_l += a;
+        }
+        if (lane == 31) s_scan[warp] = inc_l;
+        bar_arrive(BAR_COUNTS + b, PASS_THREADS);   // the look-back warps take it from here
+        bar_sync(BAR_SORTERS, SORT_THREADS);
+        {
             uint32_t off_l = 0;
 #pragma unroll
             for (int w = 0; w < RADIX / 32; w++) off_l += (w < warp) ? s_scan[w] : 0;
-            local_start = off_l + inc_l - count;
-            s_local_start[tid] = local_start;
+            s_local_start[b][tid] = off_l + inc_l - count;
         }
-        __syncthreads();
         FGS_T(2);
 
-        // place keys and values at their partition-local sorted position (the stage is free: its
-        // contents live in registers)
+        // the previous partition: its offsets have been looked up while this one was loaded and ranked
+        if (it > 0) {
+            bar_sync(BAR_OFFSETS + (b ^ 1), PASS_THREADS);
+            FGS_T(4);
+            if (!s_abort) write_out(b ^ 1, prev_valid, s_gstart[b ^ 1], s_local_start[b ^ 1]);
+            FGS_T(5);
+        }
+        bar_sync(BAR_SORTERS, SORT_THREADS);   // OUT is free, s_local_start[b] is complete
+
+        // reorder this partition into OUT
 #pragma unroll
         for (int i = 0; i < SORT_ITEMS; i++) {
             const uint32_t d = (uint32_t)(key[i] >> shift) & digit_mask;
-            const uint32_t pos = s_local_start[d] + s_whist[warp][d] + rank[i];
-            sk[pos] = key[i];
-            sv[pos] = val[i];
+            const uint32_t pos = s_local_start[b][d] + s_whist[warp][d] + rank[i];
+            out_keys[pos] = key[i];
+            out_vals[pos] = val[i];
         }
+        prev_valid = valid;
+        // after a failed wait no further partitions are started: both loops end within two iterations
+        if (tid == 0) s_tickets[(it + 2) & 3] = s_abort ? NO_TICKET : ticket_after_next;
+        bar_sync(BAR_SORTERS, SORT_THREADS);   // OUT complete, ticket visible
         FGS_T(3);
-
-        // decoupled look-back over earlier partitions for digit `tid`
-        if (tid < RADIX) {
-            uint32_t earlier = 0;
-            bool done = (part == 0), failed = false;
-            int polls = 0;
-            while (!done) {
-                int used = 0;   // window entries consumed, nearest partition first, while they are published
-#pragma unroll
-                for (int k = 0; k < LOOKBACK_WINDOW; k++) {
-                    if (!done && used == k) {
-                        const uint32_t f = sw[k] & FLAG_MASK;
-                        if (f != 0) {
-                            earlier += sw[k] & VALUE_MASK;
-                            used = k + 1;
-                            done = (f == FLAG_INCLUSIVE);   // partition 0 always publishes FLAG_INCLUSIVE
-                        }
-                    }
-                }
-                if (done) break;
-                if (used == 0) {
-                    // the nearest unread partition has not published yet: wait for that one word only (polling
-                    // whole windows from every block saturates the L2) and back off between polls
-                    if (++polls > LOOKBACK_MAX_POLLS) { failed = true; break; }
-                    __nanosleep(LOOKBACK_SLEEP_NS);
-                    sw[0] = ld_relaxed(status_words + (size_t)p0 * RADIX + tid);
-                    continue;
-                }
-                p0 -= used;
-#pragma unroll
-                for (int k = 0; k < LOOKBACK_WINDOW; k++)
-                    sw[k] = (p0 - k >= 0) ? ld_relaxed(status_words + (size_t)(p0 - k) * RADIX + tid) : FLAG_INCLUSIVE;
-            }
-            if (failed) { atomicOr(dev_status, FGS_ERR_LOOKBACK_TIMEOUT); s_abort = 1; }
-            if (publish && part > 0) st_relaxed(my_status, FLAG_INCLUSIVE | ((earlier + count) & VALUE_MASK));
-            s_global_delta[tid] = (int64_t)s_digit_base[tid] + (int64_t)earlier - (int64_t)local_start;
-        }
-        __syncthreads();
-        FGS_T(4);
-        if (s_abort) break;
-
-        // runs of equal digits are contiguous in shared memory and in the destination
-#pragma unroll
-        for (int i = 0; i < SORT_ITEMS; i++) {
-            const int j = i * SORT_THREADS + tid;
-            if (j < valid) {
-                const uint64_t k = sk[j];
-                const uint32_t d = (uint32_t)(k >> shift) & digit_mask;
-                const int64_t dst = s_global_delta[d] + j;
-                keys_out[dst] = k;
-                vals_out[dst] = sv[j];
-            }
-        }
-        FGS_T(5);
-        if (tid == 0) s_tickets[(it + 2) & 3] = ticket_after_next;
-        __syncthreads();   // the stage may now be refilled by the copy started in the next iteration
-        FGS_T(6);
     }
-
-    // Leaving early (a wait gave up): a copy into the other stage may still be in flight; wait for it
-    // (bounded) so that nothing writes into shared memory after the block is gone.
-    if (tid == 0) {
-        for (int st = 0; st < 2; st++)
-            if (pending & (1u << st)) mbar_wait(&s_bar[st], (phase_bits >> st) & 1u);
+    if (it > 0) {   // the last partition
+        const int b = (it - 1) & 1;
+        bar_sync(BAR_OFFSETS + b, PASS_THREADS);
+        if (!s_abort) write_out(b, prev_valid, s_gstart[b], s_local_start[b]);
     }
+    // Leaving after a failed wait: a copy into IN may still be in flight; wait for it (bounded) so that
+    // nothing writes into shared memory after the block is gone.
+    if (tid == 0 && copy_pending) mbar_wait(&s_bar, in_parity);
 }
 
 __global__ void copy_pairs_kernel(const uint64_t* __restrict__ ki, const uint32_t* __restrict__ vi,
@@ -517,7 +560,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
 
     const uint64_t* src_k = keys_unsorted;
     const uint32_t* src_v = values_unsorted;
-    const int resident = SORT_BLOCKS_PER_SM * sm_count[dev];   // persistent blocks
+    const int resident = 2 * sm_count[dev];   // persistent blocks, two per SM
     const int grid_blocks = L.parts < resident ? L.parts : resident;
     for (int p = 0; p < passes; p++) {
         const bool to_out = ((passes - 1 - p) & 1) == 0;
@@ -526,7 +569,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         const int shift = p * RADIX_BITS;
         const int bits = (end_bit - shift) < RADIX_BITS ? (end_bit - shift) : RADIX_BITS;
         const int use_bulk = aligned16(src_k) && aligned16(src_v);
-        onesweep_kernel<<<grid_blocks, SORT_THREADS, SORT_SMEM_BYTES, st>>>(src_k, src_v, dst_k, dst_v, n, L.parts, shift,
+        onesweep_kernel<<<grid_blocks, PASS_THREADS, SORT_SMEM_BYTES, st>>>(src_k, src_v, dst_k, dst_v, n, L.parts, shift,
                                                          (1u << bits) - 1u, use_bulk, tickets + p, hist + p * RADIX,
                                                          status_words + (size_t)p * L.parts * RADIX,
                                                          dev_status, g_debug_skip_publish_part);
