@@ -199,11 +199,22 @@ constexpr int BAR_COUNTS = 2;                               // +parity: counts o
 constexpr int BAR_OFFSETS = 4;                              // +parity: global offsets of a partition are in shared memory
 constexpr uint32_t NO_TICKET = 0xFFFFFFFFu;
 static_assert(LB_THREADS * 4 == RADIX, "a look-back thread owns four digit values");
+static_assert(SORT_THREADS == RADIX, "sorting thread d owns digit value d");
 
+// Digit of a key: SHIFT is a multiple of 8 known at compile time, so the digit is a byte of the low or of
+// the high word and costs one shift-and-mask.
+template <int SHIFT>
+__device__ __forceinline__ uint32_t digit_of(uint64_t key, uint32_t digit_mask)
+{
+    const uint32_t word = SHIFT < 32 ? (uint32_t)key : (uint32_t)(key >> 32);
+    return (word >> (SHIFT & 31)) & digit_mask;
+}
+
+template <int SHIFT>
 __global__ void __launch_bounds__(PASS_THREADS, 2)
 onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                 uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
-                int n, int num_parts, int shift, uint32_t digit_mask, int use_bulk,
+                int n, int num_parts, uint32_t digit_mask, int use_bulk,
                 uint32_t* __restrict__ ticket, const uint32_t* __restrict__ hist,
                 uint32_t* __restrict__ status_words, int* __restrict__ dev_status, int skip_publish_part)
 {
@@ -213,6 +224,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
     __shared__ __align__(16) uint32_t s_count[2][RADIX];      // block digit counts of a partition (by parity)
     __shared__ __align__(16) uint32_t s_gstart[2][RADIX];     // global index where the partition's run of a digit starts
     __shared__ uint32_t s_local_start[2][RADIX];              // where that run starts inside the reordered partition
+    __shared__ uint32_t s_delta[RADIX];                       // s_gstart - s_local_start of the partition being written out
     __shared__ __align__(16) uint32_t s_digit_base[RADIX];    // exclusive scan of the global histogram
     __shared__ uint32_t s_scan[RADIX / 32];
     __shared__ uint32_t s_tickets[4];                         // partition of iteration i lives in s_tickets[i & 3]
@@ -331,15 +343,15 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
         s_copy_issued[iter & 1] = issue ? 1 : 0;
     };
     // write the reordered partition held in OUT to its digits' global runs
-    auto write_out = [&](int b, int valid, uint32_t* gstart, uint32_t* lstart) {
-        (void)b;
+    auto write_out = [&](int valid, const uint32_t* gstart, const uint32_t* lstart) {
+        s_delta[tid] = gstart[tid] - lstart[tid];   // destination index minus index inside OUT, per digit (mod 2^32)
+        bar_sync(BAR_SORTERS, SORT_THREADS);
 #pragma unroll
         for (int i = 0; i < SORT_ITEMS; i++) {
             const int j = i * SORT_THREADS + tid;
             if (j < valid) {
                 const uint64_t k = out_keys[j];
-                const uint32_t d = (uint32_t)(k >> shift) & digit_mask;
-                const uint32_t dst = gstart[d] + ((uint32_t)j - lstart[d]);
+                const uint32_t dst = s_delta[digit_of<SHIFT>(k, digit_mask)] + (uint32_t)j;
                 keys_out[dst] = k;
                 vals_out[dst] = out_vals[j];
             }
@@ -390,15 +402,12 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
         uint32_t rank[SORT_ITEMS];
 #pragma unroll
         for (int i = 0; i < SORT_ITEMS; i++) {
-            const uint32_t d = (uint32_t)(key[i] >> shift) & digit_mask;
+            const uint32_t d = digit_of<SHIFT>(key[i], digit_mask);
             const unsigned peers = match_digit(d);
-            const int leader = __ffs(peers) - 1;
-            uint32_t pre = 0;
-            if (lane == leader) {
-                pre = s_whist[warp][d];
-                s_whist[warp][d] = (uint16_t)(pre + __popc(peers));
-            }
-            pre = __shfl_sync(FULL_MASK, pre, leader);
+            // every lane of a peer group reads the group's running count, then its lowest lane adds the group
+            const uint32_t pre = s_whist[warp][d];
+            __syncwarp();
+            if ((peers & lt) == 0) s_whist[warp][d] = (uint16_t)(pre + __popc(peers));
             rank[i] = pre + __popc(peers & lt);
             __syncwarp();
         }
@@ -439,7 +448,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
         if (it > 0) {
             bar_sync(BAR_OFFSETS + (b ^ 1), PASS_THREADS);
             FGS_T(4);
-            if (!s_abort) write_out(b ^ 1, prev_valid, s_gstart[b ^ 1], s_local_start[b ^ 1]);
+            write_out(s_abort ? 0 : prev_valid, s_gstart[b ^ 1], s_local_start[b ^ 1]);
             FGS_T(5);
         }
         bar_sync(BAR_SORTERS, SORT_THREADS);   // OUT is free, s_local_start[b] is complete
@@ -447,7 +456,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
         // reorder this partition into OUT
 #pragma unroll
         for (int i = 0; i < SORT_ITEMS; i++) {
-            const uint32_t d = (uint32_t)(key[i] >> shift) & digit_mask;
+            const uint32_t d = digit_of<SHIFT>(key[i], digit_mask);
             const uint32_t pos = s_local_start[b][d] + s_whist[warp][d] + rank[i];
             out_keys[pos] = key[i];
             out_vals[pos] = val[i];
@@ -461,7 +470,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
     if (it > 0) {   // the last partition
         const int b = (it - 1) & 1;
         bar_sync(BAR_OFFSETS + b, PASS_THREADS);
-        if (!s_abort) write_out(b, prev_valid, s_gstart[b], s_local_start[b]);
+        write_out(s_abort ? 0 : prev_valid, s_gstart[b], s_local_start[b]);
     }
     // Leaving after a failed wait: a copy into IN may still be in flight; wait for it (bounded) so that
     // nothing writes into shared memory after the block is gone.
@@ -544,8 +553,11 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     if (!smem_opt_in[dev]) {
         if (cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count[dev] <= 0)
             return FGS_ERR_CUDA;
-        if (cudaFuncSetAttribute(onesweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SORT_SMEM_BYTES) != cudaSuccess)
-            return FGS_ERR_CUDA;
+        cudaError_t e = cudaSuccess;
+#define FGS_OPT_IN(SHIFT) if (e == cudaSuccess) e = cudaFuncSetAttribute(onesweep_kernel<SHIFT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SORT_SMEM_BYTES);
+        FGS_OPT_IN(0) FGS_OPT_IN(8) FGS_OPT_IN(16) FGS_OPT_IN(24) FGS_OPT_IN(32) FGS_OPT_IN(40) FGS_OPT_IN(48) FGS_OPT_IN(56)
+#undef FGS_OPT_IN
+        if (e != cudaSuccess) return FGS_ERR_CUDA;
         smem_opt_in[dev] = true;
     }
 
@@ -569,10 +581,17 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         const int shift = p * RADIX_BITS;
         const int bits = (end_bit - shift) < RADIX_BITS ? (end_bit - shift) : RADIX_BITS;
         const int use_bulk = aligned16(src_k) && aligned16(src_v);
-        onesweep_kernel<<<grid_blocks, PASS_THREADS, SORT_SMEM_BYTES, st>>>(src_k, src_v, dst_k, dst_v, n, L.parts, shift,
-                                                         (1u << bits) - 1u, use_bulk, tickets + p, hist + p * RADIX,
-                                                         status_words + (size_t)p * L.parts * RADIX,
-                                                         dev_status, g_debug_skip_publish_part);
+#define FGS_PASS(SHIFT)                                                                                            \
+    case SHIFT:                                                                                                    \
+        onesweep_kernel<SHIFT><<<grid_blocks, PASS_THREADS, SORT_SMEM_BYTES, st>>>(                                \
+            src_k, src_v, dst_k, dst_v, n, L.parts, (1u << bits) - 1u, use_bulk, tickets + p, hist + p * RADIX,    \
+            status_words + (size_t)p * L.parts * RADIX, dev_status, g_debug_skip_publish_part);                    \
+        break;
+        switch (shift) {
+            FGS_PASS(0) FGS_PASS(8) FGS_PASS(16) FGS_PASS(24) FGS_PASS(32) FGS_PASS(40) FGS_PASS(48) FGS_PASS(56)
+        default: return FGS_ERR_BAD_ARG;
+        }
+#undef FGS_PASS
         src_k = dst_k;
         src_v = dst_v;
         if (events) cudaEventRecord(events[2 + p], st);
