@@ -46,6 +46,7 @@ NCU_DRAM_BYTES_PER_UNIT = {
     "onesweep_kernel": (125.1e6 / 7.349e6, "R"),      # per pair and pass
     "preprocess_kernel": (295.1e6 / 1.5e6, "P"),      # per Gaussian
     "blend_kernel": (115.6e6 / 7.161e6, "S"),         # per blended pair
+    "local_sort_kernel": (24.0, "R"),                 # not captured yet: the algorithmic 24 B per pair
 }
 
 
@@ -312,10 +313,13 @@ def main():
     peak, peak_src = measured_peaks()
     stages = {}
     roofline = None
+    kind = []
     if args.impl == "ours":
         L = _lib.load()
         import ctypes as C
-        ms = (C.c_float * 16)()
+        CAPN = 32
+        ms = (C.c_float * CAPN)()
+        kinds = (C.c_int * CAPN)()
         nl = C.c_int(0)
         per = []
         for _ in range(5):
@@ -324,17 +328,24 @@ def main():
             st = L.fgs_sort_pairs_profile(n, W, H, 16, 16, ras.list_sorting_space.data_ptr(), ras.list_sorting_space.numel(),
                                           ras.gaussian_keys_unsorted.data_ptr(), ras.gaussian_values_unsorted.data_ptr(),
                                           ras.gaussian_keys_sorted.data_ptr(), ras.gaussian_values_sorted.data_ptr(),
-                                          torch.cuda.current_stream().cuda_stream, ms, 16, C.byref(nl))
+                                          torch.cuda.current_stream().cuda_stream, ms, kinds, CAPN, C.byref(nl))
             _lib.check("fgs_sort_pairs_profile", st)
             per.append([ms[i] for i in range(nl.value)])
-        per = np.median(np.array(per), axis=0) if nl.value else np.zeros(1)
-        hist_ms, pass_ms = float(per[0]), [float(x) for x in per[1:]]
+        per = np.median(np.array(per), axis=0) if nl.value else np.zeros(0)
+        kind = [kinds[i] for i in range(nl.value)]
+        by_kind = lambda k: [float(per[i]) for i in range(len(kind)) if kind[i] == k]  # noqa: E731
+        hist_ms = sum(by_kind(0))
+        pass_ms = by_kind(1)
+        seg_ms, local_ms, standby_ms = sum(by_kind(2)), sum(by_kind(3)), sum(by_kind(4))
         gbs = lambda b, t: b / (t * 1e-3) / 1e9 if t > 0 else 0.0  # noqa: E731
         mean_pass = float(np.mean(pass_ms)) if pass_ms else 0.0
         stages = {
             "preprocess": {"ms": pre_ms, "launches": 1, "bytes": bytes_pre, "gbs": gbs(bytes_pre, pre_ms)},
             "sort_histogram": {"ms": hist_ms, "launches": 1, "bytes": bytes_hist, "gbs": gbs(bytes_hist, hist_ms)},
-            "sort_pass": {"ms": mean_pass, "launches": len(pass_ms), "bytes": bytes_sort_pass, "gbs": gbs(bytes_sort_pass, mean_pass)},
+            "sort_digit_pass": {"ms": mean_pass, "launches": len(pass_ms), "bytes": bytes_sort_pass, "gbs": gbs(bytes_sort_pass, mean_pass)},
+            "sort_tile_segments": {"ms": seg_ms, "launches": len(by_kind(2))},
+            "sort_tile_local": {"ms": local_ms, "launches": len(by_kind(3)), "bytes": bytes_sort_pass, "gbs": gbs(bytes_sort_pass, local_ms)},
+            "sort_standby_passes": {"ms": standby_ms, "launches": len(by_kind(4))},
             "sort_total": {"ms": sort_ms, "bytes_compulsory": 24 * R},
             "ranges_blend": {"ms": render_ms, "launches": 2, "bytes": bytes_render, "gbs": gbs(bytes_render, render_ms),
                              "pixel_splat_pairs": None if S is None else S * 256},
@@ -343,10 +354,11 @@ def main():
             if "gbs" in s:
                 s["frac"] = s["gbs"] / peak
         # the dominant kernel: the one with the largest total time per frame
-        cand = {"preprocess": pre_ms, "sort_pass": mean_pass * len(pass_ms), "ranges_blend": render_ms}
+        cand = {"preprocess": pre_ms, "sort_digit_pass": mean_pass * len(pass_ms), "sort_tile_local": local_ms, "ranges_blend": render_ms}
         dom = max(cand, key=cand.get)
         d = stages[dom]
-        roofline = {"kernel": {"preprocess": "preprocess_kernel", "sort_pass": "onesweep_kernel", "ranges_blend": "blend_kernel"}[dom],
+        roofline = {"kernel": {"preprocess": "preprocess_kernel", "sort_digit_pass": "onesweep_kernel",
+                               "sort_tile_local": "local_sort_kernel", "ranges_blend": "blend_kernel"}[dom],
                     "bound": "hbm", "achieved": d["gbs"], "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                     "frac": d["gbs"] / peak, "traffic": None, "traffic_source": None,
                     "algorithmic_bytes_per_launch": d["bytes"], "launch_ms": d["ms"], "launches_per_frame": d["launches"]}
@@ -413,6 +425,7 @@ def main():
         out_img = bufs[0]
 
     status = ops.device_status() if args.impl == "ours" else 0
+    launches_per_frame = 3 + (len(kind) if args.impl == "ours" else 0)   # preprocess, tile ranges, blend + the sort's kernels
 
     cpu_baseline = None
     if args.impl == "ours" and rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -427,7 +440,7 @@ def main():
             "steps": K, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
             "clocks": clocks, "e2e": e2e,
-            "gpu_launches": (10 * K) if args.impl == "ours" else 0,
+            "gpu_launches": (launches_per_frame * K) if args.impl == "ours" else 0,
             "stage_ms": {"preprocess": pre_ms, "sort": sort_ms, "ranges_blend": render_ms},
             "counters": {"P": P, "P1": P1, "P2": P2, "V": V, "R": R, "S": S, "tiles": Tn},
             "device_status": status,

@@ -30,12 +30,14 @@ SIGNATURES = {
                                   _p, _p, _p, _p, _p, _i64, _p, _p]),
     "fgs_sort_temp_bytes": (C.c_size_t, [_i64]),
     "fgs_sort_pairs": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p]),
-    "fgs_sort_pairs_profile": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p, _p, _i, _p]),
+    "fgs_sort_pairs_profile": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p, _p, _p, _i, _p]),
     "fgs_render_16x16": (_i, [_i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]),
     "fgs_render_32x16": (_i, [_i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]),
     "fgs_render_32x32": (_i, [_i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]),
     "fgs_render_ex": (_i, [_i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _p, _p, _p, _p, _p]),
     "fgs_tile_ranges": (_i, [_i, _i, _p, _p, _p]),
+    "fgs_ply_vertex_count": (C.c_longlong, [C.c_char_p]),
+    "fgs_ply_load": (_i, [C.c_char_p, C.c_longlong, _p, _p, _p, _p]),
 }
 
 _lib = None
@@ -64,6 +66,8 @@ def load():
             fn.argtypes = args
         lib.fgs_debug_sort_skip_publish.restype = None
         lib.fgs_debug_sort_skip_publish.argtypes = [_i]
+        lib.fgs_debug_sort_plain.restype = None
+        lib.fgs_debug_sort_plain.argtypes = [_i]
         lib.fgs_debug_preprocess_no_column_cull.restype = None
         lib.fgs_debug_preprocess_no_column_cull.argtypes = [_i]
         _lib = lib

@@ -194,6 +194,15 @@ __device__ __forceinline__ void stage_floats(float* dst, const float* src, int n
     }
 }
 
+// Optional per-phase cycle accounting (compile with -DFGS_PRE_TIMING): thread 0 of every block adds the SM
+// cycles spent in each phase to g_pre_cycles; read with fgs_debug_pre_phase_cycles.
+#ifdef FGS_PRE_TIMING
+__device__ unsigned long long g_pre_cycles[8];
+#define FGS_PT(i) do { if (threadIdx.x == 0) { const long long now_ = clock64(); atomicAdd(&g_pre_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
+#else
+#define FGS_PT(i) do { } while (0)
+#endif
+
 template <bool VEC>
 __global__ void __launch_bounds__(PRE_THREADS)
 preprocess_kernel(int P,
@@ -217,6 +226,9 @@ preprocess_kernel(int P,
     __shared__ int s_woff[32];
     __shared__ int s_wsum[PRE_WARPS];
 
+#ifdef FGS_PRE_TIMING
+    long long t_prev_ = clock64();
+#endif
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int base = blockIdx.x * PRE_THREADS;
@@ -227,6 +239,7 @@ preprocess_kernel(int P,
     stage_floats<VEC>(s_opa, opacities + base, n_here);
     s_vis[tid] = 0;
     __syncthreads();
+    FGS_PT(0);
 
     // ---- per-Gaussian projection (preprocess.cu:282-316) ----
     bool point_valid = false;
@@ -273,6 +286,7 @@ preprocess_kernel(int P,
         } while (false);
     }
 
+    FGS_PT(1);
     // Work items of this Gaussian: one per (tile row, window of 32 tile columns).
     const int rect_w = point_valid ? (maxx - minx) : 0;
     const int nseg = (rect_w + 31) >> 5;
@@ -313,6 +327,7 @@ preprocess_kernel(int P,
     s_prefix[tid] = wbase + incl - items;
     if (tid == PRE_THREADS - 1) s_prefix[PRE_THREADS] = wbase + incl;
     __syncthreads();
+    FGS_PT(2);
     const int total = s_prefix[PRE_THREADS];
 
     // ---- walk the item space: PRE_K items per thread per chunk ----
@@ -354,9 +369,9 @@ preprocess_kernel(int P,
                         x_end = x_begin;
                     } else {
                         const float det = q.x * q.z - q.y * q.y;
-                        const float s_lo = sqrtf(fmaxf(0.f, q.x * cu.x - det * d_lo * d_lo));
-                        const float s_hi = sqrtf(fmaxf(0.f, q.x * cu.x - det * d_hi * d_hi));
-                        const float inv_a = 1.0f / q.x;
+                        const float s_lo = approx_sqrt(fmaxf(0.f, q.x * cu.x - det * d_lo * d_lo));
+                        const float s_hi = approx_sqrt(fmaxf(0.f, q.x * cu.x - det * d_hi * d_hi));
+                        const float inv_a = __frcp_rn(q.x);
                         const float xh = (cu.w >= d_lo && cu.w <= d_hi) ? cu.y
                                          : fmaxf((-q.y * d_lo + s_lo) * inv_a, (-q.y * d_hi + s_hi) * inv_a);
                         const float xl = (-cu.w >= d_lo && -cu.w <= d_hi) ? -cu.y
@@ -427,6 +442,7 @@ preprocess_kernel(int P,
         }
     }
     __syncthreads();
+    FGS_PT(3);
 
     // ---- features of visible Gaussians (preprocess.cu:411-417) ----
     if (tid < n_here && s_vis[tid]) {
@@ -449,6 +465,7 @@ preprocess_kernel(int P,
         conic_opacity[idx] = make_float4((-0.5f * kLog2e) * conic.x, -kLog2e * conic.y, (-0.5f * kLog2e) * conic.z, log2_opacity);
         rgb_depth[idx] = make_float4(r, g, b, depth);
     }
+    FGS_PT(4);
 }
 
 } // namespace
@@ -460,6 +477,15 @@ void host_view_proj(int width, int height, const float* pos, const float* rot, f
                     float zFar, float zNear, float* view, float* proj);
 
 } // namespace fgs
+
+#ifdef FGS_PRE_TIMING
+extern "C" int fgs_debug_pre_phase_cycles(unsigned long long* out8, int reset)
+{
+    if (cudaMemcpyFromSymbol(out8, fgs::g_pre_cycles, sizeof(unsigned long long) * 8) != cudaSuccess) return FGS_ERR_CUDA;
+    if (reset) { unsigned long long z[8] = {0}; cudaMemcpyToSymbol(fgs::g_pre_cycles, z, sizeof z); }
+    return FGS_OK;
+}
+#endif
 
 // Test hook: non-zero makes the next preprocess calls run the exact tile test on every tile of a
 // splat's bounding rectangle, as the reference does, instead of first narrowing each row's column

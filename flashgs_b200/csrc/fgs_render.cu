@@ -14,7 +14,8 @@
 // batches in flight, so that the gather of batch b+1 and the index read of batch b+2 overlap
 // the arithmetic of batch b. All lanes then read each splat from shared memory as a broadcast.
 // The exponent of a splat at pixel (x, y) is split into per-column terms (computed TX times),
-// a per-row term (TY times) and two FMAs per pixel; alpha = ex2.approx.ftz(exponent).
+// a per-row term (TY times) and two FMAs per pixel; alpha = ex2.approx.ftz(exponent). The arithmetic
+// runs on horizontal pixel pairs with the packed fp32x2 add/mul/fma instructions of sm_100.
 //
 // Stop rule, identical to the reference's (render.cu:315,394-407,486-487): splats are consumed
 // two at a time and after each pair a warp vote ends the tile once every pixel of the tile
@@ -30,7 +31,10 @@
 namespace fgs {
 namespace {
 
-constexpr int BLEND_WARPS = 4;      // tiles per block
+#ifndef FGS_BLEND_WARPS
+#define FGS_BLEND_WARPS 2
+#endif
+constexpr int BLEND_WARPS = FGS_BLEND_WARPS;   // tiles per block (one warp each); 1 lets the hardware scheduler balance tiles individually
 constexpr int BATCH = 32;           // splats per staged batch (one per lane)
 constexpr int STAGES = 2;
 
@@ -71,6 +75,15 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Two fp32 lanes in one 64-bit register: Blackwell issues add/mul/fma on such pairs as one instruction
+// (each lane rounds exactly like the scalar instruction), which halves the issue slots of the pixel math.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { f32x2 d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) { f32x2 d; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+
 // render.cu:54-57
 __device__ __forceinline__ uint8_t encode_u8(float x) { return (uint8_t)fminf(fmaxf(0.0f, x * 255.0f), 255.0f); }
 
@@ -106,17 +119,19 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
 
     const int lx = lane & 7, ly = lane >> 3;
     const int px0 = tile_x * BX + lx * TX, py0 = tile_y * BY + ly * TY;
-    float pxf[TX], pyf[TY];
+    // Pixels are handled as horizontal pairs (columns 2p and 2p+1 of the thread's block) in packed registers.
+    constexpr int PX = TX / 2;
+    f32x2 px2[PX], py2[TY];
 #pragma unroll
-    for (int j = 0; j < TX; j++) pxf[j] = (float)(px0 + j);
+    for (int p = 0; p < PX; p++) px2[p] = pack2((float)(px0 + 2 * p), (float)(px0 + 2 * p + 1));
 #pragma unroll
-    for (int i = 0; i < TY; i++) pyf[i] = (float)(py0 + i);
+    for (int i = 0; i < TY; i++) py2[i] = pack2((float)(py0 + i), (float)(py0 + i));
 
-    float T[TY][TX], Cr[TY][TX], Cg[TY][TX], Cb[TY][TX], D[TY][TX];
+    f32x2 T2[TY][PX], Cr2[TY][PX], Cg2[TY][PX], Cb2[TY][PX], D2[TY][PX];
 #pragma unroll
     for (int i = 0; i < TY; i++)
 #pragma unroll
-        for (int j = 0; j < TX; j++) { T[i][j] = 1.0f; Cr[i][j] = Cg[i][j] = Cb[i][j] = 0.0f; D[i][j] = 0.0f; }
+        for (int p = 0; p < PX; p++) { T2[i][p] = pack2(1.0f, 1.0f); Cr2[i][p] = Cg2[i][p] = Cb2[i][p] = D2[i][p] = pack2(0.0f, 0.0f); }
 
     int used = 0;
     if (n > 0) {
@@ -154,27 +169,30 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
                         const float2 xy = s.xy[k + h];
                         const float4 co = s.con[k + h];
                         const float4 rd = s.rgbd[k + h];
-                        float A[TX], B[TX];
+                        const f32x2 sx2 = pack2(xy.x, xy.x), sy2 = pack2(xy.y, xy.y);
+                        const f32x2 cx2 = pack2(co.x, co.x), cy2 = pack2(co.y, co.y), cz2 = pack2(co.z, co.z), cw2 = pack2(co.w, co.w);
+                        const f32x2 r2 = pack2(rd.x, rd.x), g2 = pack2(rd.y, rd.y), b2 = pack2(rd.z, rd.z), z2 = pack2(rd.w, rd.w);
+                        f32x2 A2[PX], B2[PX];   // per column: co.w + co.x*dx^2 and co.y*dx
 #pragma unroll
-                        for (int j = 0; j < TX; j++) {
-                            const float dx = xy.x - pxf[j];
-                            A[j] = fmaf(co.x * dx, dx, co.w);
-                            B[j] = co.y * dx;
+                        for (int p = 0; p < PX; p++) {
+                            const f32x2 dx2 = sub2(sx2, px2[p]);
+                            A2[p] = fma2(mul2(cx2, dx2), dx2, cw2);
+                            B2[p] = mul2(cy2, dx2);
                         }
 #pragma unroll
                         for (int i = 0; i < TY; i++) {
-                            const float dy = xy.y - pyf[i];
+                            const f32x2 dy2 = sub2(sy2, py2[i]);
 #pragma unroll
-                            for (int j = 0; j < TX; j++) {
-                                const float t = fmaf(co.z, dy, B[j]);
-                                const float power = fmaf(t, dy, A[j]);
-                                const float alpha = ex2_approx_ftz(power);
-                                const float aT = alpha * T[i][j];
-                                Cr[i][j] = fmaf(rd.x, aT, Cr[i][j]);
-                                Cg[i][j] = fmaf(rd.y, aT, Cg[i][j]);
-                                Cb[i][j] = fmaf(rd.z, aT, Cb[i][j]);
-                                if (EXTRA) D[i][j] = fmaf(rd.w, aT, D[i][j]);
-                                T[i][j] -= aT;
+                            for (int p = 0; p < PX; p++) {
+                                const f32x2 t2 = fma2(cz2, dy2, B2[p]);
+                                float p0, p1;
+                                unpack2(fma2(t2, dy2, A2[p]), p0, p1);
+                                const f32x2 aT2 = mul2(pack2(ex2_approx_ftz(p0), ex2_approx_ftz(p1)), T2[i][p]);
+                                Cr2[i][p] = fma2(r2, aT2, Cr2[i][p]);
+                                Cg2[i][p] = fma2(g2, aT2, Cg2[i][p]);
+                                Cb2[i][p] = fma2(b2, aT2, Cb2[i][p]);
+                                if (EXTRA) D2[i][p] = fma2(z2, aT2, D2[i][p]);
+                                T2[i][p] = sub2(T2[i][p], aT2);
                             }
                         }
                     }
@@ -183,7 +201,11 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
 #pragma unroll
                 for (int i = 0; i < TY; i++)
 #pragma unroll
-                    for (int j = 0; j < TX; j++) done = done && (T[i][j] < 0.0001f);
+                    for (int p = 0; p < PX; p++) {
+                        float t0, t1;
+                        unpack2(T2[i][p], t0, t1);
+                        done = done && (t0 < 0.0001f) && (t1 < 0.0001f);
+                    }
                 if (__all_sync(FULL_MASK, done)) { stop = true; used = b * BATCH + min(k + 2, cnt); break; }
             }
             __syncwarp();
@@ -194,6 +216,17 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
     if (EXTRA && consumed && lane == 0) consumed[tile] = used;
 
     // ---- write-out (render.cu:59-73; background-only tiles: render.cu:530-546, here bounds-checked) ----
+    float T[TY][TX], Cr[TY][TX], Cg[TY][TX], Cb[TY][TX], D[TY][TX];
+#pragma unroll
+    for (int i = 0; i < TY; i++)
+#pragma unroll
+        for (int p = 0; p < PX; p++) {
+            unpack2(T2[i][p], T[i][2 * p], T[i][2 * p + 1]);
+            unpack2(Cr2[i][p], Cr[i][2 * p], Cr[i][2 * p + 1]);
+            unpack2(Cg2[i][p], Cg[i][2 * p], Cg[i][2 * p + 1]);
+            unpack2(Cb2[i][p], Cb[i][2 * p], Cb[i][2 * p + 1]);
+            unpack2(D2[i][p], D[i][2 * p], D[i][2 * p + 1]);
+        }
     uint8_t (*so)[BX * 3] = s_out[warp];
 #pragma unroll
     for (int i = 0; i < TY; i++)

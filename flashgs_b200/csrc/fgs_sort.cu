@@ -45,6 +45,9 @@ constexpr int SORT_PART = SORT_THREADS * SORT_ITEMS;    // pairs per partition
 constexpr int RADIX_BITS = 8;
 constexpr int RADIX = 1 << RADIX_BITS;
 constexpr int MAX_PASSES = 8;
+constexpr int MAX_TILE_BITS = 16;                        // tile-bucketed path: at most 2^16 tile values
+constexpr int MAX_TILE_VALUES = 1 << MAX_TILE_BITS;
+constexpr int LOCAL_CAP = 4096;                         // longest tile list the in-block sort takes
 constexpr int HIST_THREADS = 256;
 static_assert(RADIX <= SORT_THREADS, "thread d < RADIX owns digit value d in the scans and the look-back");
 
@@ -71,7 +74,7 @@ __device__ __forceinline__ void st_relaxed(uint32_t* p, uint32_t v)
 }
 
 struct SortLayout {
-    size_t tickets_off, hist_off, status_off, alt_keys_off, alt_vals_off, total;
+    size_t tickets_off, flag_off, hist_off, status_off, seg_off, alt_keys_off, alt_vals_off, total;
     int parts;
 };
 
@@ -82,10 +85,12 @@ inline SortLayout make_layout(int64_t n)
     SortLayout L;
     if (n < 1) n = 1;
     L.parts = (int)((n + SORT_PART - 1) / SORT_PART);
-    L.tickets_off = 0;                                           // MAX_PASSES tickets (+ padding)
+    L.tickets_off = 0;                                           // MAX_PASSES tickets
+    L.flag_off = 128;                                            // "a tile is too long for the in-block sort" flag
     L.hist_off = 256;                                            // MAX_PASSES x RADIX counts
     L.status_off = L.hist_off + (size_t)MAX_PASSES * RADIX * 4;  // passes x parts x RADIX words
-    L.alt_keys_off = align_up(L.status_off + (size_t)MAX_PASSES * L.parts * RADIX * 4, 256);
+    L.seg_off = align_up(L.status_off + (size_t)MAX_PASSES * L.parts * RADIX * 4, 256);   // [first, last) per tile value
+    L.alt_keys_off = align_up(L.seg_off + (size_t)MAX_TILE_VALUES * 8, 256);
     L.alt_vals_off = align_up(L.alt_keys_off + (size_t)n * 8, 256);
     L.total = align_up(L.alt_vals_off + (size_t)n * 4, 256);
     return L;
@@ -216,8 +221,12 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
                 uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
                 int n, int num_parts, uint32_t digit_mask, int use_bulk,
                 uint32_t* __restrict__ ticket, const uint32_t* __restrict__ hist,
-                uint32_t* __restrict__ status_words, int* __restrict__ dev_status, int skip_publish_part)
+                uint32_t* __restrict__ status_words, int* __restrict__ dev_status, int skip_publish_part,
+                const int* __restrict__ run_only_if)
 {
+    // Passes of the plain six-digit sort are launched behind the tile-bucketed path and do nothing unless
+    // that path found a tile list too long for its in-block sort.
+    if (run_only_if != nullptr && *run_only_if == 0) return;
     extern __shared__ __align__(128) unsigned char s_dyn[];   // IN stage | OUT stage, each keys 8*PART | values 4*PART
     __shared__ __align__(8) uint64_t s_bar;                   // completion of the bulk copy into IN
     __shared__ uint16_t s_whist[SORT_WARPS][RADIX];           // per-warp digit counts, then exclusive warp offsets
@@ -477,6 +486,160 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
     if (tid == 0 && copy_pending) mbar_wait(&s_bar, in_parity);
 }
 
+// ---- tile-bucketed path: after the digit passes over the tile bits, every tile's pairs are contiguous ----
+// One thread per tile value: [first, one-past-last) of that tile in the tile-grouped list, by binary search.
+__global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, int tile_values, uint32_t tile_mask,
+                                int2* __restrict__ seg, int* __restrict__ too_long)
+{
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tile_values) return;
+    auto lower = [&](uint32_t v) {
+        int lo = 0, hi = n;
+        while (lo < hi) {
+            const int mid = (int)(((unsigned)lo + (unsigned)hi) >> 1);
+            if (((uint32_t)(__ldg(keys + mid) >> 32) & tile_mask) < v) lo = mid + 1; else hi = mid;
+        }
+        return lo;
+    };
+    const int first = lower((uint32_t)t);
+    const int last = (t + 1 == tile_values) ? n : lower((uint32_t)t + 1u);
+    seg[t] = make_int2(first, last);
+    if (last - first > LOCAL_CAP) atomicOr(too_long, 1);
+}
+
+// One block per tile: order the tile's pairs by (depth bits, position inside the tile's list) in shared memory,
+// then gather keys and values in that order. The position makes equal depths keep their input order, i.e. the
+// result is what a stable sort of the whole list gives.
+//
+// The order is found by a bucket sort: depths of one tile are spread fairly evenly between the tile's nearest
+// and farthest splat, so CAP/2 equal-width depth buckets receive about one element each; the elements
+// are counted, placed bucket by bucket (shared-memory atomics) and every bucket is then put in order by one
+// thread. A tile whose depths pile up in one bucket (more than LOCAL_BUCKET_LIMIT elements) is sorted by a
+// bitonic network over the whole tile instead, so the cost stays bounded for any input.
+//
+// Three instantiations cover list lengths (0,1024], (1024,2048] and (2048,LOCAL_CAP] with shared-memory
+// footprints of 16, 32 and 64 KB, so that the many short lists run with many blocks per SM; each is launched
+// over all tiles and a block whose tile belongs to another size class returns at once.
+constexpr int LOCAL_BUCKET_LIMIT = 24;
+template <int CAP> constexpr int local_smem_bytes() { return CAP * 8 + CAP * 4 + (CAP / 2 + 1) * 4 + (CAP / 2) * 4; }
+
+template <int CAP, int MIN_N, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __restrict__ vals_grouped,
+                  uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
+                  const int2* __restrict__ seg, const int* __restrict__ too_long)
+{
+    constexpr int NB = CAP / 2;   // depth buckets
+    extern __shared__ __align__(16) unsigned char s_local[];
+    uint64_t* a = reinterpret_cast<uint64_t*>(s_local);                         // [CAP] depth << 32 | position
+    uint32_t* order = reinterpret_cast<uint32_t*>(s_local + CAP * 8);     // [CAP] positions, bucket by bucket
+    uint32_t* start = order + CAP;                                        // [NB + 1]
+    uint32_t* cursor = start + NB + 1;                               // [NB]
+    __shared__ uint32_t s_min, s_max, s_wsum[THREADS / 32];
+    __shared__ int s_piled;
+
+    if (*too_long) return;
+    const int2 r = seg[blockIdx.x];
+    const int n = r.y - r.x;
+    if (n <= MIN_N || n > CAP) return;   // empty, or another size class
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) { s_min = 0xFFFFFFFFu; s_max = 0u; s_piled = 0; }
+    for (int i = tid; i < NB; i += THREADS) cursor[i] = 0;
+    __syncthreads();
+    uint32_t lo = 0xFFFFFFFFu, hi = 0u;
+    for (int i = tid; i < n; i += THREADS) {
+        const uint32_t d = (uint32_t)__ldg(keys_grouped + r.x + i);
+        a[i] = ((uint64_t)d << 32) | (uint32_t)i;
+        lo = min(lo, d);
+        hi = max(hi, d);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        lo = min(lo, __shfl_xor_sync(FULL_MASK, lo, o));
+        hi = max(hi, __shfl_xor_sync(FULL_MASK, hi, o));
+    }
+    if (lane == 0) { atomicMin(&s_min, lo); atomicMax(&s_max, hi); }
+    __syncthreads();
+    const uint32_t dmin = s_min, span = s_max - s_min;
+    bool gathered = false;
+    if (span == 0) {
+        // all depths equal: the input order is the sorted order
+        for (int i = tid; i < n; i += THREADS) order[i] = (uint32_t)i;
+        gathered = true;
+    } else {
+        // bucket of a depth: monotone in the depth (conversion and multiplication round monotonically)
+        const float scale = (float)NB / ((float)span + 1.0f);
+        auto bucket_of = [&](uint32_t d) { return min((int)((float)(d - dmin) * scale), NB - 1); };
+        for (int i = tid; i < n; i += THREADS) atomicAdd(&cursor[bucket_of((uint32_t)(a[i] >> 32))], 1u);
+        __syncthreads();
+        // exclusive scan of the bucket counts: 8 consecutive buckets per thread, then warps, then the block
+        constexpr int PER = NB / THREADS;
+        uint32_t c[PER], sum = 0, biggest = 0;
+#pragma unroll
+        for (int q = 0; q < PER; q++) { c[q] = cursor[tid * PER + q]; sum += c[q]; biggest = max(biggest, c[q]); }
+        if (biggest > LOCAL_BUCKET_LIMIT) s_piled = 1;
+        uint32_t inc = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t v = __shfl_up_sync(FULL_MASK, inc, o);
+            if (lane >= o) inc += v;
+        }
+        if (lane == 31) s_wsum[warp] = inc;
+        __syncthreads();
+        uint32_t off = inc - sum;
+        for (int w = 0; w < warp; w++) off += s_wsum[w];
+        const bool piled = s_piled != 0;
+        if (!piled) {
+#pragma unroll
+            for (int q = 0; q < PER; q++) { start[tid * PER + q] = off; cursor[tid * PER + q] = off; off += c[q]; }
+            if (tid == THREADS - 1) start[NB] = off;
+            __syncthreads();
+            for (int i = tid; i < n; i += THREADS)
+                order[atomicAdd(&cursor[bucket_of((uint32_t)(a[i] >> 32))], 1u)] = (uint32_t)i;
+            __syncthreads();
+            // every bucket in order of (depth, position): insertion sort, at most LOCAL_BUCKET_LIMIT elements
+            for (int bkt = tid; bkt < NB; bkt += THREADS) {
+                const int s0 = (int)start[bkt], s1 = (int)start[bkt + 1];
+                for (int x = s0 + 1; x < s1; x++) {
+                    const uint32_t cur = order[x];
+                    const uint64_t kc = a[cur];
+                    int y = x - 1;
+                    while (y >= s0 && a[order[y]] > kc) { order[y + 1] = order[y]; y--; }
+                    order[y + 1] = cur;
+                }
+            }
+            gathered = true;
+        }
+    }
+    __syncthreads();
+    if (!gathered) {
+        // bitonic network over the whole tile (positions beyond n hold the largest key)
+        int m = 2;
+        while (m < n) m <<= 1;
+        for (int i = n + tid; i < m; i += THREADS) a[i] = ~0ull;
+        __syncthreads();
+        for (int k = 2; k <= m; k <<= 1) {
+            for (int j = k >> 1; j > 0; j >>= 1) {
+                for (int t = tid; t < (m >> 1); t += THREADS) {
+                    const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+                    const int p = i | j;
+                    const bool up = (i & k) == 0;
+                    const uint64_t x = a[i], y = a[p];
+                    if ((x > y) == up) { a[i] = y; a[p] = x; }
+                }
+                __syncthreads();
+            }
+        }
+        for (int i = tid; i < n; i += THREADS) order[i] = (uint32_t)a[i];
+        __syncthreads();
+    }
+    for (int i = tid; i < n; i += THREADS) {
+        const uint32_t from = order[i];
+        keys_out[r.x + i] = __ldg(keys_grouped + r.x + from);
+        vals_out[r.x + i] = __ldg(vals_grouped + r.x + from);
+    }
+}
+
 __global__ void copy_pairs_kernel(const uint64_t* __restrict__ ki, const uint32_t* __restrict__ vi,
                                   uint64_t* __restrict__ ko, uint32_t* __restrict__ vo, int n)
 {
@@ -514,14 +677,21 @@ extern "C" size_t fgs_sort_temp_bytes(int64_t num_rendered)
 }
 
 namespace fgs {
-// `events`, when given, receives passes + 2 recorded events: before the histogram kernel, after it,
-// and after every onesweep pass; `passes_out` receives the pass count.
+int g_debug_plain_sort = 0;
+
+// Launch kinds reported by the profiling entry point.
+enum { LAUNCH_HISTOGRAM = 0, LAUNCH_DIGIT_PASS = 1, LAUNCH_SEGMENTS = 2, LAUNCH_LOCAL_SORT = 3, LAUNCH_STANDBY_PASS = 4 };
+constexpr int MAX_LAUNCHES = 2 * MAX_PASSES + 8;
+
+// `events`, when given, receives one recorded event before the first kernel and one after every kernel;
+// `kinds` the kind of each kernel; `num_launches` how many there were.
 static int sort_pairs_impl(int num_rendered, int width, int height, int block_x, int block_y,
                            void* temp, size_t temp_bytes,
                            const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
                            uint64_t* keys_sorted, uint32_t* values_sorted, void* stream,
-                           cudaEvent_t* events, int* passes_out)
+                           cudaEvent_t* events, int* kinds, int* num_launches)
 {
+    if (num_launches) *num_launches = 0;
     if (num_rendered < 0 || num_rendered >= (1 << 30) || width <= 0 || height <= 0 || block_x <= 0 || block_y <= 0)
         return FGS_ERR_BAD_ARG;
     if (num_rendered == 0) return FGS_OK;
@@ -538,11 +708,20 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     const int end_bit = 32 + bit_length(tiles);
     const int passes = (end_bit + RADIX_BITS - 1) / RADIX_BITS;
     if (passes > MAX_PASSES) return FGS_ERR_BAD_ARG;
+    const int tile_bits = end_bit - 32;
+    const int depth_passes = 32 / RADIX_BITS;
+    // Tile-bucketed path: digit passes over the tile bits only, then an in-block sort of every tile by depth.
+    // It needs the ticket/status slots behind the plain passes' own (passes + tile passes <= MAX_PASSES).
+    const int tile_passes = passes - depth_passes;
+    const bool bucketed = !g_debug_plain_sort && tile_bits <= MAX_TILE_BITS && tile_passes >= 1 &&
+                          passes + tile_passes <= MAX_PASSES;
 
     char* base = static_cast<char*>(temp);
     uint32_t* tickets = reinterpret_cast<uint32_t*>(base + L.tickets_off);
+    int* too_long = reinterpret_cast<int*>(base + L.flag_off);
     uint32_t* hist = reinterpret_cast<uint32_t*>(base + L.hist_off);
     uint32_t* status_words = reinterpret_cast<uint32_t*>(base + L.status_off);
+    int2* seg = reinterpret_cast<int2*>(base + L.seg_off);
     uint64_t* alt_keys = reinterpret_cast<uint64_t*>(base + L.alt_keys_off);
     uint32_t* alt_vals = reinterpret_cast<uint32_t*>(base + L.alt_vals_off);
 
@@ -557,48 +736,92 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
 #define FGS_OPT_IN(SHIFT) if (e == cudaSuccess) e = cudaFuncSetAttribute(onesweep_kernel<SHIFT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SORT_SMEM_BYTES);
         FGS_OPT_IN(0) FGS_OPT_IN(8) FGS_OPT_IN(16) FGS_OPT_IN(24) FGS_OPT_IN(32) FGS_OPT_IN(40) FGS_OPT_IN(48) FGS_OPT_IN(56)
 #undef FGS_OPT_IN
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<LOCAL_CAP, 2048, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<LOCAL_CAP>());
         if (e != cudaSuccess) return FGS_ERR_CUDA;
         smem_opt_in[dev] = true;
     }
 
-    const size_t clear_bytes = L.status_off + (size_t)passes * L.parts * RADIX * 4;
+    const int slots = passes + (bucketed ? tile_passes : 0);
+    const size_t clear_bytes = L.status_off + (size_t)slots * L.parts * RADIX * 4;
     if (cudaMemsetAsync(base, 0, clear_bytes, st) != cudaSuccess) return FGS_ERR_CUDA;
 
-    if (passes_out) *passes_out = passes;
+    int launches = 0;
+    auto mark = [&](int kind) {
+        if (events) cudaEventRecord(events[launches + 1], st);
+        if (kinds) kinds[launches] = kind;
+        launches++;
+    };
     if (events) cudaEventRecord(events[0], st);
     int hist_blocks = L.parts < 148 * 8 ? L.parts : 148 * 8;
     histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, passes, end_bit, hist);
-    if (events) cudaEventRecord(events[1], st);
+    mark(LAUNCH_HISTOGRAM);
 
-    const uint64_t* src_k = keys_unsorted;
-    const uint32_t* src_v = values_unsorted;
     const int resident = 2 * sm_count[dev];   // persistent blocks, two per SM
     const int grid_blocks = L.parts < resident ? L.parts : resident;
-    for (int p = 0; p < passes; p++) {
-        const bool to_out = ((passes - 1 - p) & 1) == 0;
-        uint64_t* dst_k = to_out ? keys_sorted : alt_keys;
-        uint32_t* dst_v = to_out ? values_sorted : alt_vals;
+    // one digit pass: digit `p` of the key, bookkeeping slot `slot`
+    auto digit_pass = [&](int p, int slot, const uint64_t* src_k, const uint32_t* src_v, uint64_t* dst_k, uint32_t* dst_v,
+                          const int* run_only_if) -> int {
         const int shift = p * RADIX_BITS;
         const int bits = (end_bit - shift) < RADIX_BITS ? (end_bit - shift) : RADIX_BITS;
         const int use_bulk = aligned16(src_k) && aligned16(src_v);
 #define FGS_PASS(SHIFT)                                                                                            \
     case SHIFT:                                                                                                    \
         onesweep_kernel<SHIFT><<<grid_blocks, PASS_THREADS, SORT_SMEM_BYTES, st>>>(                                \
-            src_k, src_v, dst_k, dst_v, n, L.parts, (1u << bits) - 1u, use_bulk, tickets + p, hist + p * RADIX,    \
-            status_words + (size_t)p * L.parts * RADIX, dev_status, g_debug_skip_publish_part);                    \
+            src_k, src_v, dst_k, dst_v, n, L.parts, (1u << bits) - 1u, use_bulk, tickets + slot, hist + p * RADIX, \
+            status_words + (size_t)slot * L.parts * RADIX, dev_status, g_debug_skip_publish_part, run_only_if);    \
         break;
         switch (shift) {
             FGS_PASS(0) FGS_PASS(8) FGS_PASS(16) FGS_PASS(24) FGS_PASS(32) FGS_PASS(40) FGS_PASS(48) FGS_PASS(56)
         default: return FGS_ERR_BAD_ARG;
         }
 #undef FGS_PASS
-        src_k = dst_k;
-        src_v = dst_v;
-        if (events) cudaEventRecord(events[2 + p], st);
+        return FGS_OK;
+    };
+
+    if (bucketed) {
+        // tile digits, least significant first; the last one leaves the tile-grouped list in the alternate buffers
+        const uint64_t* src_k = keys_unsorted;
+        const uint32_t* src_v = values_unsorted;
+        for (int i = 0; i < tile_passes; i++) {
+            const bool to_alt = ((tile_passes - 1 - i) & 1) == 0;
+            uint64_t* dst_k = to_alt ? alt_keys : keys_sorted;
+            uint32_t* dst_v = to_alt ? alt_vals : values_sorted;
+            if (digit_pass(depth_passes + i, passes + i, src_k, src_v, dst_k, dst_v, nullptr) != FGS_OK) return FGS_ERR_BAD_ARG;
+            mark(LAUNCH_DIGIT_PASS);
+            src_k = dst_k;
+            src_v = dst_v;
+        }
+        const int tile_values = 1 << tile_bits;
+        segments_kernel<<<(tile_values + 255) / 256, 256, 0, st>>>(alt_keys, n, tile_values, (uint32_t)tile_values - 1u, seg, too_long);
+        mark(LAUNCH_SEGMENTS);
+        local_sort_kernel<1024, 0, 128><<<tile_values, 128, local_smem_bytes<1024>(), st>>>(alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long);
+        mark(LAUNCH_LOCAL_SORT);
+        local_sort_kernel<2048, 1024, 256><<<tile_values, 256, local_smem_bytes<2048>(), st>>>(alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long);
+        mark(LAUNCH_LOCAL_SORT);
+        local_sort_kernel<LOCAL_CAP, 2048, 256><<<tile_values, 256, local_smem_bytes<LOCAL_CAP>(), st>>>(alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long);
+        mark(LAUNCH_LOCAL_SORT);
     }
+    // the plain sort: all digits, least significant first; behind the bucketed path it only runs if that gave up
+    {
+        const uint64_t* src_k = keys_unsorted;
+        const uint32_t* src_v = values_unsorted;
+        for (int p = 0; p < passes; p++) {
+            const bool to_out = ((passes - 1 - p) & 1) == 0;
+            uint64_t* dst_k = to_out ? keys_sorted : alt_keys;
+            uint32_t* dst_v = to_out ? values_sorted : alt_vals;
+            if (digit_pass(p, p, src_k, src_v, dst_k, dst_v, bucketed ? too_long : nullptr) != FGS_OK) return FGS_ERR_BAD_ARG;
+            mark(bucketed ? LAUNCH_STANDBY_PASS : LAUNCH_DIGIT_PASS);
+            src_k = dst_k;
+            src_v = dst_v;
+        }
+    }
+    if (num_launches) *num_launches = launches;
     return launch_status();
 }
 } // namespace fgs
+
+// Test hook: non-zero makes the next sorts skip the tile-bucketed path and run the plain digit passes only.
+extern "C" void fgs_debug_sort_plain(int on) { fgs::g_debug_plain_sort = on; }
 
 extern "C" int fgs_sort_pairs(int num_rendered, int width, int height, int block_x, int block_y,
                               void* temp, size_t temp_bytes,
@@ -606,29 +829,29 @@ extern "C" int fgs_sort_pairs(int num_rendered, int width, int height, int block
                               uint64_t* keys_sorted, uint32_t* values_sorted, void* stream)
 {
     return fgs::sort_pairs_impl(num_rendered, width, height, block_x, block_y, temp, temp_bytes, keys_unsorted,
-                                values_unsorted, keys_sorted, values_sorted, stream, nullptr, nullptr);
+                                values_unsorted, keys_sorted, values_sorted, stream, nullptr, nullptr, nullptr);
 }
 
 extern "C" int fgs_sort_pairs_profile(int num_rendered, int width, int height, int block_x, int block_y,
                                       void* temp, size_t temp_bytes,
                                       const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
                                       uint64_t* keys_sorted, uint32_t* values_sorted, void* stream,
-                                      float* launch_ms, int launch_ms_len, int* num_launches)
+                                      float* launch_ms, int* launch_kind, int capacity, int* num_launches)
 {
     using namespace fgs;
-    if (!launch_ms || !num_launches || launch_ms_len < MAX_PASSES + 1) return FGS_ERR_BAD_ARG;
-    cudaEvent_t ev[MAX_PASSES + 2];
+    if (!launch_ms || !launch_kind || !num_launches || capacity < MAX_LAUNCHES) return FGS_ERR_BAD_ARG;
+    cudaEvent_t ev[MAX_LAUNCHES + 1];
     for (auto& e : ev)
         if (cudaEventCreate(&e) != cudaSuccess) return FGS_ERR_CUDA;
-    int passes = 0;
+    int launches = 0;
     int st = sort_pairs_impl(num_rendered, width, height, block_x, block_y, temp, temp_bytes, keys_unsorted,
-                             values_unsorted, keys_sorted, values_sorted, stream, ev, &passes);
+                             values_unsorted, keys_sorted, values_sorted, stream, ev, launch_kind, &launches);
     *num_launches = 0;
-    if (st == FGS_OK && num_rendered > 0) {
+    if (st == FGS_OK && launches > 0) {
         if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) st = FGS_ERR_CUDA;
-        for (int i = 0; st == FGS_OK && i < passes + 1; i++)
+        for (int i = 0; st == FGS_OK && i < launches; i++)
             if (cudaEventElapsedTime(&launch_ms[i], ev[i], ev[i + 1]) != cudaSuccess) st = FGS_ERR_CUDA;
-        if (st == FGS_OK) *num_launches = passes + 1;
+        if (st == FGS_OK) *num_launches = launches;
     }
     for (auto& e : ev) cudaEventDestroy(e);
     return st;

@@ -117,17 +117,18 @@ int fgs_sort_pairs(int num_rendered, int width, int height, int block_x, int blo
                    uint64_t* keys_sorted, uint32_t* values_sorted, void* stream);
 
 /*
- * fgs_sort_pairs with CUDA events recorded around each of its kernel launches; waits for the
- * stream and fills launch_ms[0] (histogram kernel) and launch_ms[1..] (one onesweep pass each);
- * *num_launches receives how many entries were filled (0 when num_rendered is 0). launch_ms must
- * hold at least 9 floats. A measurement aid for benchmarks: it creates and destroys events and
- * blocks the host, so it is not for the frame loop. No counterpart in the reference.
+ * fgs_sort_pairs with CUDA events recorded around each of its kernel launches; waits for the stream and
+ * fills launch_ms[i] and launch_kind[i] for every launch i (kinds: 0 histogram, 1 digit pass, 2 tile
+ * segments, 3 in-block tile sort, 4 stand-by digit pass that returns at once unless a tile list was too
+ * long for the in-block sort); *num_launches receives the count (0 when num_rendered is 0). Both arrays
+ * must hold `capacity` >= 24 entries. A measurement aid for benchmarks: it creates and destroys events
+ * and blocks the host, so it is not for the frame loop. No counterpart in the reference.
  */
 int fgs_sort_pairs_profile(int num_rendered, int width, int height, int block_x, int block_y,
                            void* temp, size_t temp_bytes,
                            const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
                            uint64_t* keys_sorted, uint32_t* values_sorted, void* stream,
-                           float* launch_ms, int launch_ms_len, int* num_launches);
+                           float* launch_ms, int* launch_kind, int capacity, int* num_launches);
 
 /*
  * Tile ranges + front-to-back alpha blending into an 8-bit RGB image.
@@ -177,6 +178,16 @@ int fgs_render_ex(int block_x, int block_y, int num_rendered, int width, int hei
  * identifyTileRanges plus the memset before it (csrc/cuda_rasterizer/render.cu:9-31,557).
  */
 int fgs_tile_ranges(int num_rendered, int num_tiles, const uint64_t* keys_sorted, int* ranges, void* stream);
+
+/*
+ * Scene loading (host only, no GPU work). Replace loadPly_torch / computeCov3D (csrc/pybind.cpp:12-120):
+ * a binary PLY with 62 floats per vertex (position, normal, f_dc, f_rest channel-major, opacity logit,
+ * log-scale, quaternion w,x,y,z) becomes position [n,3], shs [n,48] as [coef][rgb], opacity = sigmoid,
+ * cov3d [n,6] (xx, xy, xz, yy, yz, zz). fgs_ply_vertex_count returns the header's vertex count or a negative
+ * FGS_ERR_* value; fgs_ply_load fills HOST arrays sized for that count.
+ */
+long long fgs_ply_vertex_count(const char* path);
+int fgs_ply_load(const char* path, long long n, float* position, float* shs, float* opacity, float* cov3d);
 
 #ifdef __cplusplus
 }

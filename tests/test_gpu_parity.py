@@ -302,6 +302,43 @@ def test_sort_adversarial(ops, oracle_lib):
     _sort_case(ops, oracle_lib, (rng.integers(0, 2, n, dtype=np.uint64) << np.uint64(32)) | (base & np.uint64(0xFFFFFFFF)), vals, 16, 16)
 
 
+def test_bucketed_and_plain_sort_agree(ops):
+    """The tile-bucketed path (tile digit passes + in-block depth sort) and the plain six-pass sort give the same bytes."""
+    from flashgs_b200 import _lib
+    L = _lib.load()
+    rng = np.random.default_rng(7)
+    for n, W, H in ((300000, 800, 800), (2000000, 3840, 2160), (5000, 64, 64)):
+        tiles = ((W + 15) // 16) * ((H + 15) // 16)
+        keys = (rng.integers(0, tiles, n, dtype=np.uint64) << np.uint64(32)) | (rng.integers(0, 1 << 20, n, dtype=np.uint64) << np.uint64(8))
+        ki, vi = _t(keys.view(np.int64)), _t(np.arange(n, dtype=np.int32))
+        tmp = torch.zeros(ops.get_sort_buffer_size(n), device=DEV, dtype=torch.int8)
+        outs = []
+        for plain in (0, 1):
+            ko, vo = torch.zeros_like(ki), torch.zeros_like(vi)
+            L.fgs_debug_sort_plain(plain)
+            try:
+                ops.sort_gaussian(n, W, H, 16, 16, tmp, ki, vi, ko, vo)
+                torch.cuda.synchronize()
+            finally:
+                L.fgs_debug_sort_plain(0)
+            outs.append((ko, vo))
+        assert (outs[0][0] == outs[1][0]).all() and (outs[0][1] == outs[1][1]).all()
+        tk, ti = torch.sort(ki, stable=True)
+        assert (tk == outs[0][0]).all() and (vi[ti] == outs[0][1]).all()
+    # one tile whose depths pile up at two values (the bucket sort hands over to the bitonic network), one tile
+    # with all depths equal, and a list too long for the in-block sort (the stand-by digit passes take over)
+    for n, depths in ((3000, [1, 1 << 30]), (3000, [12345]), (6000, [1, 1 << 30]), (4096, list(range(1, 4097)))):
+        keys = rng.choice(np.array(depths, dtype=np.uint64), n)
+        ki, vi = _t(keys.view(np.int64)), _t(np.arange(n, dtype=np.int32))
+        ko, vo = torch.zeros_like(ki), torch.zeros_like(vi)
+        tmp = torch.zeros(ops.get_sort_buffer_size(n), device=DEV, dtype=torch.int8)
+        ops.sort_gaussian(n, 16, 16, 16, 16, tmp, ki, vi, ko, vo)
+        torch.cuda.synchronize()
+        tk, ti = torch.sort(ki, stable=True)
+        assert (tk == ko).all() and (vi[ti] == vo).all()
+    assert ops.device_status() == 0
+
+
 def test_tile_ranges_match_oracle(ops, oracle_lib):
     from flashgs_b200 import _lib
     L = _lib.load()
