@@ -856,3 +856,46 @@ extern "C" int fgs_sort_pairs_profile(int num_rendered, int width, int height, i
     for (auto& e : ev) cudaEventDestroy(e);
     return st;
 }
+
+// ---- sorting without any caller-provided or allocated scratch ----
+// Scratch for fgs_sort_pairs_static: a fixed array inside the library's device image. Every GPU that loads the
+// library carries these bytes until the process exits, which is why the limit is modest.
+#define FGS_STATIC_SORT_MAX_PAIRS (1 << 18)
+namespace fgs {
+namespace {
+constexpr size_t static_sort_bytes()
+{
+    // the layout of make_layout(FGS_STATIC_SORT_MAX_PAIRS), spelled out so that it is a compile-time constant
+    constexpr size_t parts = (FGS_STATIC_SORT_MAX_PAIRS + SORT_PART - 1) / SORT_PART;
+    constexpr size_t status_off = 256 + (size_t)MAX_PASSES * RADIX * 4;
+    constexpr size_t seg_off = (status_off + (size_t)MAX_PASSES * parts * RADIX * 4 + 255) / 256 * 256;
+    constexpr size_t alt_keys_off = (seg_off + (size_t)MAX_TILE_VALUES * 8 + 255) / 256 * 256;
+    constexpr size_t alt_vals_off = (alt_keys_off + (size_t)FGS_STATIC_SORT_MAX_PAIRS * 8 + 255) / 256 * 256;
+    return (alt_vals_off + (size_t)FGS_STATIC_SORT_MAX_PAIRS * 4 + 255) / 256 * 256;
+}
+static __device__ __align__(256) unsigned char g_static_sort_scratch[static_sort_bytes()];
+void* g_static_sort_ptr[64];   // device address of the array, per device, resolved on first use
+} // namespace
+} // namespace fgs
+
+extern "C" int fgs_sort_static_max_pairs(void) { return FGS_STATIC_SORT_MAX_PAIRS; }
+
+extern "C" int fgs_sort_pairs_static(int num_rendered, int width, int height, int block_x, int block_y,
+                                     const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                                     uint64_t* keys_sorted, uint32_t* values_sorted, void* stream)
+{
+    using namespace fgs;
+    if (num_rendered < 0 || num_rendered > FGS_STATIC_SORT_MAX_PAIRS) return FGS_ERR_TEMP_TOO_SMALL;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FGS_ERR_CUDA;
+    if (!g_static_sort_ptr[dev]) {
+        // In host code the array's name is only a handle; the address kernels can use comes from the runtime,
+        // asked for with this device current.
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_sort_scratch) != cudaSuccess || !p) return FGS_ERR_CUDA;
+        g_static_sort_ptr[dev] = p;
+    }
+    if (make_layout(FGS_STATIC_SORT_MAX_PAIRS).total > static_sort_bytes()) return FGS_ERR_TEMP_TOO_SMALL;
+    return sort_pairs_impl(num_rendered, width, height, block_x, block_y, g_static_sort_ptr[dev], static_sort_bytes(),
+                           keys_unsorted, values_unsorted, keys_sorted, values_sorted, stream, nullptr, nullptr, nullptr);
+}

@@ -117,6 +117,24 @@ int fgs_sort_pairs(int num_rendered, int width, int height, int block_x, int blo
                    uint64_t* keys_sorted, uint32_t* values_sorted, void* stream);
 
 /*
+ * fgs_sort_pairs for callers that have no scratch buffer to give and must not allocate one: code that runs
+ * where device allocation is off limits (inside another framework's memory plan, in a callback, in a process
+ * whose allocator is owned by someone else). It has no counterpart in the reference, whose sort always takes
+ * caller scratch. The scratch lives in a fixed array inside the library (about 4.7 MB that every GPU loading
+ * the library holds until the process ends), so the call is limited to fgs_sort_static_max_pairs() = 262144
+ * pairs and returns FGS_ERR_TEMP_TOO_SMALL beyond that. Nothing is allocated or freed, by this library or by any
+ * library it calls. The first call on each device looks up the array's device address (with that device
+ * current); make that first call outside any stream capture. All calls on a device share the one array and
+ * it keeps what the previous call left (the entry point clears the parts that must start at zero), so two
+ * calls that overlap on the GPU -- different streams, or different host threads -- race: keep them ordered.
+ * Inputs, outputs and result are those of fgs_sort_pairs.
+ */
+int fgs_sort_static_max_pairs(void);
+int fgs_sort_pairs_static(int num_rendered, int width, int height, int block_x, int block_y,
+                          const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                          uint64_t* keys_sorted, uint32_t* values_sorted, void* stream);
+
+/*
  * fgs_sort_pairs with CUDA events recorded around each of its kernel launches; waits for the stream and
  * fills launch_ms[i] and launch_kind[i] for every launch i (kinds: 0 histogram, 1 digit pass, 2 tile
  * segments, 3 in-block tile sort, 4 stand-by digit pass that returns at once unless a tile list was too
