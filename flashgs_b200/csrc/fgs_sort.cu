@@ -130,7 +130,7 @@ __device__ __forceinline__ unsigned match_digit(uint32_t d)
     return peers;
 }
 
-// ---- asynchronous bulk copies (TMA, 1-D, no multicast) and their mbarrier ----
+// ---- asynchronous bulk copies (TMA, 1-D, into this block only) and their mbarrier ----
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
 {
