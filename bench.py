@@ -134,6 +134,12 @@ def tile_grid(cam, block=16):
 
 
 def main():
+    # Libraries (NCCL's version banner, for one) write to stdout; the contract is ONE JSON line there. Everything
+    # but that line is sent to stderr: fd 1 is pointed at stderr and the line goes to a saved copy of the real stdout.
+    sys.stdout.flush()
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    emit = lambda obj: (real_stdout.write(json.dumps(obj) + "\n"), real_stdout.flush())  # noqa: E731
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
@@ -161,7 +167,7 @@ def main():
     if args.impl == "port":
         if rank == 0:
             b = run_port(args, scene, cam)
-            print(json.dumps({"impl": "port", "metric": "4K frames/sec at 6M Gaussians", "value": b["value"], "unit": "frames/s",
+            emit(({"impl": "port", "metric": "4K frames/sec at 6M Gaussians", "value": b["value"], "unit": "frames/s",
                               "n_gpus": 0, "steps": 1, "warmup": 0, "ms_per_step": 1000.0 / b["value"],
                               "higher_is_better": True, "dtype": "f32", "data": "synthetic", "config": config,
                               "cpu_baseline": b}))
@@ -185,7 +191,7 @@ def main():
         from oracle import ref
         mod = ref.load()
         if mod is None:
-            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref (the reference's CUDA build) is not present"}))
+            emit({"impl": "reference", "unavailable": "oracle/_ref (the reference's CUDA build) is not present"})
             return
         ops = mod.ops
     else:
@@ -228,8 +234,8 @@ def main():
     torch.cuda.synchronize()
     tile_counts = torch.bincount(ras.gaussian_keys_sorted[:R_full] >> 32, minlength=gx * gy)
     if args.impl == "reference" and int(((tile_counts > 0) & (tile_counts < 3)).sum()) > 0:
-        print(json.dumps({"impl": "reference", "unavailable": "frame has tiles with one or two splats, for which the "
-                          "reference's blend kernel reads an uninitialised register (render.cu:268-306); not run"}))
+        emit({"impl": "reference", "unavailable": "frame has tiles with one or two splats, for which the "
+              "reference's blend kernel reads an uninitialised register (render.cu:268-306); not run"})
         return
     row_cost = tile_counts.view(gy, gx).sum(dim=1).double().cpu().tolist()
     all_rows = parallel.balanced_strip_rows(row_cost, world) if use_dist else [(0, gy)]
@@ -375,6 +381,7 @@ def main():
         host_img = torch.empty((H, W, 3), dtype=torch.int8).pin_memory()
         copy_stream = torch.cuda.Stream(device=dev)
         done = [torch.cuda.Event() for _ in range(2)]
+        keep = [None, None]
         bufs = [out_img, torch.zeros_like(out_img)] if args.impl == "ours" else [out_img, out_img]
 
         def e2e_frame(k):
@@ -388,10 +395,17 @@ def main():
                 out_img = bufs[k % 2]
             frame(rows)
             if use_dist:
+                # strips -> rank 0 over NCCL, then the copy to the host overlaps the next frame like on one GPU
+                done[k % 2].synchronize()
                 full = parallel.gather_strips(out_img[:H], all_rows, 16, H, dst=0)
                 if rank == 0:
-                    host_img.copy_(full, non_blocking=True)
-                    torch.cuda.current_stream().synchronize()
+                    keep[k % 2] = full
+                    ready = torch.cuda.Event()
+                    ready.record()
+                    with torch.cuda.stream(copy_stream):
+                        copy_stream.wait_event(ready)
+                        host_img.copy_(full, non_blocking=True)
+                        done[k % 2].record(copy_stream)
             elif args.impl == "ours":
                 ready = torch.cuda.Event()
                 ready.record()
@@ -421,7 +435,8 @@ def main():
                "h2d_bytes_per_step": 12 * 4 + 188, "d2h_bytes_per_step": H * W * 3 + 4,
                "note": "camera (12 floats) read from pinned host memory and handed to the kernel as a parameter block; "
                        "8-bit image copied to pinned host memory every frame"
-                       + ("; copy of frame k overlaps frame k+1" if args.impl == "ours" and not use_dist else "")}
+                       + ("; copy of frame k overlaps frame k+1" if args.impl == "ours" else "")
+                       + ("; strips gathered on rank 0 with one NCCL gather per frame" if use_dist else "")}
         out_img = bufs[0]
 
     status = ops.device_status() if args.impl == "ours" else 0
@@ -455,7 +470,7 @@ def main():
             line["cpu_baseline"] = {"value": value, "unit": "frames/s", "cores": 0, "kind": "reference",
                                     "sample": "the reference has no CPU path: this arm is its own CUDA build "
                                               "(compiled unmodified, -O1 as its setup.py asks) on one B200, whole frames"}
-        print(json.dumps(line))
+        emit(line)
     if use_dist:
         dist.destroy_process_group()
 
