@@ -47,7 +47,8 @@ constexpr int RADIX = 1 << RADIX_BITS;
 constexpr int MAX_PASSES = 8;
 constexpr int MAX_TILE_BITS = 16;                        // tile-bucketed path: at most 2^16 tile values
 constexpr int MAX_TILE_VALUES = 1 << MAX_TILE_BITS;
-constexpr int LOCAL_CAP = 4096;                         // longest tile list the in-block sort takes
+constexpr int LOCAL_CAP = 4096;
+constexpr int LOCAL_CLASSES = 3;                        // list-length classes of the in-block sort: <=1024, <=2048, <=LOCAL_CAP                         // longest tile list the in-block sort takes
 constexpr int HIST_THREADS = 256;
 static_assert(RADIX <= SORT_THREADS, "thread d < RADIX owns digit value d in the scans and the look-back");
 
@@ -74,7 +75,7 @@ __device__ __forceinline__ void st_relaxed(uint32_t* p, uint32_t v)
 }
 
 struct SortLayout {
-    size_t tickets_off, flag_off, hist_off, status_off, seg_off, alt_keys_off, alt_vals_off, total;
+    size_t tickets_off, flag_off, hist_off, status_off, seg_off, class_off, alt_keys_off, alt_vals_off, total;
     int parts;
 };
 
@@ -90,7 +91,8 @@ inline SortLayout make_layout(int64_t n)
     L.hist_off = 256;                                            // MAX_PASSES x RADIX counts
     L.status_off = L.hist_off + (size_t)MAX_PASSES * RADIX * 4;  // passes x parts x RADIX words
     L.seg_off = align_up(L.status_off + (size_t)MAX_PASSES * L.parts * RADIX * 4, 256);   // [first, last) per tile value
-    L.alt_keys_off = align_up(L.seg_off + (size_t)MAX_TILE_VALUES * 8, 256);
+    L.class_off = align_up(L.seg_off + (size_t)MAX_TILE_VALUES * 8, 256);                 // tile ids per length class
+    L.alt_keys_off = align_up(L.class_off + (size_t)LOCAL_CLASSES * MAX_TILE_VALUES * 4, 256);
     L.alt_vals_off = align_up(L.alt_keys_off + (size_t)n * 8, 256);
     L.total = align_up(L.alt_vals_off + (size_t)n * 4, 256);
     return L;
@@ -487,9 +489,11 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
 }
 
 // ---- tile-bucketed path: after the digit passes over the tile bits, every tile's pairs are contiguous ----
-// One thread per tile value: [first, one-past-last) of that tile in the tile-grouped list, by binary search.
+// One thread per tile value: [first, one-past-last) of that tile in the tile-grouped list, by binary search;
+// non-empty tiles are appended to the work list of their length class.
 __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, int tile_values, uint32_t tile_mask,
-                                int2* __restrict__ seg, int* __restrict__ too_long)
+                                int2* __restrict__ seg, int* __restrict__ too_long,
+                                int* __restrict__ class_count, uint32_t* __restrict__ class_tiles)
 {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= tile_values) return;
@@ -504,7 +508,12 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, int ti
     const int first = lower((uint32_t)t);
     const int last = (t + 1 == tile_values) ? n : lower((uint32_t)t + 1u);
     seg[t] = make_int2(first, last);
-    if (last - first > LOCAL_CAP) atomicOr(too_long, 1);
+    const int len = last - first;
+    if (len > LOCAL_CAP) atomicOr(too_long, 1);
+    else if (len > 0) {   // queue the tile for the in-block sort of its length class
+        const int c = len <= 1024 ? 0 : (len <= 2048 ? 1 : 2);
+        class_tiles[(size_t)c * MAX_TILE_VALUES + atomicAdd(class_count + c, 1)] = (uint32_t)t;
+    }
 }
 
 // One block per tile: order the tile's pairs by (depth bits, position inside the tile's list) in shared memory,
@@ -518,18 +527,27 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, int ti
 // bitonic network over the whole tile instead, so the cost stays bounded for any input.
 //
 // Three instantiations cover list lengths (0,1024], (1024,2048] and (2048,LOCAL_CAP] with shared-memory
-// footprints of 16, 32 and 64 KB, so that the many short lists run with many blocks per SM; each is launched
-// over all tiles and a block whose tile belongs to another size class returns at once.
-constexpr int LOCAL_BUCKET_LIMIT = 24;
-template <int CAP> constexpr int local_smem_bytes() { return CAP * 8 + CAP * 4 + (CAP / 2 + 1) * 4 + (CAP / 2) * 4; }
+// footprints that grow with the class, so that the many short lists run with many blocks per SM; each is a
+// small grid of persistent blocks that walks the work list segments_kernel built for its class (an empty
+// class costs one launch of blocks that return at once).
+#ifndef FGS_LOCAL_BUCKET_LIMIT
+#define FGS_LOCAL_BUCKET_LIMIT 64
+#endif
+#ifndef FGS_LOCAL_BUCKETS_PER_CAP_LOG2
+#define FGS_LOCAL_BUCKETS_PER_CAP_LOG2 0   // buckets = CAP * 2^this
+#endif
+constexpr int LOCAL_BUCKET_LIMIT = FGS_LOCAL_BUCKET_LIMIT;
+__host__ __device__ constexpr int local_buckets(int cap) { return FGS_LOCAL_BUCKETS_PER_CAP_LOG2 >= 0 ? cap << (FGS_LOCAL_BUCKETS_PER_CAP_LOG2 >= 0 ? FGS_LOCAL_BUCKETS_PER_CAP_LOG2 : 0) : cap >> (FGS_LOCAL_BUCKETS_PER_CAP_LOG2 < 0 ? -(FGS_LOCAL_BUCKETS_PER_CAP_LOG2) : 0); }
+template <int CAP> constexpr int local_smem_bytes() { return CAP * 8 + CAP * 4 + (local_buckets(CAP) + 1) * 4 + local_buckets(CAP) * 4; }
 
-template <int CAP, int MIN_N, int THREADS>
+template <int CAP, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __restrict__ vals_grouped,
                   uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
-                  const int2* __restrict__ seg, const int* __restrict__ too_long)
+                  const int2* __restrict__ seg, const int* __restrict__ too_long,
+                  const int* __restrict__ work_count, const uint32_t* __restrict__ work_tiles, int* __restrict__ work_ticket)
 {
-    constexpr int NB = CAP / 2;   // depth buckets
+    constexpr int NB = local_buckets(CAP);   // depth buckets
     extern __shared__ __align__(16) unsigned char s_local[];
     uint64_t* a = reinterpret_cast<uint64_t*>(s_local);                         // [CAP] depth << 32 | position
     uint32_t* order = reinterpret_cast<uint32_t*>(s_local + CAP * 8);     // [CAP] positions, bucket by bucket
@@ -539,11 +557,19 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     __shared__ int s_piled;
 
     if (*too_long) return;
-    const int2 r = seg[blockIdx.x];
-    const int n = r.y - r.x;
-    if (n <= MIN_N || n > CAP) return;   // empty, or another size class
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) { s_min = 0xFFFFFFFFu; s_max = 0u; s_piled = 0; }
+    const int work = *work_count;
+    __shared__ int s_next;
+    if (tid == 0) s_next = atomicAdd(work_ticket, 1);
+    __syncthreads();
+    for (;;) {   // persistent blocks draw tiles of the class's work list from a ticket counter
+    const int w = s_next;
+    if (w >= work) break;
+    const int2 r = seg[work_tiles[w]];
+    const int n = r.y - r.x;
+    __syncthreads();   // everyone has read s_next; the previous tile's shared memory is no longer read
+    int next_ticket = 0;
+    if (tid == 0) { s_min = 0xFFFFFFFFu; s_max = 0u; s_piled = 0; next_ticket = atomicAdd(work_ticket, 1); }
     for (int i = tid; i < NB; i += THREADS) cursor[i] = 0;
     __syncthreads();
     uint32_t lo = 0xFFFFFFFFu, hi = 0u;
@@ -587,7 +613,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
         if (lane == 31) s_wsum[warp] = inc;
         __syncthreads();
         uint32_t off = inc - sum;
-        for (int w = 0; w < warp; w++) off += s_wsum[w];
+        for (int ww = 0; ww < warp; ww++) off += s_wsum[ww];
         const bool piled = s_piled != 0;
         if (!piled) {
 #pragma unroll
@@ -637,6 +663,9 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
         const uint32_t from = order[i];
         keys_out[r.x + i] = __ldg(keys_grouped + r.x + from);
         vals_out[r.x + i] = __ldg(vals_grouped + r.x + from);
+    }
+    if (tid == 0) s_next = next_ticket;   // requested at the top of the iteration, so its latency is hidden
+    __syncthreads();
     }
 }
 
@@ -736,7 +765,8 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
 #define FGS_OPT_IN(SHIFT) if (e == cudaSuccess) e = cudaFuncSetAttribute(onesweep_kernel<SHIFT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SORT_SMEM_BYTES);
         FGS_OPT_IN(0) FGS_OPT_IN(8) FGS_OPT_IN(16) FGS_OPT_IN(24) FGS_OPT_IN(32) FGS_OPT_IN(40) FGS_OPT_IN(48) FGS_OPT_IN(56)
 #undef FGS_OPT_IN
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<LOCAL_CAP, 2048, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<LOCAL_CAP>());
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<LOCAL_CAP, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<LOCAL_CAP>());
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<2048, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<2048>());
         if (e != cudaSuccess) return FGS_ERR_CUDA;
         smem_opt_in[dev] = true;
     }
@@ -792,13 +822,21 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
             src_v = dst_v;
         }
         const int tile_values = 1 << tile_bits;
-        segments_kernel<<<(tile_values + 255) / 256, 256, 0, st>>>(alt_keys, n, tile_values, (uint32_t)tile_values - 1u, seg, too_long);
+        int* class_count = reinterpret_cast<int*>(base + L.flag_off) + 1;   // behind the flag, cleared above: three list lengths, three tickets
+        uint32_t* class_tiles = reinterpret_cast<uint32_t*>(base + L.class_off);
+        segments_kernel<<<(tile_values + 255) / 256, 256, 0, st>>>(alt_keys, n, tile_values, (uint32_t)tile_values - 1u, seg, too_long,
+                                                                  class_count, class_tiles);
         mark(LAUNCH_SEGMENTS);
-        local_sort_kernel<1024, 0, 128><<<tile_values, 128, local_smem_bytes<1024>(), st>>>(alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long);
+        const int sms = sm_count[dev];
+        auto grid_for = [&](int per_sm) { return tile_values < per_sm * sms ? tile_values : per_sm * sms; };
+        local_sort_kernel<1024, 128><<<grid_for(12), 128, local_smem_bytes<1024>(), st>>>(
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long, class_count + 0, class_tiles, class_count + 3);
         mark(LAUNCH_LOCAL_SORT);
-        local_sort_kernel<2048, 1024, 256><<<tile_values, 256, local_smem_bytes<2048>(), st>>>(alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long);
+        local_sort_kernel<2048, 256><<<grid_for(6), 256, local_smem_bytes<2048>(), st>>>(
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long, class_count + 1, class_tiles + MAX_TILE_VALUES, class_count + 4);
         mark(LAUNCH_LOCAL_SORT);
-        local_sort_kernel<LOCAL_CAP, 2048, 256><<<tile_values, 256, local_smem_bytes<LOCAL_CAP>(), st>>>(alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long);
+        local_sort_kernel<LOCAL_CAP, 256><<<grid_for(3), 256, local_smem_bytes<LOCAL_CAP>(), st>>>(
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long, class_count + 2, class_tiles + 2 * MAX_TILE_VALUES, class_count + 5);
         mark(LAUNCH_LOCAL_SORT);
     }
     // the plain sort: all digits, least significant first; behind the bucketed path it only runs if that gave up
@@ -869,7 +907,8 @@ constexpr size_t static_sort_bytes()
     constexpr size_t parts = (FGS_STATIC_SORT_MAX_PAIRS + SORT_PART - 1) / SORT_PART;
     constexpr size_t status_off = 256 + (size_t)MAX_PASSES * RADIX * 4;
     constexpr size_t seg_off = (status_off + (size_t)MAX_PASSES * parts * RADIX * 4 + 255) / 256 * 256;
-    constexpr size_t alt_keys_off = (seg_off + (size_t)MAX_TILE_VALUES * 8 + 255) / 256 * 256;
+    constexpr size_t class_off = (seg_off + (size_t)MAX_TILE_VALUES * 8 + 255) / 256 * 256;
+    constexpr size_t alt_keys_off = (class_off + (size_t)LOCAL_CLASSES * MAX_TILE_VALUES * 4 + 255) / 256 * 256;
     constexpr size_t alt_vals_off = (alt_keys_off + (size_t)FGS_STATIC_SORT_MAX_PAIRS * 8 + 255) / 256 * 256;
     return (alt_vals_off + (size_t)FGS_STATIC_SORT_MAX_PAIRS * 4 + 255) / 256 * 256;
 }
