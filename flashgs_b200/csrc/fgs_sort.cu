@@ -98,23 +98,26 @@ inline SortLayout make_layout(int64_t n)
     return L;
 }
 
-// ---- digit histograms of all passes in one read of the keys ----
+// ---- digit histograms of passes [first_pass, last_pass) in one read of the keys ----
 __global__ void __launch_bounds__(HIST_THREADS)
-histogram_kernel(const uint64_t* __restrict__ keys, int n, int passes, int end_bit, uint32_t* __restrict__ hist)
+histogram_kernel(const uint64_t* __restrict__ keys, int n, int first_pass, int last_pass, int end_bit,
+                 uint32_t* __restrict__ hist, const int* __restrict__ run_only_if)
 {
+    if (run_only_if != nullptr && *run_only_if == 0) return;
     __shared__ uint32_t s_hist[MAX_PASSES * RADIX];
-    for (int i = threadIdx.x; i < passes * RADIX; i += HIST_THREADS) s_hist[i] = 0;
+    const int np = last_pass - first_pass;
+    for (int i = threadIdx.x; i < np * RADIX; i += HIST_THREADS) s_hist[i] = 0;
     __syncthreads();
     const uint64_t live = end_bit >= 64 ? ~0ull : ((1ull << end_bit) - 1ull);
     for (int64_t i = (int64_t)blockIdx.x * HIST_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * HIST_THREADS) {
-        const uint64_t k = __ldg(keys + i) & live;
-        for (int p = 0; p < passes; p++)
+        const uint64_t k = (__ldg(keys + i) & live) >> (first_pass * RADIX_BITS);
+        for (int p = 0; p < np; p++)
             atomicAdd(&s_hist[p * RADIX + (uint32_t)((k >> (p * RADIX_BITS)) & (RADIX - 1))], 1u);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < passes * RADIX; i += HIST_THREADS) {
+    for (int i = threadIdx.x; i < np * RADIX; i += HIST_THREADS) {
         const uint32_t c = s_hist[i];
-        if (c) atomicAdd(hist + i, c);
+        if (c) atomicAdd(hist + first_pass * RADIX + i, c);
     }
 }
 
@@ -783,7 +786,8 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     };
     if (events) cudaEventRecord(events[0], st);
     int hist_blocks = L.parts < 148 * 8 ? L.parts : 148 * 8;
-    histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, passes, end_bit, hist);
+    // the bucketed path needs the tile digits' counts only; the depth digits' are counted on stand-by
+    histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, bucketed ? depth_passes : 0, passes, end_bit, hist, nullptr);
     mark(LAUNCH_HISTOGRAM);
 
     const int resident = 2 * sm_count[dev];   // persistent blocks, two per SM
@@ -840,6 +844,10 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         mark(LAUNCH_LOCAL_SORT);
     }
     // the plain sort: all digits, least significant first; behind the bucketed path it only runs if that gave up
+    if (bucketed) {
+        histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, 0, depth_passes, end_bit, hist, too_long);
+        mark(LAUNCH_STANDBY_PASS);
+    }
     {
         const uint64_t* src_k = keys_unsorted;
         const uint32_t* src_v = values_unsorted;
