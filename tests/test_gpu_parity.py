@@ -415,3 +415,71 @@ def test_rasterizer_loop_matches_stage_calls(ops):
     # drop-in module name of the reference extension
     import flash_gaussian_splatting
     assert flash_gaussian_splatting.ops.render_16x16 is ops.render_16x16
+
+
+def test_example_flow_from_ply(ops, oracle_lib, tmp_path):
+    """The call sequence of the reference's example.py (loadPly -> Scene on device -> Rasterizer.forward -> PPM),
+    through the drop-in module name, on a PLY written from raw model parameters."""
+    import flash_gaussian_splatting
+    from flashgs_b200 import ply
+    from flashgs_b200.rasterizer import Rasterizer, TorchCamera, save_ppm
+    rng = np.random.default_rng(21)
+    n = 20000
+    path = str(tmp_path / "point_cloud.ply")
+    ply.save_ply(path, rng.normal(size=(n, 3)) * 2.0, rng.normal(size=(n, 3)) * 0.5, rng.normal(size=(n, 45)) * 0.05,
+                 rng.normal(size=n) * 2.0, rng.normal(size=(n, 3)) * 0.8 - 4.0, rng.normal(size=(n, 4)))
+    num_vertex, pos, shs, opa, cov = flash_gaussian_splatting.ops.loadPly(path)
+    assert num_vertex == n
+
+    class DevScene:   # example.py:10-27
+        device = torch.device(DEV)
+    sc = DevScene()
+    sc.num_vertex, sc.position, sc.shs, sc.opacity, sc.cov3d = n, pos.to(DEV), shs.to(DEV), opa.to(DEV), cov.to(DEV)
+    cam = scenes.look_at_camera(640, 480, 9.0, 60.0, 20.0, 10.0)
+    ras = Rasterizer(sc, 1 << 21, 1 << 12, ops=flash_gaussian_splatting.ops)
+    img = ras.forward(sc, TorchCamera(cam), torch.zeros(3))
+    out = tmp_path / "view.ppm"
+    save_ppm(img, str(out))
+    assert out.read_bytes().startswith(b"P6\n640 480\n255\n") and out.stat().st_size == 15 + 640 * 480 * 3
+    host = scenes.Scene(position=pos.numpy(), shs=shs.numpy(), opacity=opa.numpy(), cov3d=cov.numpy())
+    want = oracle_lib.render_frame(host, cam, floats=False)
+    assert ras.num_rendered == int(want["counters"][3])
+    d = np.abs(img.cpu().numpy().view(np.uint8).astype(int) - want["u8"].astype(int))
+    assert d.max() <= 1 and (d > 0).mean() <= 1e-3
+
+
+def test_full_size_properties(ops):
+    """Headline workload at full size (6 M Gaussians, 3840x2160): properties that need no oracle run.
+    Sortedness and permutation of the pair list, tile ranges consistent with the keys, stand-alone stages equal to
+    the frame loop, every pixel written."""
+    from flashgs_b200.rasterizer import DeviceScene, Rasterizer, TorchCamera
+    w, sc, cams = scenes.make_workload("C4")
+    cam = cams[0]
+    ds = DeviceScene(sc, DEV)
+    ras = Rasterizer(ds, 1 << 25, 1 << 16)
+    img = torch.full((cam.height, cam.width, 3), 0x5A, device=DEV, dtype=torch.int8)
+    ras.forward(ds, TorchCamera(cam), torch.tensor([1.0, 0.0, 1.0]), out_color=img)
+    torch.cuda.synchronize()
+    R = ras.num_rendered
+    assert 25_000_000 < R < (1 << 25)
+    ku, vu = ras.gaussian_keys_unsorted[:R], ras.gaussian_values_unsorted[:R]
+    ks, vs = ras.gaussian_keys_sorted[:R], ras.gaussian_values_sorted[:R]
+    assert (ks[1:] >= ks[:-1]).all()                                     # sorted
+    assert int(ku.sum()) == int(ks.sum()) and int(vu.sum(dtype=torch.int64)) == int(vs.sum(dtype=torch.int64))
+    assert int((ku ^ (vu.long() << 20)).sum()) == int((ks ^ (vs.long() << 20)).sum())   # pairs stay together
+    gx, gy = scenes.tile_grid(cam.width, cam.height)
+    tiles = ks >> 32
+    assert int(tiles.max()) < gx * gy
+    counts = torch.bincount(tiles, minlength=gx * gy)
+    rg = ras.ranges[: gx * gy].long()
+    assert ((rg[:, 1] - rg[:, 0]) == counts).all()
+    nonempty = counts > 0
+    assert (rg[nonempty, 0] == (torch.cumsum(counts, 0) - counts)[nonempty]).all()
+    # depth bits of a key are the depth stored for its Gaussian
+    sample = torch.randint(0, R, (200000,), device=DEV)
+    assert ((ks[sample] & 0xFFFFFFFF) == ras.rgb_depth[vs[sample].long(), 3].view(torch.int32).long()).all()
+    # magenta background, dense scene: no untouched byte pattern left, image not constant
+    u8 = img.view(torch.uint8)
+    assert not bool((u8 == 0x5A).all(dim=2).any()) or int((u8 == 0x5A).all(dim=2).sum()) < 100
+    assert u8.float().std() > 5
+    assert ops.device_status() == 0
