@@ -40,6 +40,10 @@ namespace {
 
 constexpr int PRE_THREADS = 256;
 constexpr int PRE_WARPS = PRE_THREADS / 32;
+#ifndef FGS_PRE_BLOCKS_PER_SM
+#define FGS_PRE_BLOCKS_PER_SM 4
+#endif
+constexpr int PRE_BLOCKS_PER_SM = FGS_PRE_BLOCKS_PER_SM;   // persistent blocks per SM
 constexpr int PRE_K = 4;  // slot iterations per offset chunk (PRE_K * PRE_WARPS == 32 counts, one warp scans them)
 static_assert(PRE_K * PRE_WARPS == 32, "one warp scans the chunk's per-warp counts");
 
@@ -181,6 +185,16 @@ __device__ __forceinline__ void sh_color(const float (&sh)[48], const f3& p, con
 
 // Cooperative copy of `nfloats` floats starting at a 16-byte aligned global address into
 // shared memory: whole float4s first, then the ragged tail one float at a time.
+// Same copy, asynchronous (cp.async, 16 bytes per request) for the whole float4s; the ragged tail is copied
+// at once with plain loads. The caller commits and waits for the group.
+__device__ __forceinline__ void stage_floats_async(float* dst, const float* src, int nfloats)
+{
+    const int nv = nfloats >> 2;
+    for (int i = threadIdx.x; i < nv; i += PRE_THREADS)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst + 4 * i)), "l"(src + 4 * i) : "memory");
+    for (int i = (nv << 2) + threadIdx.x; i < nfloats; i += PRE_THREADS) dst[i] = __ldg(src + i);
+}
+
 template <bool VEC>
 __device__ __forceinline__ void stage_floats(float* dst, const float* src, int nfloats)
 {
@@ -204,7 +218,7 @@ __device__ unsigned long long g_pre_cycles[8];
 #endif
 
 template <bool VEC>
-__global__ void __launch_bounds__(PRE_THREADS)
+__global__ void __launch_bounds__(PRE_THREADS, PRE_BLOCKS_PER_SM)
 preprocess_kernel(int P,
                   const float* __restrict__ positions, const float* __restrict__ opacities,
                   const float* __restrict__ cov3ds, const float* __restrict__ shs,
@@ -213,9 +227,9 @@ preprocess_kernel(int P,
                   uint64_t* __restrict__ keys, uint32_t* __restrict__ values, long long capacity,
                   int* __restrict__ curr_offset, int* __restrict__ status)
 {
-    __shared__ __align__(16) float s_pos[PRE_THREADS * 3];
-    __shared__ __align__(16) float s_cov[PRE_THREADS * 6];
-    __shared__ __align__(16) float s_opa[PRE_THREADS];
+    __shared__ __align__(16) float s_pos2[2][PRE_THREADS * 3];   // two stages: the next block of Gaussians is
+    __shared__ __align__(16) float s_cov2[2][PRE_THREADS * 6];   // fetched while the current one is processed
+    __shared__ __align__(16) float s_opa2[2][PRE_THREADS];
     __shared__ float2 s_xy[PRE_THREADS];
     __shared__ float4 s_con[PRE_THREADS];      // conic.x, conic.y, conic.z, power
     __shared__ int4 s_rect[PRE_THREADS];       // min_x, min_y, width, float_bits(depth)
@@ -231,12 +245,36 @@ preprocess_kernel(int P,
 #endif
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
-    const int base = blockIdx.x * PRE_THREADS;
+    // Persistent blocks: block b takes the groups of 256 Gaussians b, b + gridDim.x, ...
+    const int num_groups = (P + PRE_THREADS - 1) / PRE_THREADS;
+    auto fetch = [&](int group, int stage) {
+        const int gb = group * PRE_THREADS;
+        const int cnt = min(PRE_THREADS, P - gb);
+        if (VEC) {
+            stage_floats_async(s_pos2[stage], positions + (size_t)gb * 3, cnt * 3);
+            stage_floats_async(s_cov2[stage], cov3ds + (size_t)gb * 6, cnt * 6);
+            stage_floats_async(s_opa2[stage], opacities + gb, cnt);
+        } else {
+            stage_floats<false>(s_pos2[stage], positions + (size_t)gb * 3, cnt * 3);
+            stage_floats<false>(s_cov2[stage], cov3ds + (size_t)gb * 6, cnt * 6);
+            stage_floats<false>(s_opa2[stage], opacities + gb, cnt);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if ((int)blockIdx.x < num_groups) fetch(blockIdx.x, 0);
+    int stage = 0;
+    for (int group = blockIdx.x; group < num_groups; group += gridDim.x, stage ^= 1) {
+    const int base = group * PRE_THREADS;
     const int n_here = min(PRE_THREADS, P - base);
-
-    stage_floats<VEC>(s_pos, positions + (size_t)base * 3, n_here * 3);
-    stage_floats<VEC>(s_cov, cov3ds + (size_t)base * 6, n_here * 6);
-    stage_floats<VEC>(s_opa, opacities + base, n_here);
+    const float* s_pos = s_pos2[stage];
+    const float* s_cov = s_cov2[stage];
+    const float* s_opa = s_opa2[stage];
+    if (group + (int)gridDim.x < num_groups) {
+        fetch(group + gridDim.x, stage ^ 1);   // the other stage was last read one iteration ago (barrier at the loop's end)
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     s_vis[tid] = 0;
     __syncthreads();
     FGS_PT(0);
@@ -466,6 +504,8 @@ preprocess_kernel(int P,
         rgb_depth[idx] = make_float4(r, g, b, depth);
     }
     FGS_PT(4);
+    __syncthreads();   // shared memory of this group is no longer read
+    }
 }
 
 } // namespace
@@ -525,7 +565,14 @@ extern "C" int fgs_preprocess_strip(int P, const float* positions, const float* 
     cam.cull_columns = g_debug_no_column_cull ? 0 : 1;
 
     const bool vec = aligned16(positions) && aligned16(shs) && aligned16(opacities) && aligned16(cov3ds);
-    const int blocks = (P + PRE_THREADS - 1) / PRE_THREADS;
+    const int groups = (P + PRE_THREADS - 1) / PRE_THREADS;
+    static int sm_count[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FGS_ERR_CUDA;
+    if (!sm_count[dev] && (cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count[dev] <= 0))
+        return FGS_ERR_CUDA;
+    const int resident = sm_count[dev] * PRE_BLOCKS_PER_SM;
+    const int blocks = groups < resident ? groups : resident;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (vec)
         preprocess_kernel<true><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,

@@ -63,12 +63,6 @@ constexpr int LOOKBACK_SLEEP_NS = FGS_LOOKBACK_SLEEP_NS;
 constexpr int SORT_SMEM_BYTES = 2 * STAGE_BYTES;        // IN stage + OUT stage
 constexpr int MBAR_MAX_POLLS = 1 << 20;                 // tries of at most ~1 us each: a bulk copy gets about a second
 
-__device__ __forceinline__ uint32_t ld_relaxed(const uint32_t* p)
-{
-    uint32_t v;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ void st_relaxed(uint32_t* p, uint32_t v)
 {
     asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -669,15 +663,6 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     }
     if (tid == 0) s_next = next_ticket;   // requested at the top of the iteration, so its latency is hidden
     __syncthreads();
-    }
-}
-
-__global__ void copy_pairs_kernel(const uint64_t* __restrict__ ki, const uint32_t* __restrict__ vi,
-                                  uint64_t* __restrict__ ko, uint32_t* __restrict__ vo, int n)
-{
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        ko[i] = ki[i];
-        vo[i] = vi[i];
     }
 }
 
