@@ -302,6 +302,23 @@ preprocess_kernel(int P,
             const float p_w = 1.0f / (hw + 0.0000001f);
             const float projx = hx * p_w, projy = hy * p_w;
 
+            if (cam.row_begin > 0 || cam.row_end < cam.grid_y) {
+                // Rendering a strip of tile rows: drop, before the covariance work, splats that cannot reach it.
+                // The vertical screen variance is at most |row y of J|^2 * trace(Sigma) + 0.3 (J's row has norm
+                // focal_y/z * sqrt(1 + (y/z)^2) with y/z clamped, the view rotation preserves norms, the largest
+                // eigenvalue of a PSD matrix is at most its trace); the bound is padded by 2 % and a whole tile,
+                // so nothing the exact rectangle would keep is dropped.
+                const float* c3 = s_cov + 6 * tid;
+                const float fz = cam.focal_y / p_view.z;
+                const float ly = 1.3f * cam.tan_fovy;
+                const float var = fz * fz * (1.0f + ly * ly) * (c3[0] + c3[3] + c3[5]) * 1.02f + 0.3f;
+                const float pw_strip = fmaxf(kLn2 * 8.0f + kLn2 * approx_lg2(opacity), 0.0f);
+                const float reach = 1.414214f * sqrtf(var * pw_strip) * 1.02f + 2.0f + (float)cam.block_y;
+                const float py_strip = ndc_to_pix(projy, cam.H);
+                // written so that a NaN (degenerate input) is never dropped here
+                if (py_strip + reach < (float)(cam.row_begin * cam.block_y) || py_strip - reach > (float)(cam.row_end * cam.block_y)) break;
+            }
+
             const f3 cov = cov2d(p_orig, cam, s_cov + 6 * tid);
             const float det = (cov.x * cov.z - cov.y * cov.y);
             const float det_inv = 1.f / det;

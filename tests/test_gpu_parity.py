@@ -483,3 +483,30 @@ def test_full_size_properties(ops):
     assert not bool((u8 == 0x5A).all(dim=2).any()) or int((u8 == 0x5A).all(dim=2).sum()) < 100
     assert u8.float().std() > 5
     assert ops.device_status() == 0
+
+
+def test_render_scene_driver(tmp_path, oracle_lib):
+    """Model directory in, PPM files out: the driver that mirrors the reference's example script."""
+    from flashgs_b200 import ply, render_scene
+    rng = np.random.default_rng(33)
+    n = 8000
+    d = tmp_path / "model"
+    (d / "point_cloud" / "iteration_30000").mkdir(parents=True)
+    ply.save_ply(str(d / "point_cloud" / "iteration_30000" / "point_cloud.ply"), rng.normal(size=(n, 3)) * 2.0,
+                 rng.normal(size=(n, 3)) * 0.5, rng.normal(size=(n, 45)) * 0.05, rng.normal(size=n) * 2.0,
+                 rng.normal(size=(n, 3)) * 0.8 - 4.0, rng.normal(size=(n, 4)))
+    cams = [scenes.look_at_camera(320, 240, 9.0, 60.0, az, 10.0, cam_id=i) for i, az in enumerate((0.0, 120.0))]
+    import json
+    (d / "cameras.json").write_text(json.dumps([render_scene.camera_to_json(c) for c in cams]))
+    times = render_scene.render_scene(str(d), test_performance=True, max_num_rendered=1 << 21, max_num_tiles=1 << 12)
+    assert set(times) == {"view000", "view001"}
+    _, pos, shs, opa, cov = ply.load_ply(str(d / "point_cloud" / "iteration_30000" / "point_cloud.ply"))
+    host = scenes.Scene(position=pos.numpy(), shs=shs.numpy(), opacity=opa.numpy(), cov3d=cov.numpy())
+    for c in cams:
+        raw = (d / "test_out" / (c.img_name + ".ppm")).read_bytes()
+        head = b"P6\n320 240\n255\n"
+        assert raw.startswith(head)
+        img = np.frombuffer(raw[len(head):], np.uint8).reshape(240, 320, 3)
+        want = oracle_lib.render_frame(host, c, floats=False)["u8"]
+        diff = np.abs(img.astype(int) - want.astype(int))
+        assert diff.max() <= 1 and (diff > 0).mean() <= 1e-3
