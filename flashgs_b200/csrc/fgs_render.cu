@@ -38,10 +38,15 @@ constexpr int BLEND_WARPS = FGS_BLEND_WARPS;   // tiles per block (one warp each
 constexpr int BATCH = 32;           // splats per staged batch (one per lane)
 constexpr int STAGES = 2;
 
-__global__ void tile_ranges_kernel(const uint64_t* __restrict__ keys, int n, int num_tiles, int2* __restrict__ ranges)
+__global__ void tile_ranges_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict__ n_dev, int num_tiles,
+                                   int2* __restrict__ ranges)
 {
     const int tile = blockIdx.x * blockDim.x + threadIdx.x;
     if (tile >= num_tiles) return;
+    if (n_dev != nullptr) {   // count produced on the device by the same frame (bounded by the buffers' capacity n)
+        const int v = *n_dev;
+        n = v < 0 ? 0 : (v < n ? v : n);
+    }
     // first index whose tile id is >= t
     auto lower = [&](uint32_t t) {
         int lo = 0, hi = n;
@@ -276,13 +281,14 @@ int launch_render(int num_rendered, int width, int height,
                   const float* points_xy, const float* rgb_depth, const float* conic_opacity,
                   const uint64_t* keys_sorted, const uint32_t* values_sorted, int* ranges, const float* bg,
                   int row_begin, int row_end,
-                  uint8_t* out_color, float* out_rgb, float* out_alpha, float* out_depth, int* consumed, cudaStream_t st)
+                  uint8_t* out_color, float* out_rgb, float* out_alpha, float* out_depth, int* consumed, cudaStream_t st,
+                  const int* n_dev = nullptr)
 {
     const int grid_x = (width + BX - 1) / BX, grid_y = (height + BY - 1) / BY;
     const int num_tiles = grid_x * grid_y;
     if (row_begin < 0) row_begin = 0;
     if (row_end < 0 || row_end > grid_y) row_end = grid_y;
-    tile_ranges_kernel<<<(num_tiles + 255) / 256, 256, 0, st>>>(keys_sorted, num_rendered, num_tiles,
+    tile_ranges_kernel<<<(num_tiles + 255) / 256, 256, 0, st>>>(keys_sorted, num_rendered, n_dev, num_tiles,
                                                                reinterpret_cast<int2*>(ranges));
     if (row_end <= row_begin) return launch_status();
     const int strip_tiles = (row_end - row_begin) * grid_x;
@@ -305,13 +311,52 @@ int launch_render(int num_rendered, int width, int height,
 }
 
 } // namespace
+
+int sort_pairs_device_count(int capacity, const int* n_dev, int width, int height, int block_x, int block_y,
+                            void* temp, size_t temp_bytes, const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                            uint64_t* keys_sorted, uint32_t* values_sorted, void* stream);
 } // namespace fgs
+
+// One whole frame without any host round trip: preprocess -> sort -> tile ranges -> blend, the pair count staying on
+// the device. See include/flashgs_b200.h.
+extern "C" int fgs_render_frame(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                                int width, int height, int block_x, int block_y,
+                                const float* cam_position, const float* cam_rotation,
+                                float focal_x, float focal_y, float zFar, float zNear, const float* bg_color,
+                                float* points_xy, float* rgb_depth, float* conic_opacity,
+                                uint64_t* keys_unsorted, uint32_t* values_unsorted,
+                                uint64_t* keys_sorted, uint32_t* values_sorted, int64_t pair_capacity,
+                                void* sort_temp, size_t sort_temp_bytes, int* ranges, int* curr_offset,
+                                int tile_row_begin, int tile_row_end, uint8_t* out_color, void* stream)
+{
+    using namespace fgs;
+    if (pair_capacity <= 0 || pair_capacity >= (1 << 30) || !curr_offset || !out_color || !bg_color || !ranges) return FGS_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(curr_offset, 0, sizeof(int), st) != cudaSuccess) return FGS_ERR_CUDA;
+    int rc = fgs_preprocess_strip(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y, cam_position, cam_rotation,
+                                  focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end, points_xy, rgb_depth, conic_opacity,
+                                  keys_unsorted, values_unsorted, pair_capacity, curr_offset, stream);
+    if (rc != FGS_OK) return rc;
+    rc = sort_pairs_device_count((int)pair_capacity, curr_offset, width, height, block_x, block_y, sort_temp, sort_temp_bytes,
+                                 keys_unsorted, values_unsorted, keys_sorted, values_sorted, stream);
+    if (rc != FGS_OK) return rc;
+#define FGS_FRAME_CASE(BX, BY)                                                                                          \
+    if (block_x == BX && block_y == BY)                                                                                 \
+        return launch_render<BX, BY>((int)pair_capacity, width, height, points_xy, rgb_depth, conic_opacity, keys_sorted, \
+                                     values_sorted, ranges, bg_color, tile_row_begin, tile_row_end, out_color, nullptr,  \
+                                     nullptr, nullptr, nullptr, st, curr_offset);
+    FGS_FRAME_CASE(16, 16)
+    FGS_FRAME_CASE(32, 16)
+    FGS_FRAME_CASE(32, 32)
+#undef FGS_FRAME_CASE
+    return FGS_ERR_BAD_ARG;
+}
 
 extern "C" int fgs_tile_ranges(int num_rendered, int num_tiles, const uint64_t* keys_sorted, int* ranges, void* stream)
 {
     if (num_rendered < 0 || num_tiles <= 0 || !ranges || (num_rendered > 0 && !keys_sorted)) return FGS_ERR_BAD_ARG;
     fgs::tile_ranges_kernel<<<(num_tiles + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        keys_sorted, num_rendered, num_tiles, reinterpret_cast<int2*>(ranges));
+        keys_sorted, num_rendered, nullptr, num_tiles, reinterpret_cast<int2*>(ranges));
     return fgs::launch_status();
 }
 

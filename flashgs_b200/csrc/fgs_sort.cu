@@ -92,12 +92,41 @@ inline SortLayout make_layout(int64_t n)
     return L;
 }
 
+// The pair count of a sort is either a host value or, for the frame entry point that never waits for the GPU,
+// a device counter written by an earlier kernel on the same stream; `n` is then the capacity that bounds it.
+__device__ __forceinline__ int device_count(int n, const int* n_dev)
+{
+    if (n_dev == nullptr) return n;
+    const int v = *n_dev;
+    return v < 0 ? 0 : (v < n ? v : n);
+}
+
+// Clears the ticket counters, flags, digit counts and the look-back words of the partitions a sort of the
+// device-side count uses (the host-count path uses a memset of exactly that region instead).
+__global__ void clear_bookkeeping_kernel(uint32_t* __restrict__ base_words, size_t head_words, uint32_t* __restrict__ status_words,
+                                         int slots, int parts_stride, int n, const int* __restrict__ n_dev)
+{
+    n = device_count(n, n_dev);
+    const int parts = (n + SORT_PART - 1) / SORT_PART;
+    const size_t per_slot = (size_t)parts * RADIX;
+    const size_t total = head_words + (size_t)slots * per_slot;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        if (i < head_words) base_words[i] = 0;
+        else {
+            const size_t j = i - head_words;
+            const size_t slot = j / per_slot;
+            status_words[slot * (size_t)parts_stride * RADIX + (j - slot * per_slot)] = 0;
+        }
+    }
+}
+
 // ---- digit histograms of passes [first_pass, last_pass) in one read of the keys ----
 __global__ void __launch_bounds__(HIST_THREADS)
-histogram_kernel(const uint64_t* __restrict__ keys, int n, int first_pass, int last_pass, int end_bit,
-                 uint32_t* __restrict__ hist, const int* __restrict__ run_only_if)
+histogram_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict__ n_dev, int first_pass, int last_pass,
+                 int end_bit, uint32_t* __restrict__ hist, const int* __restrict__ run_only_if)
 {
     if (run_only_if != nullptr && *run_only_if == 0) return;
+    n = device_count(n, n_dev);
     __shared__ uint32_t s_hist[MAX_PASSES * RADIX];
     const int np = last_pass - first_pass;
     for (int i = threadIdx.x; i < np * RADIX; i += HIST_THREADS) s_hist[i] = 0;
@@ -221,11 +250,15 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
                 int n, int num_parts, uint32_t digit_mask, int use_bulk,
                 uint32_t* __restrict__ ticket, const uint32_t* __restrict__ hist,
                 uint32_t* __restrict__ status_words, int* __restrict__ dev_status, int skip_publish_part,
-                const int* __restrict__ run_only_if)
+                const int* __restrict__ run_only_if, const int* __restrict__ n_dev)
 {
     // Passes of the plain six-digit sort are launched behind the tile-bucketed path and do nothing unless
     // that path found a tile list too long for its in-block sort.
     if (run_only_if != nullptr && *run_only_if == 0) return;
+    if (n_dev != nullptr) {
+        n = device_count(n, n_dev);
+        num_parts = (n + SORT_PART - 1) / SORT_PART;
+    }
     extern __shared__ __align__(128) unsigned char s_dyn[];   // IN stage | OUT stage, each keys 8*PART | values 4*PART
     __shared__ __align__(8) uint64_t s_bar;                   // completion of the bulk copy into IN
     __shared__ uint16_t s_whist[SORT_WARPS][RADIX];           // per-warp digit counts, then exclusive warp offsets
@@ -488,10 +521,11 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
 // ---- tile-bucketed path: after the digit passes over the tile bits, every tile's pairs are contiguous ----
 // One thread per tile value: [first, one-past-last) of that tile in the tile-grouped list, by binary search;
 // non-empty tiles are appended to the work list of their length class.
-__global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, int tile_values, uint32_t tile_mask,
-                                int2* __restrict__ seg, int* __restrict__ too_long,
+__global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict__ n_dev, int tile_values,
+                                uint32_t tile_mask, int2* __restrict__ seg, int* __restrict__ too_long,
                                 int* __restrict__ class_count, uint32_t* __restrict__ class_tiles)
 {
+    n = device_count(n, n_dev);
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= tile_values) return;
     auto lower = [&](uint32_t v) {
@@ -706,8 +740,9 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
                            void* temp, size_t temp_bytes,
                            const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
                            uint64_t* keys_sorted, uint32_t* values_sorted, void* stream,
-                           cudaEvent_t* events, int* kinds, int* num_launches)
+                           cudaEvent_t* events, int* kinds, int* num_launches, const int* n_dev = nullptr)
 {
+    // With n_dev the count lives on the device (clamped to num_rendered, which is then the buffers' capacity).
     if (num_launches) *num_launches = 0;
     if (num_rendered < 0 || num_rendered >= (1 << 30) || width <= 0 || height <= 0 || block_x <= 0 || block_y <= 0)
         return FGS_ERR_BAD_ARG;
@@ -760,8 +795,13 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     }
 
     const int slots = passes + (bucketed ? tile_passes : 0);
-    const size_t clear_bytes = L.status_off + (size_t)slots * L.parts * RADIX * 4;
-    if (cudaMemsetAsync(base, 0, clear_bytes, st) != cudaSuccess) return FGS_ERR_CUDA;
+    if (n_dev == nullptr) {
+        const size_t clear_bytes = L.status_off + (size_t)slots * L.parts * RADIX * 4;
+        if (cudaMemsetAsync(base, 0, clear_bytes, st) != cudaSuccess) return FGS_ERR_CUDA;
+    } else {
+        clear_bookkeeping_kernel<<<sm_count[dev] * 8, 256, 0, st>>>(reinterpret_cast<uint32_t*>(base), L.status_off / 4, status_words,
+                                                                slots, L.parts, n, n_dev);
+    }
 
     int launches = 0;
     auto mark = [&](int kind) {
@@ -772,7 +812,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     if (events) cudaEventRecord(events[0], st);
     int hist_blocks = L.parts < 148 * 8 ? L.parts : 148 * 8;
     // the bucketed path needs the tile digits' counts only; the depth digits' are counted on stand-by
-    histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, bucketed ? depth_passes : 0, passes, end_bit, hist, nullptr);
+    histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, n_dev, bucketed ? depth_passes : 0, passes, end_bit, hist, nullptr);
     mark(LAUNCH_HISTOGRAM);
 
     const int resident = 2 * sm_count[dev];   // persistent blocks, two per SM
@@ -787,7 +827,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     case SHIFT:                                                                                                    \
         onesweep_kernel<SHIFT><<<grid_blocks, PASS_THREADS, SORT_SMEM_BYTES, st>>>(                                \
             src_k, src_v, dst_k, dst_v, n, L.parts, (1u << bits) - 1u, use_bulk, tickets + slot, hist + p * RADIX, \
-            status_words + (size_t)slot * L.parts * RADIX, dev_status, g_debug_skip_publish_part, run_only_if);    \
+            status_words + (size_t)slot * L.parts * RADIX, dev_status, g_debug_skip_publish_part, run_only_if, n_dev); \
         break;
         switch (shift) {
             FGS_PASS(0) FGS_PASS(8) FGS_PASS(16) FGS_PASS(24) FGS_PASS(32) FGS_PASS(40) FGS_PASS(48) FGS_PASS(56)
@@ -813,7 +853,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         const int tile_values = 1 << tile_bits;
         int* class_count = reinterpret_cast<int*>(base + L.flag_off) + 1;   // behind the flag, cleared above: three list lengths, three tickets
         uint32_t* class_tiles = reinterpret_cast<uint32_t*>(base + L.class_off);
-        segments_kernel<<<(tile_values + 255) / 256, 256, 0, st>>>(alt_keys, n, tile_values, (uint32_t)tile_values - 1u, seg, too_long,
+        segments_kernel<<<(tile_values + 255) / 256, 256, 0, st>>>(alt_keys, n, n_dev, tile_values, (uint32_t)tile_values - 1u, seg, too_long,
                                                                   class_count, class_tiles);
         mark(LAUNCH_SEGMENTS);
         const int sms = sm_count[dev];
@@ -830,7 +870,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     }
     // the plain sort: all digits, least significant first; behind the bucketed path it only runs if that gave up
     if (bucketed) {
-        histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, 0, depth_passes, end_bit, hist, too_long);
+        histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, n_dev, 0, depth_passes, end_bit, hist, too_long);
         mark(LAUNCH_STANDBY_PASS);
     }
     {
@@ -848,6 +888,18 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     }
     if (num_launches) *num_launches = launches;
     return launch_status();
+}
+} // namespace fgs
+
+namespace fgs {
+// Sort whose pair count is the device counter *n_dev (at most `capacity`); used by the frame entry point.
+int sort_pairs_device_count(int capacity, const int* n_dev, int width, int height, int block_x, int block_y,
+                            void* temp, size_t temp_bytes, const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                            uint64_t* keys_sorted, uint32_t* values_sorted, void* stream)
+{
+    if (!n_dev || capacity <= 0) return FGS_ERR_BAD_ARG;
+    return sort_pairs_impl(capacity, width, height, block_x, block_y, temp, temp_bytes, keys_unsorted, values_unsorted,
+                           keys_sorted, values_sorted, stream, nullptr, nullptr, nullptr, n_dev);
 }
 } // namespace fgs
 

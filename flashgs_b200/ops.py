@@ -192,6 +192,45 @@ def render_ex(block_x, block_y, num_rendered, width, height, points_xy, rgb_dept
     _lib.check("render_ex", st)
 
 
+def render_frame(orig_points, shs, opacities, cov3Ds, width, height, block_x, block_y,
+                 position, rotation, focal_x, focal_y, zFar, zNear, bg_color,
+                 points_xy, rgb_depth, conic_opacity,
+                 gaussian_keys_unsorted, gaussian_values_unsorted, gaussian_keys_sorted, gaussian_values_sorted,
+                 list_sorting_space, ranges, curr_offset, out_color,
+                 tile_row_begin: int = 0, tile_row_end: int = -1) -> None:
+    """One frame in one call with no host round trip (no reference counterpart): what ``preprocess``,
+    ``sort_gaussian`` and ``render_*`` do in sequence, the pair count staying in ``curr_offset`` on the device.
+    Read ``curr_offset`` afterwards if the count is wanted; an overflow of the pair buffers shows in ``device_status``."""
+    f32 = torch.float32
+    pos = _host(position, "position", 3)
+    rot = _host(rotation, "rotation", 9)
+    bg = _host(bg_color, "bg_color", 3)
+    ku = _out(gaussian_keys_unsorted, "gaussian_keys_unsorted", torch.int64)
+    vu = _out(gaussian_values_unsorted, "gaussian_values_unsorted", torch.int32)
+    ks = _out(gaussian_keys_sorted, "gaussian_keys_sorted", torch.int64)
+    vs = _out(gaussian_values_sorted, "gaussian_values_sorted", torch.int32)
+    cap = min(int(ku.numel()), int(vu.numel()), int(ks.numel()), int(vs.numel()))
+    tmp = list_sorting_space
+    if not tmp.is_cuda or not tmp.is_contiguous():
+        raise RuntimeError("list_sorting_space must be a contiguous CUDA tensor")
+    if not out_color.is_cuda or not out_color.is_contiguous() or out_color.element_size() != 1:
+        raise RuntimeError("out_color must be a contiguous CUDA int8/uint8 tensor")
+    if out_color.numel() < int(width) * int(height) * 3:
+        raise RuntimeError("out_color is smaller than height*width*3")
+    op = _in(opacities, "opacities", f32)
+    st = _L.fgs_render_frame(int(op.size(0)), _in(orig_points, "orig_points", f32).data_ptr(), _in(shs, "shs", f32).data_ptr(),
+                             op.data_ptr(), _in(cov3Ds, "cov3Ds", f32).data_ptr(),
+                             int(width), int(height), int(block_x), int(block_y), pos.data_ptr(), rot.data_ptr(),
+                             float(focal_x), float(focal_y), float(zFar), float(zNear), bg.data_ptr(),
+                             _out(points_xy, "points_xy", f32).data_ptr(), _out(rgb_depth, "rgb_depth", f32).data_ptr(),
+                             _out(conic_opacity, "conic_opacity", f32).data_ptr(),
+                             ku.data_ptr(), vu.data_ptr(), ks.data_ptr(), vs.data_ptr(), cap,
+                             tmp.data_ptr(), tmp.numel() * tmp.element_size(),
+                             _out(ranges, "ranges", torch.int32).data_ptr(), _out(curr_offset, "curr_offset", torch.int32).data_ptr(),
+                             int(tile_row_begin), int(tile_row_end), out_color.data_ptr(), _stream())
+    _lib.check("render_frame", st)
+
+
 def device_status(reset: bool = True) -> int:
     """OR of the error bits raised by kernels on the current device since the last reset (synchronises)."""
     return int(_L.fgs_device_status(1 if reset else 0, _stream()))

@@ -101,6 +101,23 @@ class Rasterizer:
         return out_color
 
 
+    def forward_fused(self, scene: DeviceScene, camera, bg_color, out_color=None, rows=None):
+        """One frame through the single-call entry point: nothing waits for the GPU, the pair count stays in
+        ``self.curr_offset`` (read it later if needed). Same image as ``forward``."""
+        if out_color is None:
+            out_color = torch.zeros((camera.height, camera.width, 3), device=scene.device, dtype=torch.int8)
+        r = rows or (0, -1)
+        self.ops.render_frame(scene.position, scene.shs, scene.opacity, scene.cov3d,
+                              camera.width, camera.height, self.block[0], self.block[1],
+                              camera.position, camera.rotation, camera.focal_x, camera.focal_y, camera.zFar, camera.zNear,
+                              bg_color, self.points_xy, self.rgb_depth, self.conic_opacity,
+                              self.gaussian_keys_unsorted, self.gaussian_values_unsorted,
+                              self.gaussian_keys_sorted, self.gaussian_values_sorted,
+                              self.list_sorting_space, self.ranges, self.curr_offset, out_color,
+                              tile_row_begin=r[0], tile_row_end=r[1])
+        return out_color
+
+
 def strip_rows(grid_y: int, world_size: int, rank: int):
     """Tile rows [begin, end) of ``rank`` when ``grid_y`` rows are dealt out as evenly as possible."""
     base, rem = divmod(grid_y, world_size)

@@ -192,6 +192,26 @@ int fgs_render_ex(int block_x, int block_y, int num_rendered, int width, int hei
                   void* stream);
 
 /*
+ * One whole frame in a single call that never waits for the GPU: zero the pair counter, preprocess (optionally a
+ * strip of tile rows), sort, tile ranges, blend. The pair count stays on the device (curr_offset), so there is no
+ * host read-back between the stages as the reference's operator signatures force (example.py:79 reads the
+ * counter because csrc/ops.h:41,49 take it as a host int); the caller may read curr_offset afterwards, at its
+ * own pace, to learn the count. All buffers as in the per-stage entry points; pair_capacity is the length of the
+ * four pair buffers and sort_temp must hold fgs_sort_temp_bytes(pair_capacity). If the frame produces more
+ * pairs than pair_capacity the surplus is dropped, the image is built from the pairs that fit and
+ * FGS_ERR_PAIR_OVERFLOW is raised in the device status word. No counterpart in the reference.
+ */
+int fgs_render_frame(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                     int width, int height, int block_x, int block_y,
+                     const float* cam_position, const float* cam_rotation,
+                     float focal_x, float focal_y, float zFar, float zNear, const float* bg_color,
+                     float* points_xy, float* rgb_depth, float* conic_opacity,
+                     uint64_t* keys_unsorted, uint32_t* values_unsorted,
+                     uint64_t* keys_sorted, uint32_t* values_sorted, int64_t pair_capacity,
+                     void* sort_temp, size_t sort_temp_bytes, int* ranges, int* curr_offset,
+                     int tile_row_begin, int tile_row_end, uint8_t* out_color, void* stream);
+
+/*
  * Tile ranges only (the first half of the render entry points). Replaces
  * identifyTileRanges plus the memset before it (csrc/cuda_rasterizer/render.cu:9-31,557).
  */

@@ -510,3 +510,46 @@ def test_render_scene_driver(tmp_path, oracle_lib):
         want = oracle_lib.render_frame(host, c, floats=False)["u8"]
         diff = np.abs(img.astype(int) - want.astype(int))
         assert diff.max() <= 1 and (diff > 0).mean() <= 1e-3
+
+
+def test_fused_frame_equals_stage_calls(ops, oracle_lib):
+    """fgs_render_frame (no host read-back, device-side pair count) against the three stage calls."""
+    from flashgs_b200 import _lib
+    from flashgs_b200.rasterizer import DeviceScene, Rasterizer, TorchCamera
+    for name, n, block in (("C1", 60000, (16, 16)), ("C4", 150000, (16, 16)), ("C1", 30000, (32, 32))):
+        w = scenes.WORKLOADS[name]
+        sc = scenes.make_scene(n, w.clusters, w.log_scale, seed=4)
+        cam = scenes.look_at_camera(960, 544, w.radius, w.hfov_deg, w.azimuth_deg, w.elevation_deg)
+        ds = DeviceScene(sc, DEV)
+        tc = TorchCamera(cam)
+        bg = torch.tensor([0.1, 0.2, 0.3])
+        ras = Rasterizer(ds, 1 << 22, 1 << 14, block=block)
+        a = ras.forward(ds, tc, bg).cpu().numpy().view(np.uint8)
+        R = ras.num_rendered
+        ks_a = ras.gaussian_keys_sorted[:R].clone()
+        vs_a = ras.gaussian_values_sorted[:R].clone()
+        ras.gaussian_keys_sorted.zero_(); ras.gaussian_values_sorted.zero_()
+        b = ras.forward_fused(ds, tc, bg).cpu().numpy().view(np.uint8)
+        assert int(ras.curr_offset.cpu()[0]) == R
+        assert (ras.gaussian_keys_sorted[:R] == ks_a).all()
+        assert (canonical_sorted_values(ks_a.cpu().numpy().view(np.uint64), vs_a.cpu().numpy().view(np.uint32)) ==
+                canonical_sorted_values(ras.gaussian_keys_sorted[:R].cpu().numpy().view(np.uint64),
+                                        ras.gaussian_values_sorted[:R].cpu().numpy().view(np.uint32))).all()
+        d = np.abs(a.astype(int) - b.astype(int))
+        assert d.max() <= 1 and (d > 0).mean() <= 1e-5
+        # a strip through the fused call
+        gy = scenes.tile_grid(cam.width, cam.height, *block)[1]
+        rows = (gy // 3, 2 * gy // 3)
+        c = ras.forward_fused(ds, tc, bg, rows=rows).cpu().numpy().view(np.uint8)
+        y0, y1 = rows[0] * block[1], min(cam.height, rows[1] * block[1])
+        d = np.abs(a[y0:y1].astype(int) - c[y0:y1].astype(int))
+        assert d.max() <= 1 and (d > 0).mean() <= 1e-5
+        assert ops.device_status() == 0
+    # pair buffers too small: the call still completes, the overflow is reported, the context stays usable
+    small = Rasterizer(ds, 4096, 1 << 14, block=(32, 32))
+    small.list_sorting_space = torch.zeros(ops.get_sort_buffer_size(4096), device=DEV, dtype=torch.int8)
+    small.forward_fused(ds, tc, bg)
+    torch.cuda.synchronize()
+    assert int(small.curr_offset.cpu()[0]) > 4096
+    assert ops.device_status() & _lib.ERR_PAIR_OVERFLOW
+    assert ops.device_status() == 0
