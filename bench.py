@@ -315,6 +315,38 @@ def main():
     ms_per_step = total_ms / K
     value = 1000.0 / ms_per_step
 
+    # ---- the single-call frame (no host read-back of the pair count), plain launches and as a CUDA graph ----
+    fused = None
+    if args.impl == "ours":
+        def timed(fn):
+            for _ in range(args.warmup):
+                fn()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(K):
+                fn()
+            b.record()
+            barrier()
+            return max_over_ranks(a.elapsed_time(b)) / K
+        fused_ms = timed(lambda: ras.forward_fused(ds, tc, bg, out_color=out_img, rows=rows))
+        fused = {"ms_per_step": fused_ms, "value": 1000.0 / fused_ms, "unit": "frames/s",
+                 "note": "fgs_render_frame: whole frame in one C-ABI call, pair count stays on the device"}
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                ras.forward_fused(ds, tc, bg, out_color=out_img, rows=rows)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                ras.forward_fused(ds, tc, bg, out_color=out_img, rows=rows)
+            graph_ms = timed(graph.replay)
+            fused["graph_ms_per_step"] = graph_ms
+            fused["graph_value"] = 1000.0 / graph_ms
+        except Exception as exc:
+            fused["graph_error"] = repr(exc)[:200]
+
     # ---- per-launch times of the sort (its passes are separate launches inside one op) ----
     peak, peak_src = measured_peaks()
     stages = {}
@@ -461,6 +493,7 @@ def main():
             "device_status": status,
         }
         if args.impl == "ours":
+            line["fused_frame"] = fused
             line["roofline"] = roofline
             line["stages"] = stages
             line["cpu_baseline"] = cpu_baseline

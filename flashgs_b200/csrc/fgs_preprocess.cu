@@ -589,7 +589,12 @@ extern "C" int fgs_preprocess_strip(int P, const float* positions, const float* 
     if (!sm_count[dev] && (cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count[dev] <= 0))
         return FGS_ERR_CUDA;
     const int resident = sm_count[dev] * PRE_BLOCKS_PER_SM;
-    const int blocks = groups < resident ? groups : resident;
+#ifndef FGS_PRE_PERSISTENT_MODE
+#define FGS_PRE_PERSISTENT_MODE 0   // 0: one block per group of 256 Gaussians; 1: persistent blocks always; 2: persistent for strips only
+#endif
+    const bool strip = cam.row_begin > 0 || cam.row_end < cam.grid_y;
+    const bool persistent = FGS_PRE_PERSISTENT_MODE == 1 || (FGS_PRE_PERSISTENT_MODE == 2 && strip);
+    const int blocks = (!persistent || groups < resident) ? groups : resident;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (vec)
         preprocess_kernel<true><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,

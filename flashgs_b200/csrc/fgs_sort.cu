@@ -562,7 +562,7 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
 // small grid of persistent blocks that walks the work list segments_kernel built for its class (an empty
 // class costs one launch of blocks that return at once).
 #ifndef FGS_LOCAL_BUCKET_LIMIT
-#define FGS_LOCAL_BUCKET_LIMIT 64
+#define FGS_LOCAL_BUCKET_LIMIT 192
 #endif
 #ifndef FGS_LOCAL_BUCKETS_PER_CAP_LOG2
 #define FGS_LOCAL_BUCKETS_PER_CAP_LOG2 0   // buckets = CAP * 2^this
@@ -570,6 +570,13 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
 constexpr int LOCAL_BUCKET_LIMIT = FGS_LOCAL_BUCKET_LIMIT;
 __host__ __device__ constexpr int local_buckets(int cap) { return FGS_LOCAL_BUCKETS_PER_CAP_LOG2 >= 0 ? cap << (FGS_LOCAL_BUCKETS_PER_CAP_LOG2 >= 0 ? FGS_LOCAL_BUCKETS_PER_CAP_LOG2 : 0) : cap >> (FGS_LOCAL_BUCKETS_PER_CAP_LOG2 < 0 ? -(FGS_LOCAL_BUCKETS_PER_CAP_LOG2) : 0); }
 template <int CAP> constexpr int local_smem_bytes() { return CAP * 8 + CAP * 4 + (local_buckets(CAP) + 1) * 4 + local_buckets(CAP) * 4; }
+
+#ifdef FGS_SORT_TIMING
+__device__ unsigned long long g_local_cycles[8];
+#define FGS_LT(i) do { if (tid == 0) { const long long now_ = clock64(); atomicAdd(&g_local_cycles[i], (unsigned long long)(now_ - lt_prev_)); lt_prev_ = now_; } } while (0)
+#else
+#define FGS_LT(i) do { } while (0)
+#endif
 
 template <int CAP, int THREADS>
 __global__ void __launch_bounds__(THREADS)
@@ -589,6 +596,9 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
 
     if (*too_long) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#ifdef FGS_SORT_TIMING
+    long long lt_prev_ = clock64();
+#endif
     const int work = *work_count;
     __shared__ int s_next;
     if (tid == 0) s_next = atomicAdd(work_ticket, 1);
@@ -603,6 +613,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     if (tid == 0) { s_min = 0xFFFFFFFFu; s_max = 0u; s_piled = 0; next_ticket = atomicAdd(work_ticket, 1); }
     for (int i = tid; i < NB; i += THREADS) cursor[i] = 0;
     __syncthreads();
+    FGS_LT(0);
     uint32_t lo = 0xFFFFFFFFu, hi = 0u;
     for (int i = tid; i < n; i += THREADS) {
         const uint32_t d = (uint32_t)__ldg(keys_grouped + r.x + i);
@@ -617,6 +628,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     }
     if (lane == 0) { atomicMin(&s_min, lo); atomicMax(&s_max, hi); }
     __syncthreads();
+    FGS_LT(1);
     const uint32_t dmin = s_min, span = s_max - s_min;
     bool gathered = false;
     if (span == 0) {
@@ -629,6 +641,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
         auto bucket_of = [&](uint32_t d) { return min((int)((float)(d - dmin) * scale), NB - 1); };
         for (int i = tid; i < n; i += THREADS) atomicAdd(&cursor[bucket_of((uint32_t)(a[i] >> 32))], 1u);
         __syncthreads();
+        FGS_LT(2);
         // exclusive scan of the bucket counts: 8 consecutive buckets per thread, then warps, then the block
         constexpr int PER = NB / THREADS;
         uint32_t c[PER], sum = 0, biggest = 0;
@@ -651,20 +664,38 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
             for (int q = 0; q < PER; q++) { start[tid * PER + q] = off; cursor[tid * PER + q] = off; off += c[q]; }
             if (tid == THREADS - 1) start[NB] = off;
             __syncthreads();
+            FGS_LT(3);
             for (int i = tid; i < n; i += THREADS)
                 order[atomicAdd(&cursor[bucket_of((uint32_t)(a[i] >> 32))], 1u)] = (uint32_t)i;
             __syncthreads();
-            // every bucket in order of (depth, position): insertion sort, at most LOCAL_BUCKET_LIMIT elements
-            for (int bkt = tid; bkt < NB; bkt += THREADS) {
-                const int s0 = (int)start[bkt], s1 = (int)start[bkt + 1];
-                for (int x = s0 + 1; x < s1; x++) {
+            FGS_LT(4);
+            // every bucket in order of (depth, position): one thread per ELEMENT counts the smaller keys of its
+            // bucket (keys are unique), so a bucket of L elements costs L steps on L threads, not L^2 on one
+            uint32_t* final_pos = cursor;   // the cursors are no longer needed; NB >= n entries
+            uint32_t mine[(CAP + THREADS - 1) / THREADS], where[(CAP + THREADS - 1) / THREADS];
+#pragma unroll
+            for (int q = 0; q < (CAP + THREADS - 1) / THREADS; q++) {
+                const int x = tid + q * THREADS;
+                if (x < n) {
                     const uint32_t cur = order[x];
                     const uint64_t kc = a[cur];
-                    int y = x - 1;
-                    while (y >= s0 && a[order[y]] > kc) { order[y + 1] = order[y]; y--; }
-                    order[y + 1] = cur;
+                    const int bkt = bucket_of((uint32_t)(kc >> 32));
+                    const int s0 = (int)start[bkt], s1 = (int)start[bkt + 1];
+                    int rank = 0;
+                    for (int y = s0; y < s1; y++) rank += a[order[y]] < kc;
+                    mine[q] = cur;
+                    where[q] = (uint32_t)(s0 + rank);
                 }
             }
+            __syncthreads();   // all reads of order[] done
+#pragma unroll
+            for (int q = 0; q < (CAP + THREADS - 1) / THREADS; q++) {
+                const int x = tid + q * THREADS;
+                if (x < n) final_pos[where[q]] = mine[q];
+            }
+            __syncthreads();
+            for (int i = tid; i < n; i += THREADS) order[i] = final_pos[i];
+            FGS_LT(5);
             gathered = true;
         }
     }
@@ -697,6 +728,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     }
     if (tid == 0) s_next = next_ticket;   // requested at the top of the iteration, so its latency is hidden
     __syncthreads();
+    FGS_LT(6);
     }
 }
 
@@ -709,6 +741,12 @@ int g_debug_skip_publish_part = -1;
 } // namespace fgs
 
 #ifdef FGS_SORT_TIMING
+extern "C" int fgs_debug_local_phase_cycles(unsigned long long* out8, int reset)
+{
+    if (cudaMemcpyFromSymbol(out8, fgs::g_local_cycles, sizeof(unsigned long long) * 8) != cudaSuccess) return FGS_ERR_CUDA;
+    if (reset) { unsigned long long z[8] = {0}; cudaMemcpyToSymbol(fgs::g_local_cycles, z, sizeof z); }
+    return FGS_OK;
+}
 extern "C" int fgs_debug_sort_phase_cycles(unsigned long long* out8, int reset)
 {
     if (cudaMemcpyFromSymbol(out8, fgs::g_phase_cycles, sizeof(unsigned long long) * 8) != cudaSuccess) return FGS_ERR_CUDA;
