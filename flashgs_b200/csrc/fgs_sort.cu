@@ -569,7 +569,7 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
 #endif
 constexpr int LOCAL_BUCKET_LIMIT = FGS_LOCAL_BUCKET_LIMIT;
 __host__ __device__ constexpr int local_buckets(int cap) { return FGS_LOCAL_BUCKETS_PER_CAP_LOG2 >= 0 ? cap << (FGS_LOCAL_BUCKETS_PER_CAP_LOG2 >= 0 ? FGS_LOCAL_BUCKETS_PER_CAP_LOG2 : 0) : cap >> (FGS_LOCAL_BUCKETS_PER_CAP_LOG2 < 0 ? -(FGS_LOCAL_BUCKETS_PER_CAP_LOG2) : 0); }
-template <int CAP> constexpr int local_smem_bytes() { return CAP * 8 + CAP * 4 + (local_buckets(CAP) + 1) * 4 + local_buckets(CAP) * 4; }
+template <int CAP> constexpr int local_smem_bytes() { return CAP * 8 + CAP * 8 + (local_buckets(CAP) + 1) * 4 + local_buckets(CAP) * 4; }
 
 #ifdef FGS_SORT_TIMING
 __device__ unsigned long long g_local_cycles[8];
@@ -588,8 +588,8 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     constexpr int NB = local_buckets(CAP);   // depth buckets
     extern __shared__ __align__(16) unsigned char s_local[];
     uint64_t* a = reinterpret_cast<uint64_t*>(s_local);                         // [CAP] depth << 32 | position
-    uint32_t* order = reinterpret_cast<uint32_t*>(s_local + CAP * 8);     // [CAP] positions, bucket by bucket
-    uint32_t* start = order + CAP;                                        // [NB + 1]
+    uint64_t* bk = reinterpret_cast<uint64_t*>(s_local + CAP * 8);              // [CAP] the same keys, bucket by bucket
+    uint32_t* start = reinterpret_cast<uint32_t*>(s_local + CAP * 16);          // [NB + 1]
     uint32_t* cursor = start + NB + 1;                               // [NB]
     __shared__ uint32_t s_min, s_max, s_wsum[THREADS / 32];
     __shared__ int s_piled;
@@ -632,8 +632,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     const uint32_t dmin = s_min, span = s_max - s_min;
     bool gathered = false;
     if (span == 0) {
-        // all depths equal: the input order is the sorted order
-        for (int i = tid; i < n; i += THREADS) order[i] = (uint32_t)i;
+        // all depths equal: the input order is the sorted order (a[] already is in it)
         gathered = true;
     } else {
         // bucket of a depth: monotone in the depth (conversion and multiplication round monotonically)
@@ -665,36 +664,23 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
             if (tid == THREADS - 1) start[NB] = off;
             __syncthreads();
             FGS_LT(3);
-            for (int i = tid; i < n; i += THREADS)
-                order[atomicAdd(&cursor[bucket_of((uint32_t)(a[i] >> 32))], 1u)] = (uint32_t)i;
+            for (int i = tid; i < n; i += THREADS) {
+                const uint64_t k = a[i];
+                bk[atomicAdd(&cursor[bucket_of((uint32_t)(k >> 32))], 1u)] = k;
+            }
             __syncthreads();
             FGS_LT(4);
             // every bucket in order of (depth, position): one thread per ELEMENT counts the smaller keys of its
-            // bucket (keys are unique), so a bucket of L elements costs L steps on L threads, not L^2 on one
-            uint32_t* final_pos = cursor;   // the cursors are no longer needed; NB >= n entries
-            uint32_t mine[(CAP + THREADS - 1) / THREADS], where[(CAP + THREADS - 1) / THREADS];
-#pragma unroll
-            for (int q = 0; q < (CAP + THREADS - 1) / THREADS; q++) {
-                const int x = tid + q * THREADS;
-                if (x < n) {
-                    const uint32_t cur = order[x];
-                    const uint64_t kc = a[cur];
-                    const int bkt = bucket_of((uint32_t)(kc >> 32));
-                    const int s0 = (int)start[bkt], s1 = (int)start[bkt + 1];
-                    int rank = 0;
-                    for (int y = s0; y < s1; y++) rank += a[order[y]] < kc;
-                    mine[q] = cur;
-                    where[q] = (uint32_t)(s0 + rank);
-                }
+            // bucket (keys are unique), so a bucket of L elements costs L steps on L threads, not L^2 on one;
+            // the element then goes to its final place in a[] (whose load-order contents are no longer needed)
+            for (int x = tid; x < n; x += THREADS) {
+                const uint64_t kc = bk[x];
+                const int bkt = bucket_of((uint32_t)(kc >> 32));
+                const int s0 = (int)start[bkt], s1 = (int)start[bkt + 1];
+                int rank = 0;
+                for (int y = s0; y < s1; y++) rank += bk[y] < kc;
+                a[s0 + rank] = kc;
             }
-            __syncthreads();   // all reads of order[] done
-#pragma unroll
-            for (int q = 0; q < (CAP + THREADS - 1) / THREADS; q++) {
-                const int x = tid + q * THREADS;
-                if (x < n) final_pos[where[q]] = mine[q];
-            }
-            __syncthreads();
-            for (int i = tid; i < n; i += THREADS) order[i] = final_pos[i];
             FGS_LT(5);
             gathered = true;
         }
@@ -718,11 +704,10 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
                 __syncthreads();
             }
         }
-        for (int i = tid; i < n; i += THREADS) order[i] = (uint32_t)a[i];
-        __syncthreads();
     }
+    __syncthreads();
     for (int i = tid; i < n; i += THREADS) {
-        const uint32_t from = order[i];
+        const uint32_t from = (uint32_t)a[i];   // position of the i-th smallest key in the tile's list
         keys_out[r.x + i] = __ldg(keys_grouped + r.x + from);
         vals_out[r.x + i] = __ldg(vals_grouped + r.x + from);
     }
