@@ -614,12 +614,19 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     for (int i = tid; i < NB; i += THREADS) cursor[i] = 0;
     __syncthreads();
     FGS_LT(0);
-    uint32_t lo = 0xFFFFFFFFu, hi = 0u;
-    for (int i = tid; i < n; i += THREADS) {
-        const uint32_t d = (uint32_t)__ldg(keys_grouped + r.x + i);
-        a[i] = ((uint64_t)d << 32) | (uint32_t)i;
-        lo = min(lo, d);
-        hi = max(hi, d);
+    // depths of this thread's elements (positions tid + q * THREADS) stay in registers until they are placed
+    constexpr int ITEMS = CAP / THREADS;
+    // The high words of a list's keys all hold the tile, unless the caller left bits above the sorted width in
+    // them; "mixed" records that, and the write-out then fetches each key's own high word.
+    const uint32_t tile_word = (uint32_t)(__ldg(keys_grouped + r.x) >> 32);
+    uint32_t d[ITEMS], lo = 0xFFFFFFFFu, hi = 0u;
+    int mixed = 0;
+#pragma unroll
+    for (int q = 0; q < ITEMS; q++) {
+        const int i = tid + q * THREADS;
+        const uint64_t kk = i < n ? __ldg(keys_grouped + r.x + i) : 0ull;
+        d[q] = (uint32_t)kk;
+        if (i < n) { lo = min(lo, d[q]); hi = max(hi, d[q]); mixed |= (uint32_t)(kk >> 32) != tile_word; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -627,25 +634,39 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
         hi = max(hi, __shfl_xor_sync(FULL_MASK, hi, o));
     }
     if (lane == 0) { atomicMin(&s_min, lo); atomicMax(&s_max, hi); }
-    __syncthreads();
+    mixed = __syncthreads_or(mixed);
     FGS_LT(1);
     const uint32_t dmin = s_min, span = s_max - s_min;
     bool gathered = false;
     if (span == 0) {
-        // all depths equal: the input order is the sorted order (a[] already is in it)
+        // all depths equal: the input order is the sorted order
+#pragma unroll
+        for (int q = 0; q < ITEMS; q++) {
+            const int i = tid + q * THREADS;
+            if (i < n) a[i] = ((uint64_t)d[q] << 32) | (uint32_t)i;
+        }
         gathered = true;
     } else {
         // bucket of a depth: monotone in the depth (conversion and multiplication round monotonically)
         const float scale = (float)NB / ((float)span + 1.0f);
-        auto bucket_of = [&](uint32_t d) { return min((int)((float)(d - dmin) * scale), NB - 1); };
-        for (int i = tid; i < n; i += THREADS) atomicAdd(&cursor[bucket_of((uint32_t)(a[i] >> 32))], 1u);
+        auto bucket_of = [&](uint32_t dd) { return min((int)((float)(dd - dmin) * scale), NB - 1); };
+        // one atomic per element: it counts the bucket and hands the element its arrival number inside it
+        uint32_t where[ITEMS];   // bucket | arrival number << 16 (both below 65536)
+#pragma unroll
+        for (int q = 0; q < ITEMS; q++) {
+            const int i = tid + q * THREADS;
+            if (i < n) {
+                const int b = bucket_of(d[q]);
+                where[q] = (uint32_t)b | (atomicAdd(&cursor[b], 1u) << 16);
+            }
+        }
         __syncthreads();
         FGS_LT(2);
-        // exclusive scan of the bucket counts: 8 consecutive buckets per thread, then warps, then the block
+        // exclusive scan of the bucket counts: consecutive buckets per thread, then warps, then the block
         constexpr int PER = NB / THREADS;
-        uint32_t c[PER], sum = 0, biggest = 0;
+        uint32_t sum = 0, biggest = 0;
 #pragma unroll
-        for (int q = 0; q < PER; q++) { c[q] = cursor[tid * PER + q]; sum += c[q]; biggest = max(biggest, c[q]); }
+        for (int q = 0; q < PER; q++) { const uint32_t c = cursor[tid * PER + q]; sum += c; biggest = max(biggest, c); }
         if (biggest > LOCAL_BUCKET_LIMIT) s_piled = 1;
         uint32_t inc = sum;
 #pragma unroll
@@ -657,22 +678,22 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
         __syncthreads();
         uint32_t off = inc - sum;
         for (int ww = 0; ww < warp; ww++) off += s_wsum[ww];
-        const bool piled = s_piled != 0;
-        if (!piled) {
 #pragma unroll
-            for (int q = 0; q < PER; q++) { start[tid * PER + q] = off; cursor[tid * PER + q] = off; off += c[q]; }
-            if (tid == THREADS - 1) start[NB] = off;
-            __syncthreads();
-            FGS_LT(3);
-            for (int i = tid; i < n; i += THREADS) {
-                const uint64_t k = a[i];
-                bk[atomicAdd(&cursor[bucket_of((uint32_t)(k >> 32))], 1u)] = k;
+        for (int q = 0; q < PER; q++) { start[tid * PER + q] = off; off += cursor[tid * PER + q]; }
+        if (tid == THREADS - 1) start[NB] = off;
+        __syncthreads();
+        FGS_LT(3);
+        if (s_piled == 0) {
+#pragma unroll
+            for (int q = 0; q < ITEMS; q++) {
+                const int i = tid + q * THREADS;
+                if (i < n) bk[start[where[q] & 0xFFFFu] + (where[q] >> 16)] = ((uint64_t)d[q] << 32) | (uint32_t)i;
             }
             __syncthreads();
             FGS_LT(4);
             // every bucket in order of (depth, position): one thread per ELEMENT counts the smaller keys of its
             // bucket (keys are unique), so a bucket of L elements costs L steps on L threads, not L^2 on one;
-            // the element then goes to its final place in a[] (whose load-order contents are no longer needed)
+            // the element then goes to its final place in a[]
             for (int x = tid; x < n; x += THREADS) {
                 const uint64_t kc = bk[x];
                 const int bkt = bucket_of((uint32_t)(kc >> 32));
@@ -683,6 +704,12 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
             }
             FGS_LT(5);
             gathered = true;
+        } else {
+#pragma unroll
+            for (int q = 0; q < ITEMS; q++) {
+                const int i = tid + q * THREADS;
+                if (i < n) a[i] = ((uint64_t)d[q] << 32) | (uint32_t)i;
+            }
         }
     }
     __syncthreads();
@@ -706,9 +733,12 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
         }
     }
     __syncthreads();
+    // a[i] = depth << 32 | position of the i-th smallest key
     for (int i = tid; i < n; i += THREADS) {
-        const uint32_t from = (uint32_t)a[i];   // position of the i-th smallest key in the tile's list
-        keys_out[r.x + i] = __ldg(keys_grouped + r.x + from);
+        const uint64_t k = a[i];
+        const uint32_t from = (uint32_t)k;
+        const uint32_t high = mixed ? (uint32_t)(__ldg(keys_grouped + r.x + from) >> 32) : tile_word;
+        keys_out[r.x + i] = ((uint64_t)high << 32) | (k >> 32);
         vals_out[r.x + i] = __ldg(vals_grouped + r.x + from);
     }
     if (tid == 0) s_next = next_ticket;   // requested at the top of the iteration, so its latency is hidden
