@@ -11,7 +11,7 @@
 //      could not be vectorised); each thread then projects its own Gaussian.
 //   2. Work items are (Gaussian, tile row, 32-tile window of that row). The items of the
 //      block's Gaussians are laid end to end with a block-wide exclusive scan and all 256
-//      threads walk the item space together; a thread finds the Gaussian an item belongs to
+//      warps walk the item space together; a lane finds the Gaussian an item belongs to
 //      by binary search in the scan. A splat covering thousands of tiles is thus spread over
 //      the whole block instead of serialising a warp.
 //      For its item a thread first bounds, in closed form and with generous margins, the
@@ -20,10 +20,13 @@
 //      splats this skips most of the bounding rectangle; the margins are far wider than the
 //      float error of either computation, so the set of hits is the one the exact test
 //      alone would give (the parity tests compare it pair by pair).
-//   3. Pair offsets: per chunk of 1024 items the hit counts are scanned (warp shuffles, then
-//      one warp over the 32 per-warp totals), which issues ONE atomicAdd on the global pair
-//      counter for the whole chunk (a warp-aggregated prefix); every thread then stores the
-//      keys of its item's hits.
+//   3. The exact tests are spread evenly too: a warp takes 32 items, lays their candidate
+//      tiles end to end (warp scan) and tests 32 candidates at a time, one per lane, whatever
+//      item they belong to (a lane finds its candidate's item from a bit mask of the items'
+//      first candidates). Hits are compacted by ballot into a per-warp staging buffer in
+//      shared memory; a full buffer is written out with ONE atomicAdd on the global pair
+//      counter and coalesced stores, and what is left at the end goes out with one atomicAdd
+//      for the whole block.
 //   4. Gaussians with at least one hit fetch their 192-byte SH record with 16-byte loads
 //      and write the three feature records.
 //
@@ -43,9 +46,9 @@ constexpr int PRE_WARPS = PRE_THREADS / 32;
 #ifndef FGS_PRE_BLOCKS_PER_SM
 #define FGS_PRE_BLOCKS_PER_SM 4
 #endif
-constexpr int PRE_BLOCKS_PER_SM = FGS_PRE_BLOCKS_PER_SM;   // persistent blocks per SM
-constexpr int PRE_K = 4;  // slot iterations per offset chunk (PRE_K * PRE_WARPS == 32 counts, one warp scans them)
-static_assert(PRE_K * PRE_WARPS == 32, "one warp scans the chunk's per-warp counts");
+constexpr int PRE_BLOCKS_PER_SM = FGS_PRE_BLOCKS_PER_SM;   // resident blocks per SM the register budget is set for
+constexpr int STG_CAP = 256;              // hits a warp can hold before it writes them out
+constexpr int STG_FLUSH = STG_CAP - 32;   // write out once a further round of 32 tests might not fit
 
 constexpr float kLog2e = 1.4426950216293334961f;
 constexpr float kLn2 = 0.69314718055f;
@@ -227,53 +230,39 @@ preprocess_kernel(int P,
                   uint64_t* __restrict__ keys, uint32_t* __restrict__ values, long long capacity,
                   int* __restrict__ curr_offset, int* __restrict__ status)
 {
-    __shared__ __align__(16) float s_pos2[2][PRE_THREADS * 3];   // two stages: the next block of Gaussians is
-    __shared__ __align__(16) float s_cov2[2][PRE_THREADS * 6];   // fetched while the current one is processed
-    __shared__ __align__(16) float s_opa2[2][PRE_THREADS];
+    __shared__ __align__(16) float s_pos[PRE_THREADS * 3];
+    __shared__ __align__(16) float s_cov[PRE_THREADS * 6];
+    __shared__ __align__(16) float s_opa[PRE_THREADS];
     __shared__ float2 s_xy[PRE_THREADS];
     __shared__ float4 s_con[PRE_THREADS];      // conic.x, conic.y, conic.z, power
     __shared__ int4 s_rect[PRE_THREADS];       // min_x, min_y, width, float_bits(depth)
     __shared__ float4 s_cull[PRE_THREADS];     // enlarged w, dx_max (< 0: no culling), dy_max, dy where x is largest
-    __shared__ int s_prefix[PRE_THREADS + 1];  // exclusive scan of rectangle areas
-    __shared__ int s_vis[PRE_THREADS];
-    __shared__ int s_wcnt[32];
-    __shared__ int s_woff[32];
+    __shared__ int s_prefix[PRE_THREADS + 1];  // exclusive scan of the item counts
+    __shared__ uint8_t s_vis[PRE_THREADS];
+    __shared__ int4 s_rec[PRE_WARPS][32];      // per lane of a warp: first candidate number, Gaussian, tile row, first column
+    __shared__ uint8_t s_src[PRE_WARPS][32];   // the lanes that have candidates, in lane order
+    __shared__ uint2 s_stage[PRE_WARPS][STG_CAP];   // hits waiting to be written: tile, Gaussian
     __shared__ int s_wsum[PRE_WARPS];
+    __shared__ int s_wcnt[PRE_WARPS];
+    __shared__ int s_tail_base;
 
 #ifdef FGS_PRE_TIMING
     long long t_prev_ = clock64();
 #endif
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
-    // Persistent blocks: block b takes the groups of 256 Gaussians b, b + gridDim.x, ...
-    const int num_groups = (P + PRE_THREADS - 1) / PRE_THREADS;
-    auto fetch = [&](int group, int stage) {
-        const int gb = group * PRE_THREADS;
-        const int cnt = min(PRE_THREADS, P - gb);
-        if (VEC) {
-            stage_floats_async(s_pos2[stage], positions + (size_t)gb * 3, cnt * 3);
-            stage_floats_async(s_cov2[stage], cov3ds + (size_t)gb * 6, cnt * 6);
-            stage_floats_async(s_opa2[stage], opacities + gb, cnt);
-        } else {
-            stage_floats<false>(s_pos2[stage], positions + (size_t)gb * 3, cnt * 3);
-            stage_floats<false>(s_cov2[stage], cov3ds + (size_t)gb * 6, cnt * 6);
-            stage_floats<false>(s_opa2[stage], opacities + gb, cnt);
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    if ((int)blockIdx.x < num_groups) fetch(blockIdx.x, 0);
-    int stage = 0;
-    for (int group = blockIdx.x; group < num_groups; group += gridDim.x, stage ^= 1) {
-    const int base = group * PRE_THREADS;
+    const int base = blockIdx.x * PRE_THREADS;
     const int n_here = min(PRE_THREADS, P - base);
-    const float* s_pos = s_pos2[stage];
-    const float* s_cov = s_cov2[stage];
-    const float* s_opa = s_opa2[stage];
-    if (group + (int)gridDim.x < num_groups) {
-        fetch(group + gridDim.x, stage ^ 1);   // the other stage was last read one iteration ago (barrier at the loop's end)
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
+    if (VEC) {
+        stage_floats_async(s_pos, positions + (size_t)base * 3, n_here * 3);
+        stage_floats_async(s_cov, cov3ds + (size_t)base * 6, n_here * 6);
+        stage_floats_async(s_opa, opacities + base, n_here);
+        asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+        stage_floats<false>(s_pos, positions + (size_t)base * 3, n_here * 3);
+        stage_floats<false>(s_cov, cov3ds + (size_t)base * 6, n_here * 6);
+        stage_floats<false>(s_opa, opacities + base, n_here);
     }
     s_vis[tid] = 0;
     __syncthreads();
@@ -385,119 +374,130 @@ preprocess_kernel(int P,
     FGS_PT(2);
     const int total = s_prefix[PRE_THREADS];
 
-    // ---- walk the item space: PRE_K items per thread per chunk ----
+    // ---- walk the item space: each warp takes 32 consecutive items at a time ----
     const float margin = 0.5f;   // pixels, on both the band and the column range
-    for (int c0 = 0; c0 < total; c0 += PRE_THREADS * PRE_K) {
-        unsigned hit_mask[PRE_K];
-        int first_tile[PRE_K];    // tile id of bit 0 of hit_mask
-        int owner[PRE_K];
-        int excl[PRE_K];          // exclusive prefix of the hit count inside the warp, per k
+    uint2* stage = s_stage[warp];
+    int staged = 0;              // hits of this warp waiting in stage[] (the same in every lane)
+    const unsigned lt = lanemask_lt(), le = lt | (1u << lane);
+    auto write_staged = [&](long long first, int count) {
+        for (int i = lane; i < count; i += 32) {
+            const uint2 e = stage[i];
+            const long long o = first + i;
+            if (o >= 0 && o < capacity) {
+                keys[o] = ((uint64_t)e.x << 32) | (uint32_t)s_rect[e.y].w;
+                values[o] = (uint32_t)(base + (int)e.y);
+            } else {
+                atomicOr(status, FGS_ERR_PAIR_OVERFLOW);
+            }
+        }
+    };
+    for (int c0 = warp * 32; c0 < total; c0 += PRE_THREADS) {
+        // 1. this lane's item: its Gaussian, tile row and the candidate columns [x_begin, x_end)
+        const int item = c0 + lane;
+        int g = 0, ty = 0, x_begin = 0, x_end = 0;
+        if (item < total) {
+            int lo = 0, hi = PRE_THREADS;   // largest g with s_prefix[g] <= item
 #pragma unroll
-        for (int k = 0; k < PRE_K; k++) {
-            const int item = c0 + k * PRE_THREADS + tid;
-            unsigned mask = 0;
-            first_tile[k] = 0; owner[k] = 0;
-            if (item < total) {
-                int lo = 0, hi = PRE_THREADS;   // largest g with s_prefix[g] <= item
-#pragma unroll
-                for (int st = 0; st < 8; st++) {
-                    const int mid = (lo + hi) >> 1;
-                    if (s_prefix[mid] <= item) lo = mid; else hi = mid;
-                }
-                const int g = lo;
-                const int4 rc = s_rect[g];
-                const int t = item - s_prefix[g];
-                const int ns = (rc.z + 31) >> 5;
-                const int row = (ns == 1) ? t : t / ns;
-                const int seg = t - row * ns;
-                const int ty = rc.y + row;
-                int x_begin = rc.x + (seg << 5);
-                int x_end = min(rc.x + rc.z, x_begin + 32);
+            for (int st = 0; st < 8; st++) {
+                const int mid = (lo + hi) >> 1;
+                if (s_prefix[mid] <= item) lo = mid; else hi = mid;
+            }
+            g = lo;
+            const int4 rc = s_rect[g];
+            const int t = item - s_prefix[g];
+            const int ns = (rc.z + 31) >> 5;
+            const int row = (ns == 1) ? t : t / ns;
+            const int seg = t - row * ns;
+            ty = rc.y + row;
+            x_begin = rc.x + (seg << 5);
+            x_end = min(rc.x + rc.z, x_begin + 32);
+            const float4 cu = s_cull[g];
+            if (cu.y >= 0.f) {
                 const float2 c = s_xy[g];
                 const float4 q = s_con[g];
-                const float4 cu = s_cull[g];
-                if (cu.y >= 0.f) {
-                    // band of pixel rows of this tile row, relative to the centre, clipped to the ellipse's extent
-                    const float d_lo = fmaxf((float)(ty * cam.block_y) - c.y - margin, -cu.z);
-                    const float d_hi = fminf((float)(ty * cam.block_y + cam.block_y - 1) - c.y + margin, cu.z);
-                    if (d_lo > d_hi) {
-                        x_end = x_begin;
-                    } else {
-                        const float det = q.x * q.z - q.y * q.y;
-                        const float s_lo = approx_sqrt(fmaxf(0.f, q.x * cu.x - det * d_lo * d_lo));
-                        const float s_hi = approx_sqrt(fmaxf(0.f, q.x * cu.x - det * d_hi * d_hi));
-                        const float inv_a = __frcp_rn(q.x);
-                        const float xh = (cu.w >= d_lo && cu.w <= d_hi) ? cu.y
-                                         : fmaxf((-q.y * d_lo + s_lo) * inv_a, (-q.y * d_hi + s_hi) * inv_a);
-                        const float xl = (-cu.w >= d_lo && -cu.w <= d_hi) ? -cu.y
-                                         : fminf((-q.y * d_lo - s_lo) * inv_a, (-q.y * d_hi - s_hi) * inv_a);
-                        // tiles whose pixel box [tx*bx, tx*bx + bx - 1] meets [c.x + xl - margin, c.x + xh + margin]
-                        const float inv_bx = 1.0f / (float)cam.block_x;
-                        const float fl = ceilf((c.x + xl - margin - (float)(cam.block_x - 1)) * inv_bx);
-                        const float fr = floorf((c.x + xh + margin) * inv_bx);
-                        x_begin = max(x_begin, (int)fmaxf(fl, -1.0e6f));
-                        x_end = min(x_end, (int)fminf(fr, 1.0e6f) + 1);
-                    }
+                // band of pixel rows of this tile row, relative to the centre, clipped to the ellipse's extent
+                const float d_lo = fmaxf((float)(ty * cam.block_y) - c.y - margin, -cu.z);
+                const float d_hi = fminf((float)(ty * cam.block_y + cam.block_y - 1) - c.y + margin, cu.z);
+                if (d_lo > d_hi) {
+                    x_end = x_begin;
+                } else {
+                    const float det = q.x * q.z - q.y * q.y;
+                    const float s_lo = approx_sqrt(fmaxf(0.f, q.x * cu.x - det * d_lo * d_lo));
+                    const float s_hi = approx_sqrt(fmaxf(0.f, q.x * cu.x - det * d_hi * d_hi));
+                    const float inv_a = __frcp_rn(q.x);
+                    const float xh = (cu.w >= d_lo && cu.w <= d_hi) ? cu.y
+                                     : fmaxf((-q.y * d_lo + s_lo) * inv_a, (-q.y * d_hi + s_hi) * inv_a);
+                    const float xl = (-cu.w >= d_lo && -cu.w <= d_hi) ? -cu.y
+                                     : fminf((-q.y * d_lo - s_lo) * inv_a, (-q.y * d_hi - s_hi) * inv_a);
+                    // tiles whose pixel box [tx*bx, tx*bx + bx - 1] meets [c.x + xl - margin, c.x + xh + margin]
+                    const float inv_bx = 1.0f / (float)cam.block_x;
+                    const float fl = ceilf((c.x + xl - margin - (float)(cam.block_x - 1)) * inv_bx);
+                    const float fr = floorf((c.x + xh + margin) * inv_bx);
+                    x_begin = max(x_begin, (int)fmaxf(fl, -1.0e6f));
+                    x_end = min(x_end, (int)fminf(fr, 1.0e6f) + 1);
                 }
-                first_tile[k] = ty * cam.grid_x + rc.x + (seg << 5);
-                owner[k] = g;
-                const int bit0 = rc.x + (seg << 5);
-                for (int tx = x_begin; tx < x_end; tx++)
-                    if (tile_hit(tx, ty, cam.block_x, cam.block_y, c.x, c.y, q.x, q.y, q.z, q.w))
-                        mask |= 1u << (tx - bit0);
-                if (mask) s_vis[g] = 1;
             }
-            hit_mask[k] = mask;
-            const int cnt = __popc(mask);
-            int inc = cnt;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int v = __shfl_up_sync(FULL_MASK, inc, o);
-                if (lane >= o) inc += v;
-            }
-            excl[k] = inc - cnt;
-            if (lane == 31) s_wcnt[k * PRE_WARPS + warp] = inc;
         }
-        __syncthreads();
-        if (warp == 0) {
-            const int c = s_wcnt[lane];
-            int inc = c;
+        // 2. the candidate tiles of the warp's 32 items laid end to end
+        const int cnt = max(x_end - x_begin, 0);
+        int inc = cnt;
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int v = __shfl_up_sync(FULL_MASK, inc, o);
-                if (lane >= o) inc += v;
-            }
-            const int chunk_total = __shfl_sync(FULL_MASK, inc, 31);
-            int chunk_base = 0;
-            if (lane == 0 && chunk_total > 0) chunk_base = atomicAdd(curr_offset, chunk_total);
-            chunk_base = __shfl_sync(FULL_MASK, chunk_base, 0);
-            s_woff[lane] = chunk_base + inc - c;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(FULL_MASK, inc, o);
+            if (lane >= o) inc += v;
         }
-        __syncthreads();
-#pragma unroll
-        for (int k = 0; k < PRE_K; k++) {
-            unsigned m = hit_mask[k];
-            if (m) {
-                long long o = (long long)s_woff[k * PRE_WARPS + warp] + excl[k];
-                const int g = owner[k];
-                const uint32_t depth_bits = (uint32_t)s_rect[g].w;
-                const uint32_t idx = (uint32_t)(base + g);
-                while (m) {
-                    const int bit = __ffs(m) - 1;
-                    m &= m - 1;
-                    if (o >= 0 && o < capacity) {
-                        keys[o] = ((uint64_t)(uint32_t)(first_tile[k] + bit) << 32) | depth_bits;
-                        values[o] = idx;
-                    } else {
-                        atomicOr(status, FGS_ERR_PAIR_OVERFLOW);
-                    }
-                    o++;
-                }
+        const int excl = inc - cnt;
+        const int candidates = __shfl_sync(FULL_MASK, inc, 31);
+        if (candidates == 0) continue;
+        const unsigned has = __ballot_sync(FULL_MASK, cnt > 0);
+        __syncwarp();   // the previous round's reads of s_rec / s_src are over
+        if (cnt > 0) s_src[warp][__popc(has & lt)] = (uint8_t)lane;
+        s_rec[warp][lane] = make_int4(excl, g, ty, x_begin);
+        __syncwarp();
+        // 3. 32 candidates at a time, one exact test per lane; hits go to the warp's staging buffer
+        for (int b0 = 0; b0 < candidates; b0 += 32) {
+            // bit i of starts: an item's candidates begin at candidate b0 + i
+            const unsigned starts = __reduce_or_sync(FULL_MASK, (cnt > 0 && excl >= b0 && excl < b0 + 32) ? (1u << (excl - b0)) : 0u);
+            const int before = __popc(__ballot_sync(FULL_MASK, cnt > 0 && excl < b0));
+            const int j = b0 + lane;
+            bool hit = false;
+            int tile = 0, gs = 0;
+            if (j < candidates) {
+                // the item this candidate belongs to: the last one that begins at or before it
+                const int4 rc = s_rec[warp][s_src[warp][before + __popc(starts & le) - 1]];
+                const int tx = rc.w + (j - rc.x);
+                gs = rc.y;
+                const float2 c = s_xy[gs];
+                const float4 q = s_con[gs];
+                hit = tile_hit(tx, rc.z, cam.block_x, cam.block_y, c.x, c.y, q.x, q.y, q.z, q.w);
+                tile = rc.z * cam.grid_x + tx;
+            }
+            const unsigned hits = __ballot_sync(FULL_MASK, hit);
+            if (hit) {
+                stage[staged + __popc(hits & lt)] = make_uint2((unsigned)tile, (unsigned)gs);
+                s_vis[gs] = 1;
+            }
+            staged += __popc(hits);
+            if (staged >= STG_FLUSH) {   // one atomicAdd on the global pair counter per flush
+                __syncwarp();
+                int first = 0;
+                if (lane == 0) first = atomicAdd(curr_offset, staged);
+                first = __shfl_sync(FULL_MASK, first, 0);
+                write_staged(first, staged);
+                staged = 0;
+                __syncwarp();
             }
         }
     }
+    if (lane == 0) s_wcnt[warp] = staged;
     __syncthreads();
     FGS_PT(3);
+    // what the warps still hold is written after the feature phase, at offsets from ONE atomicAdd for the block
+    if (tid == 0) {
+        int rest = 0;
+        for (int w = 0; w < PRE_WARPS; w++) rest += s_wcnt[w];
+        s_tail_base = rest > 0 ? atomicAdd(curr_offset, rest) : 0;
+    }
 
     // ---- features of visible Gaussians (preprocess.cu:411-417) ----
     if (tid < n_here && s_vis[tid]) {
@@ -521,7 +521,11 @@ preprocess_kernel(int P,
         rgb_depth[idx] = make_float4(r, g, b, depth);
     }
     FGS_PT(4);
-    __syncthreads();   // shared memory of this group is no longer read
+    __syncthreads();
+    {
+        long long first = s_tail_base;
+        for (int w = 0; w < warp; w++) first += s_wcnt[w];
+        write_staged(first, staged);
     }
 }
 
@@ -583,18 +587,7 @@ extern "C" int fgs_preprocess_strip(int P, const float* positions, const float* 
 
     const bool vec = aligned16(positions) && aligned16(shs) && aligned16(opacities) && aligned16(cov3ds);
     const int groups = (P + PRE_THREADS - 1) / PRE_THREADS;
-    static int sm_count[64];
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FGS_ERR_CUDA;
-    if (!sm_count[dev] && (cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count[dev] <= 0))
-        return FGS_ERR_CUDA;
-    const int resident = sm_count[dev] * PRE_BLOCKS_PER_SM;
-#ifndef FGS_PRE_PERSISTENT_MODE
-#define FGS_PRE_PERSISTENT_MODE 0   // 0: one block per group of 256 Gaussians; 1: persistent blocks always; 2: persistent for strips only
-#endif
-    const bool strip = cam.row_begin > 0 || cam.row_end < cam.grid_y;
-    const bool persistent = FGS_PRE_PERSISTENT_MODE == 1 || (FGS_PRE_PERSISTENT_MODE == 2 && strip);
-    const int blocks = (!persistent || groups < resident) ? groups : resident;
+    const int blocks = groups;   // one block per 256 Gaussians
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (vec)
         preprocess_kernel<true><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,
