@@ -438,6 +438,7 @@ preprocess_kernel(int P,
                 }
             }
         }
+        FGS_PT(5);
         // 2. the candidate tiles of the warp's 32 items laid end to end
         const int cnt = max(x_end - x_begin, 0);
         int inc = cnt;
@@ -488,6 +489,7 @@ preprocess_kernel(int P,
                 __syncwarp();
             }
         }
+        FGS_PT(6);
     }
     if (lane == 0) s_wcnt[warp] = staged;
     __syncthreads();

@@ -586,13 +586,15 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
                   const int* __restrict__ work_count, const uint32_t* __restrict__ work_tiles, int* __restrict__ work_ticket)
 {
     constexpr int NB = local_buckets(CAP);   // depth buckets
+    constexpr int ITEMS = CAP / THREADS;     // elements per thread: positions tid + q * THREADS of the list
     extern __shared__ __align__(16) unsigned char s_local[];
-    uint64_t* a = reinterpret_cast<uint64_t*>(s_local);                         // [CAP] depth << 32 | position
+    uint64_t* a = reinterpret_cast<uint64_t*>(s_local);                         // [CAP] depth << 32 | position, sorted
     uint64_t* bk = reinterpret_cast<uint64_t*>(s_local + CAP * 8);              // [CAP] the same keys, bucket by bucket
     uint32_t* start = reinterpret_cast<uint32_t*>(s_local + CAP * 16);          // [NB + 1]
-    uint32_t* cursor = start + NB + 1;                               // [NB]
-    __shared__ uint32_t s_min, s_max, s_wsum[THREADS / 32];
+    uint32_t* cursor = start + NB + 1;                                          // [NB]
+    __shared__ uint32_t s_min, s_max, s_tile_word, s_wsum[THREADS / 32];
     __shared__ int s_piled;
+    __shared__ int2 s_seg;   // the list the block sorts next; y < x: none
 
     if (*too_long) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -600,44 +602,58 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     long long lt_prev_ = clock64();
 #endif
     const int work = *work_count;
-    __shared__ int s_next;
-    if (tid == 0) s_next = atomicAdd(work_ticket, 1);
+    // Persistent blocks draw lists of the class's work list from a ticket counter. The keys of the NEXT list are
+    // requested while the current one is ranked and written out, so their latency is not waited for.
+    auto fetch = [&](const int2 rr, uint64_t (&kk)[ITEMS]) {
+#pragma unroll
+        for (int q = 0; q < ITEMS; q++) {
+            const int i = tid + q * THREADS;
+            kk[q] = i < rr.y - rr.x ? __ldg(keys_grouped + rr.x + i) : 0ull;
+        }
+    };
+    if (tid == 0) {
+        const int w = atomicAdd(work_ticket, 1);
+        s_seg = w < work ? seg[work_tiles[w]] : make_int2(0, -1);
+    }
     __syncthreads();
-    for (;;) {   // persistent blocks draw tiles of the class's work list from a ticket counter
-    const int w = s_next;
-    if (w >= work) break;
-    const int2 r = seg[work_tiles[w]];
+    int2 r = s_seg;
+    uint64_t kk[ITEMS];
+    fetch(r, kk);
+    while (r.y >= r.x) {
     const int n = r.y - r.x;
-    __syncthreads();   // everyone has read s_next; the previous tile's shared memory is no longer read
+    __syncthreads();   // the previous list's shared memory, and s_seg, are no longer read
     int next_ticket = 0;
     if (tid == 0) { s_min = 0xFFFFFFFFu; s_max = 0u; s_piled = 0; next_ticket = atomicAdd(work_ticket, 1); }
     for (int i = tid; i < NB; i += THREADS) cursor[i] = 0;
-    __syncthreads();
     FGS_LT(0);
-    // depths of this thread's elements (positions tid + q * THREADS) stay in registers until they are placed
-    constexpr int ITEMS = CAP / THREADS;
-    // The high words of a list's keys all hold the tile, unless the caller left bits above the sorted width in
-    // them; "mixed" records that, and the write-out then fetches each key's own high word.
-    const uint32_t tile_word = (uint32_t)(__ldg(keys_grouped + r.x) >> 32);
-    uint32_t d[ITEMS], lo = 0xFFFFFFFFu, hi = 0u;
-    int mixed = 0;
+    // The depths stay in registers until they are placed. The high words of a list's keys all hold the tile,
+    // unless the caller left bits above the sorted width in them; "mixed" records that, and the write-out then
+    // fetches each key's own high word.
+    uint32_t d[ITEMS], lo = 0xFFFFFFFFu, hi = 0u, high_and = 0xFFFFFFFFu, high_or = 0u;
 #pragma unroll
     for (int q = 0; q < ITEMS; q++) {
-        const int i = tid + q * THREADS;
-        const uint64_t kk = i < n ? __ldg(keys_grouped + r.x + i) : 0ull;
-        d[q] = (uint32_t)kk;
-        if (i < n) { lo = min(lo, d[q]); hi = max(hi, d[q]); mixed |= (uint32_t)(kk >> 32) != tile_word; }
+        d[q] = (uint32_t)kk[q];
+        if (tid + q * THREADS < n) {
+            lo = min(lo, d[q]); hi = max(hi, d[q]);
+            high_and &= (uint32_t)(kk[q] >> 32); high_or |= (uint32_t)(kk[q] >> 32);
+        }
     }
+    if (tid == 0) s_tile_word = (uint32_t)(kk[0] >> 32);
+    __syncthreads();   // cursor[] is zero, s_min / s_max are set up
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         lo = min(lo, __shfl_xor_sync(FULL_MASK, lo, o));
         hi = max(hi, __shfl_xor_sync(FULL_MASK, hi, o));
     }
     if (lane == 0) { atomicMin(&s_min, lo); atomicMax(&s_max, hi); }
-    mixed = __syncthreads_or(mixed);
+    __syncthreads();
     FGS_LT(1);
+    uint32_t next_tile = 0;
+    if (tid == 0 && next_ticket < work) next_tile = __ldg(work_tiles + next_ticket);
+    const uint32_t tile_word = s_tile_word;
+    const int mixed_here = n > tid && (high_and != tile_word || high_or != tile_word);
     const uint32_t dmin = s_min, span = s_max - s_min;
-    bool gathered = false;
+    bool gathered = false, fetched = false;
     if (span == 0) {
         // all depths equal: the input order is the sorted order
 #pragma unroll
@@ -660,6 +676,8 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
                 where[q] = (uint32_t)b | (atomicAdd(&cursor[b], 1u) << 16);
             }
         }
+        int2 next_seg = make_int2(0, -1);
+        if (tid == 0 && next_ticket < work) next_seg = seg[next_tile];
         __syncthreads();
         FGS_LT(2);
         // exclusive scan of the bucket counts: consecutive buckets per thread, then warps, then the block
@@ -681,6 +699,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
 #pragma unroll
         for (int q = 0; q < PER; q++) { start[tid * PER + q] = off; off += cursor[tid * PER + q]; }
         if (tid == THREADS - 1) start[NB] = off;
+        if (tid == 0) s_seg = next_seg;
         __syncthreads();
         FGS_LT(3);
         if (s_piled == 0) {
@@ -689,6 +708,8 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
                 const int i = tid + q * THREADS;
                 if (i < n) bk[start[where[q] & 0xFFFFu] + (where[q] >> 16)] = ((uint64_t)d[q] << 32) | (uint32_t)i;
             }
+            fetch(s_seg, kk);   // the registers are free again: request the next list's keys
+            fetched = true;
             __syncthreads();
             FGS_LT(4);
             // every bucket in order of (depth, position): one thread per ELEMENT counts the smaller keys of its
@@ -712,9 +733,10 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
             }
         }
     }
+    if (span == 0 && tid == 0) s_seg = next_ticket < work ? seg[next_tile] : make_int2(0, -1);
     __syncthreads();
     if (!gathered) {
-        // bitonic network over the whole tile (positions beyond n hold the largest key)
+        // bitonic network over the whole list (positions beyond n hold the largest key)
         int m = 2;
         while (m < n) m <<= 1;
         for (int i = n + tid; i < m; i += THREADS) a[i] = ~0ull;
@@ -732,7 +754,9 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
             }
         }
     }
-    __syncthreads();
+    const int2 r_next = s_seg;
+    if (!fetched) fetch(r_next, kk);
+    const int mixed = __syncthreads_or(mixed_here);
     // a[i] = depth << 32 | position of the i-th smallest key
     for (int i = tid; i < n; i += THREADS) {
         const uint64_t k = a[i];
@@ -741,9 +765,8 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
         keys_out[r.x + i] = ((uint64_t)high << 32) | (k >> 32);
         vals_out[r.x + i] = __ldg(vals_grouped + r.x + from);
     }
-    if (tid == 0) s_next = next_ticket;   // requested at the top of the iteration, so its latency is hidden
-    __syncthreads();
     FGS_LT(6);
+    r = r_next;
     }
 }
 
