@@ -26,10 +26,6 @@ NVCC_FLAGS = [
 ]
 
 
-# Sources that launch kernels from the device (the sort's stand-by passes) are compiled as relocatable device code.
-RELOCATABLE = {"fgs_sort.cu"}
-
-
 def _stale(target, deps):
     if not os.path.exists(target):
         return True
@@ -49,8 +45,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     def compile_one(job):
         s, o = job
-        extra = ["-rdc=true"] if os.path.basename(s) in RELOCATABLE else []
-        r = subprocess.run(["nvcc", "-c", s, "-o", o] + NVCC_FLAGS + extra, capture_output=True, text=True)
+        r = subprocess.run(["nvcc", "-c", s, "-o", o] + NVCC_FLAGS, capture_output=True, text=True)
         with open(o + ".log", "w") as f:
             f.write(r.stdout + r.stderr)
         if r.returncode != 0:
@@ -63,9 +58,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 print(log)
     objs = [os.path.join(OBJ_DIR, os.path.basename(s)[:-3] + ".o") for s in srcs]
     if force or jobs or _stale(LIB, objs):
-        # nvcc device-links the relocatable objects against the device runtime (libcudadevrt) here
-        subprocess.check_call(["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs +
-                              ["-ccbin", "/usr/bin/g++", "-lcudadevrt", "-lcudart"])
+        subprocess.check_call(["nvcc", "-shared", "-o", LIB] + objs + ["-ccbin", "/usr/bin/g++", "-lcudart"])
     return LIB
 
 

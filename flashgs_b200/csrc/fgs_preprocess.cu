@@ -47,10 +47,7 @@ constexpr int PRE_WARPS = PRE_THREADS / 32;
 #define FGS_PRE_BLOCKS_PER_SM 4
 #endif
 constexpr int PRE_BLOCKS_PER_SM = FGS_PRE_BLOCKS_PER_SM;   // resident blocks per SM the register budget is set for
-#ifndef FGS_PRE_STG_CAP
-#define FGS_PRE_STG_CAP 256
-#endif
-constexpr int STG_CAP = FGS_PRE_STG_CAP;  // hits a warp can hold before it writes them out
+constexpr int STG_CAP = 256;              // hits a warp can hold before it writes them out
 constexpr int STG_FLUSH = STG_CAP - 32;   // write out once a further round of 32 tests might not fit
 
 constexpr float kLog2e = 1.4426950216293334961f;
@@ -220,10 +217,6 @@ __device__ __forceinline__ void stage_floats(float* dst, const float* src, int n
 __device__ unsigned long long g_pre_cycles[8];
 #define FGS_PT(i) do { if (threadIdx.x == 0) { const long long now_ = clock64(); atomicAdd(&g_pre_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
 #else
-#define FGS_PT(i) do { } while (0)
-#endif
-#ifdef FGS_PRE_COUNTS   // with FGS_PRE_TIMING: slots 5..7 count items, items without candidates, candidates instead
-#undef FGS_PT
 #define FGS_PT(i) do { } while (0)
 #endif
 
@@ -456,10 +449,6 @@ preprocess_kernel(int P,
         }
         const int excl = inc - cnt;
         const int candidates = __shfl_sync(FULL_MASK, inc, 31);
-#ifdef FGS_PRE_COUNTS
-        { const unsigned live = __ballot_sync(FULL_MASK, item < total), empty = __ballot_sync(FULL_MASK, item < total && cnt == 0);
-          if (lane == 0) { atomicAdd(&g_pre_cycles[5], (unsigned long long)__popc(live)); atomicAdd(&g_pre_cycles[6], (unsigned long long)__popc(empty)); atomicAdd(&g_pre_cycles[7], (unsigned long long)candidates); } }
-#endif
         if (candidates == 0) continue;
         const unsigned has = __ballot_sync(FULL_MASK, cnt > 0);
         __syncwarp();   // the previous round's reads of s_rec / s_src are over

@@ -578,9 +578,8 @@ __device__ unsigned long long g_local_cycles[8];
 #define FGS_LT(i) do { } while (0)
 #endif
 
-// BLOCKS: resident blocks per SM the shared-memory footprint allows; it caps the registers accordingly
-template <int CAP, int THREADS, int BLOCKS>
-__global__ void __launch_bounds__(THREADS, BLOCKS)
+template <int CAP, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __restrict__ vals_grouped,
                   uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
                   const int2* __restrict__ seg, const int* __restrict__ too_long,
@@ -774,46 +773,6 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
 // sort.cu:9-24 computes the position of the highest set bit plus one
 inline int bit_length(uint32_t v) { int b = 0; while (v) { b++; v >>= 1; } return b; }
 
-// ---- the plain sort on stand-by, launched from the device ----
-// The tile-bucketed path gives up when a list is too long for the in-block sort (segments_kernel raises the
-// flag). The plain sort of all digits must then run on the same input, but the host cannot look at the flag
-// without a synchronisation. One single-thread kernel reads it and, only if it is set, launches the histogram
-// and the digit passes into the tail-launch stream of the device runtime: they run, in order, after this kernel
-// and before anything the host enqueued behind it. The common case thus costs one tiny launch, not one per pass.
-struct StandbyPass {
-    const uint64_t* src_k; const uint32_t* src_v; uint64_t* dst_k; uint32_t* dst_v;
-    int shift; uint32_t digit_mask; int use_bulk;
-};
-struct StandbyPlan {
-    const int* too_long; const uint64_t* keys_unsorted; const int* n_dev;
-    uint32_t* hist; uint32_t* tickets; uint32_t* status_words; int* dev_status;
-    int n, parts, passes, depth_passes, end_bit, hist_blocks, grid_blocks, skip_publish_part;
-    StandbyPass pass[MAX_PASSES];
-};
-
-__global__ void standby_gate_kernel(const __grid_constant__ StandbyPlan plan)
-{
-    if (*plan.too_long == 0) return;
-    histogram_kernel<<<plan.hist_blocks, HIST_THREADS, 0, cudaStreamTailLaunch>>>(
-        plan.keys_unsorted, plan.n, plan.n_dev, 0, plan.depth_passes, plan.end_bit, plan.hist, nullptr);
-    for (int p = 0; p < plan.passes; p++) {
-        const StandbyPass& q = plan.pass[p];
-#define FGS_PASS(SHIFT)                                                                                            \
-    case SHIFT:                                                                                                    \
-        onesweep_kernel<SHIFT><<<plan.grid_blocks, PASS_THREADS, SORT_SMEM_BYTES, cudaStreamTailLaunch>>>(         \
-            q.src_k, q.src_v, q.dst_k, q.dst_v, plan.n, plan.parts, q.digit_mask, q.use_bulk, plan.tickets + p,    \
-            plan.hist + p * RADIX, plan.status_words + (size_t)p * plan.parts * RADIX, plan.dev_status,            \
-            plan.skip_publish_part, nullptr, plan.n_dev);                                                          \
-        break;
-        switch (q.shift) {
-            FGS_PASS(0) FGS_PASS(8) FGS_PASS(16) FGS_PASS(24) FGS_PASS(32) FGS_PASS(40) FGS_PASS(48) FGS_PASS(56)
-        default: break;
-        }
-#undef FGS_PASS
-    }
-    if (cudaGetLastError() != cudaSuccess) atomicOr(plan.dev_status, FGS_ERR_CUDA);
-}
-
 int g_debug_skip_publish_part = -1;
 
 } // namespace
@@ -905,8 +864,8 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
 #define FGS_OPT_IN(SHIFT) if (e == cudaSuccess) e = cudaFuncSetAttribute(onesweep_kernel<SHIFT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SORT_SMEM_BYTES);
         FGS_OPT_IN(0) FGS_OPT_IN(8) FGS_OPT_IN(16) FGS_OPT_IN(24) FGS_OPT_IN(32) FGS_OPT_IN(40) FGS_OPT_IN(48) FGS_OPT_IN(56)
 #undef FGS_OPT_IN
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<LOCAL_CAP, 256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<LOCAL_CAP>());
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<2048, 256, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<2048>());
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<LOCAL_CAP, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<LOCAL_CAP>());
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<2048, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<2048>());
         if (e != cudaSuccess) return FGS_ERR_CUDA;
         smem_opt_in[dev] = true;
     }
@@ -975,52 +934,30 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         mark(LAUNCH_SEGMENTS);
         const int sms = sm_count[dev];
         auto grid_for = [&](int per_sm) { return tile_values < per_sm * sms ? tile_values : per_sm * sms; };
-        local_sort_kernel<1024, 128, 9><<<grid_for(12), 128, local_smem_bytes<1024>(), st>>>(
+        local_sort_kernel<1024, 128><<<grid_for(12), 128, local_smem_bytes<1024>(), st>>>(
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long, class_count + 0, class_tiles, class_count + 3);
         mark(LAUNCH_LOCAL_SORT);
-        local_sort_kernel<2048, 256, 4><<<grid_for(6), 256, local_smem_bytes<2048>(), st>>>(
+        local_sort_kernel<2048, 256><<<grid_for(6), 256, local_smem_bytes<2048>(), st>>>(
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long, class_count + 1, class_tiles + MAX_TILE_VALUES, class_count + 4);
         mark(LAUNCH_LOCAL_SORT);
-        local_sort_kernel<LOCAL_CAP, 256, 2><<<grid_for(3), 256, local_smem_bytes<LOCAL_CAP>(), st>>>(
+        local_sort_kernel<LOCAL_CAP, 256><<<grid_for(3), 256, local_smem_bytes<LOCAL_CAP>(), st>>>(
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long, class_count + 2, class_tiles + 2 * MAX_TILE_VALUES, class_count + 5);
         mark(LAUNCH_LOCAL_SORT);
     }
-    // the plain sort: all digits, least significant first
+    // the plain sort: all digits, least significant first; behind the bucketed path it only runs if that gave up
     if (bucketed) {
-        // behind the bucketed path it only runs if that gave up: see standby_gate_kernel
-        StandbyPlan plan;
-        plan.too_long = too_long; plan.keys_unsorted = keys_unsorted; plan.n_dev = n_dev;
-        plan.hist = hist; plan.tickets = tickets; plan.status_words = status_words; plan.dev_status = dev_status;
-        plan.n = n; plan.parts = L.parts; plan.passes = passes; plan.depth_passes = depth_passes; plan.end_bit = end_bit;
-        plan.hist_blocks = hist_blocks; plan.grid_blocks = grid_blocks; plan.skip_publish_part = g_debug_skip_publish_part;
-        const uint64_t* src_k = keys_unsorted;
-        const uint32_t* src_v = values_unsorted;
-        for (int p = 0; p < MAX_PASSES; p++) {
-            StandbyPass& q = plan.pass[p];
-            q = StandbyPass{ nullptr, nullptr, nullptr, nullptr, 0, 0u, 0 };
-            if (p >= passes) continue;
-            const bool to_out = ((passes - 1 - p) & 1) == 0;
-            const int shift = p * RADIX_BITS;
-            const int bits = (end_bit - shift) < RADIX_BITS ? (end_bit - shift) : RADIX_BITS;
-            q.src_k = src_k; q.src_v = src_v;
-            q.dst_k = to_out ? keys_sorted : alt_keys;
-            q.dst_v = to_out ? values_sorted : alt_vals;
-            q.shift = shift; q.digit_mask = (1u << bits) - 1u;
-            q.use_bulk = aligned16(src_k) && aligned16(src_v);
-            src_k = q.dst_k;
-            src_v = q.dst_v;
-        }
-        standby_gate_kernel<<<1, 1, 0, st>>>(plan);
+        histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, n_dev, 0, depth_passes, end_bit, hist, too_long);
         mark(LAUNCH_STANDBY_PASS);
-    } else {
+    }
+    {
         const uint64_t* src_k = keys_unsorted;
         const uint32_t* src_v = values_unsorted;
         for (int p = 0; p < passes; p++) {
             const bool to_out = ((passes - 1 - p) & 1) == 0;
             uint64_t* dst_k = to_out ? keys_sorted : alt_keys;
             uint32_t* dst_v = to_out ? values_sorted : alt_vals;
-            if (digit_pass(p, p, src_k, src_v, dst_k, dst_v, nullptr) != FGS_OK) return FGS_ERR_BAD_ARG;
-            mark(LAUNCH_DIGIT_PASS);
+            if (digit_pass(p, p, src_k, src_v, dst_k, dst_v, bucketed ? too_long : nullptr) != FGS_OK) return FGS_ERR_BAD_ARG;
+            mark(bucketed ? LAUNCH_STANDBY_PASS : LAUNCH_DIGIT_PASS);
             src_k = dst_k;
             src_v = dst_v;
         }
@@ -1122,4 +1059,3 @@ extern "C" int fgs_sort_pairs_static(int num_rendered, int width, int height, in
     return sort_pairs_impl(num_rendered, width, height, block_x, block_y, g_static_sort_ptr[dev], static_sort_bytes(),
                            keys_unsorted, values_unsorted, keys_sorted, values_sorted, stream, nullptr, nullptr, nullptr);
 }
-
