@@ -374,7 +374,7 @@ def main():
         by_kind = lambda k: [float(per[i]) for i in range(len(kind)) if kind[i] == k]  # noqa: E731
         hist_ms = sum(by_kind(0))
         pass_ms = by_kind(1)
-        seg_ms, local_ms, standby_ms = sum(by_kind(2)), sum(by_kind(3)), sum(by_kind(4))
+        seg_ms, local_ms = sum(by_kind(2)), sum(by_kind(3))
         gbs = lambda b, t: b / (t * 1e-3) / 1e9 if t > 0 else 0.0  # noqa: E731
         mean_pass = float(np.mean(pass_ms)) if pass_ms else 0.0
         stages = {
@@ -383,7 +383,6 @@ def main():
             "sort_digit_pass": {"ms": mean_pass, "launches": len(pass_ms), "bytes": bytes_sort_pass, "gbs": gbs(bytes_sort_pass, mean_pass)},
             "sort_tile_segments": {"ms": seg_ms, "launches": len(by_kind(2))},
             "sort_tile_local": {"ms": local_ms, "launches": len(by_kind(3)), "bytes": bytes_sort_pass, "gbs": gbs(bytes_sort_pass, local_ms)},
-            "sort_standby_passes": {"ms": standby_ms, "launches": len(by_kind(4))},
             "sort_total": {"ms": sort_ms, "bytes_compulsory": 24 * R},
             "ranges_blend": {"ms": render_ms, "launches": 2, "bytes": bytes_render, "gbs": gbs(bytes_render, render_ms),
                              "pixel_splat_pairs": None if S is None else S * 256},

@@ -81,7 +81,7 @@ inline SortLayout make_layout(int64_t n)
     if (n < 1) n = 1;
     L.parts = (int)((n + SORT_PART - 1) / SORT_PART);
     L.tickets_off = 0;                                           // MAX_PASSES tickets
-    L.flag_off = 128;                                            // "a tile is too long for the in-block sort" flag
+    L.flag_off = 128;                                            // one spare word, then the class counts and tickets
     L.hist_off = 256;                                            // MAX_PASSES x RADIX counts
     L.status_off = L.hist_off + (size_t)MAX_PASSES * RADIX * 4;  // passes x parts x RADIX words
     L.seg_off = align_up(L.status_off + (size_t)MAX_PASSES * L.parts * RADIX * 4, 256);   // [first, last) per tile value
@@ -123,9 +123,8 @@ __global__ void clear_bookkeeping_kernel(uint32_t* __restrict__ base_words, size
 // ---- digit histograms of passes [first_pass, last_pass) in one read of the keys ----
 __global__ void __launch_bounds__(HIST_THREADS)
 histogram_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict__ n_dev, int first_pass, int last_pass,
-                 int end_bit, uint32_t* __restrict__ hist, const int* __restrict__ run_only_if)
+                 int end_bit, uint32_t* __restrict__ hist)
 {
-    if (run_only_if != nullptr && *run_only_if == 0) return;
     n = device_count(n, n_dev);
     __shared__ uint32_t s_hist[MAX_PASSES * RADIX];
     const int np = last_pass - first_pass;
@@ -250,11 +249,8 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
                 int n, int num_parts, uint32_t digit_mask, int use_bulk,
                 uint32_t* __restrict__ ticket, const uint32_t* __restrict__ hist,
                 uint32_t* __restrict__ status_words, int* __restrict__ dev_status, int skip_publish_part,
-                const int* __restrict__ run_only_if, const int* __restrict__ n_dev)
+                const int* __restrict__ n_dev)
 {
-    // Passes of the plain six-digit sort are launched behind the tile-bucketed path and do nothing unless
-    // that path found a tile list too long for its in-block sort.
-    if (run_only_if != nullptr && *run_only_if == 0) return;
     if (n_dev != nullptr) {
         n = device_count(n, n_dev);
         num_parts = (n + SORT_PART - 1) / SORT_PART;
@@ -522,7 +518,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
 // One thread per tile value: [first, one-past-last) of that tile in the tile-grouped list, by binary search;
 // non-empty tiles are appended to the work list of their length class.
 __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict__ n_dev, int tile_values,
-                                uint32_t tile_mask, int2* __restrict__ seg, int* __restrict__ too_long,
+                                uint32_t tile_mask, int2* __restrict__ seg,
                                 int* __restrict__ class_count, uint32_t* __restrict__ class_tiles)
 {
     n = device_count(n, n_dev);
@@ -540,11 +536,108 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
     const int last = (t + 1 == tile_values) ? n : lower((uint32_t)t + 1u);
     seg[t] = make_int2(first, last);
     const int len = last - first;
-    if (len > LOCAL_CAP) atomicOr(too_long, 1);
-    else if (len > 0) {   // queue the tile for the in-block sort of its length class
+    if (len > 0) {   // queue the tile for the in-block sort of its length class (the last class also takes longer lists)
         const int c = len <= 1024 ? 0 : (len <= 2048 ? 1 : 2);
         class_tiles[(size_t)c * MAX_TILE_VALUES + atomicAdd(class_count + c, 1)] = (uint32_t)t;
     }
+}
+
+// A list longer than the in-block sort's capacity: the block sorts it where it lies, in global memory, by a
+// least-significant-digit radix sort over the 32 depth bits (four stable 8-bit passes; a pass in which every
+// element has the same digit is skipped). The list ping-pongs between its place in the tile-grouped buffers (a)
+// and its place in the output (b) and is copied to the output at the end if it stopped in (a). Stable, so the
+// result is again what a stable sort of the whole pair list gives for this tile.
+template <int THREADS, int ITEMS>
+__device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_t* vb, int n, unsigned char* smem)
+{
+    constexpr int WARPS = THREADS / 32, CHUNK = THREADS * ITEMS;
+    static_assert(THREADS >= RADIX, "thread d owns digit value d");
+    uint32_t* run = reinterpret_cast<uint32_t*>(smem);                      // [RADIX] digit counts, then where each digit's run continues
+    uint16_t* whist = reinterpret_cast<uint16_t*>(smem + RADIX * 4);        // [WARPS][RADIX] per-warp counts of a chunk, then exclusive warp offsets
+    uint32_t* scan = reinterpret_cast<uint32_t*>(smem + RADIX * 4 + WARPS * RADIX * 2);   // [RADIX / 32]
+    int* same = reinterpret_cast<int*>(scan + RADIX / 32);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned lt = lanemask_lt();
+    uint64_t* src_k = ka; uint32_t* src_v = va; uint64_t* dst_k = kb; uint32_t* dst_v = vb;
+    for (int shift = 0; shift < 32; shift += RADIX_BITS) {
+        __syncthreads();   // the previous pass's stores are visible to the block; its shared memory is free
+        if (tid < RADIX) run[tid] = 0;
+        if (tid == 0) *same = 0;
+        __syncthreads();
+        for (int i = tid; i < n; i += THREADS) atomicAdd(&run[((uint32_t)src_k[i] >> shift) & (RADIX - 1)], 1u);
+        __syncthreads();
+        uint32_t count = 0, inc = 0;
+        if (tid < RADIX) {
+            count = run[tid];
+            if (count == (uint32_t)n) *same = 1;
+            inc = count;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(FULL_MASK, inc, o);
+                if (lane >= o) inc += v;
+            }
+            if (lane == 31) scan[warp] = inc;
+        }
+        __syncthreads();
+        if (tid < RADIX) {
+            uint32_t off = 0;
+            for (int w = 0; w < warp; w++) off += scan[w];
+            run[tid] = off + inc - count;
+        }
+        __syncthreads();
+        if (*same) continue;   // nothing would move
+        for (int c0 = 0; c0 < n; c0 += CHUNK) {
+            for (int i = tid; i < WARPS * RADIX / 2; i += THREADS) reinterpret_cast<uint32_t*>(whist)[i] = 0;
+            __syncthreads();
+            uint64_t key[ITEMS];
+            uint32_t val[ITEMS], rank[ITEMS];
+            const int wb = c0 + warp * (32 * ITEMS);   // warp-striped: item q of lane l is element wb + q*32 + l
+#pragma unroll
+            for (int q = 0; q < ITEMS; q++) {
+                const int i = wb + q * 32 + lane;
+                const bool ok = i < n;
+                key[q] = ok ? src_k[i] : 0ull;
+                val[q] = ok ? src_v[i] : 0u;
+            }
+#pragma unroll
+            for (int q = 0; q < ITEMS; q++) {
+                const bool ok = wb + q * 32 + lane < n;
+                const uint32_t d = ((uint32_t)key[q] >> shift) & (RADIX - 1);
+                const unsigned peers = match_digit(d) & __ballot_sync(FULL_MASK, ok);
+                const uint32_t pre = whist[warp * RADIX + d];
+                __syncwarp();
+                if (ok && (peers & lt) == 0) whist[warp * RADIX + d] = (uint16_t)(pre + __popc(peers));
+                rank[q] = pre + __popc(peers & lt);
+                __syncwarp();
+            }
+            __syncthreads();
+            uint32_t chunk_count = 0;
+            if (tid < RADIX) {
+                for (int w = 0; w < WARPS; w++) {
+                    const uint32_t c = whist[w * RADIX + tid];
+                    whist[w * RADIX + tid] = (uint16_t)chunk_count;
+                    chunk_count += c;
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int q = 0; q < ITEMS; q++) {
+                if (wb + q * 32 + lane < n) {
+                    const uint32_t d = ((uint32_t)key[q] >> shift) & (RADIX - 1);
+                    const uint32_t pos = run[d] + whist[warp * RADIX + d] + rank[q];
+                    dst_k[pos] = key[q];
+                    dst_v[pos] = val[q];
+                }
+            }
+            __syncthreads();
+            if (tid < RADIX) run[tid] += chunk_count;
+        }
+        uint64_t* tk = src_k; src_k = dst_k; dst_k = tk;
+        uint32_t* tv = src_v; src_v = dst_v; dst_v = tv;
+    }
+    __syncthreads();
+    if (src_k != kb)
+        for (int i = tid; i < n; i += THREADS) { kb[i] = src_k[i]; vb[i] = src_v[i]; }
 }
 
 // One block per tile: order the tile's pairs by (depth bits, position inside the tile's list) in shared memory,
@@ -578,11 +671,13 @@ __device__ unsigned long long g_local_cycles[8];
 #define FGS_LT(i) do { } while (0)
 #endif
 
-template <int CAP, int THREADS>
-__global__ void __launch_bounds__(THREADS)
-local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __restrict__ vals_grouped,
+// BLOCKS: resident blocks per SM that the shared-memory footprint allows; it caps the registers accordingly.
+// The tile-grouped buffers are not const: the long-list path of the last class uses them as its second buffer.
+template <int CAP, int THREADS, int BLOCKS>
+__global__ void __launch_bounds__(THREADS, BLOCKS)
+local_sort_kernel(uint64_t* keys_grouped, uint32_t* vals_grouped,
                   uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
-                  const int2* __restrict__ seg, const int* __restrict__ too_long,
+                  const int2* __restrict__ seg,
                   const int* __restrict__ work_count, const uint32_t* __restrict__ work_tiles, int* __restrict__ work_ticket)
 {
     constexpr int NB = local_buckets(CAP);   // depth buckets
@@ -596,7 +691,6 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     __shared__ int s_piled;
     __shared__ int2 s_seg;   // the list the block sorts next; y < x: none
 
-    if (*too_long) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 #ifdef FGS_SORT_TIMING
     long long lt_prev_ = clock64();
@@ -622,6 +716,17 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     while (r.y >= r.x) {
     const int n = r.y - r.x;
     __syncthreads();   // the previous list's shared memory, and s_seg, are no longer read
+    if constexpr (CAP == LOCAL_CAP) if (n > CAP) {
+        long_list_sort<THREADS, ITEMS>(keys_grouped + r.x, vals_grouped + r.x, keys_out + r.x, vals_out + r.x, n, s_local);
+        if (tid == 0) {
+            const int w = atomicAdd(work_ticket, 1);
+            s_seg = w < work ? seg[work_tiles[w]] : make_int2(0, -1);
+        }
+        __syncthreads();
+        r = s_seg;
+        fetch(r, kk);
+        continue;
+    }
     int next_ticket = 0;
     if (tid == 0) { s_min = 0xFFFFFFFFu; s_max = 0u; s_piled = 0; next_ticket = atomicAdd(work_ticket, 1); }
     for (int i = tid; i < NB; i += THREADS) cursor[i] = 0;
@@ -807,7 +912,7 @@ namespace fgs {
 int g_debug_plain_sort = 0;
 
 // Launch kinds reported by the profiling entry point.
-enum { LAUNCH_HISTOGRAM = 0, LAUNCH_DIGIT_PASS = 1, LAUNCH_SEGMENTS = 2, LAUNCH_LOCAL_SORT = 3, LAUNCH_STANDBY_PASS = 4 };
+enum { LAUNCH_HISTOGRAM = 0, LAUNCH_DIGIT_PASS = 1, LAUNCH_SEGMENTS = 2, LAUNCH_LOCAL_SORT = 3 };
 constexpr int MAX_LAUNCHES = 2 * MAX_PASSES + 8;
 
 // `events`, when given, receives one recorded event before the first kernel and one after every kernel;
@@ -846,7 +951,6 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
 
     char* base = static_cast<char*>(temp);
     uint32_t* tickets = reinterpret_cast<uint32_t*>(base + L.tickets_off);
-    int* too_long = reinterpret_cast<int*>(base + L.flag_off);
     uint32_t* hist = reinterpret_cast<uint32_t*>(base + L.hist_off);
     uint32_t* status_words = reinterpret_cast<uint32_t*>(base + L.status_off);
     int2* seg = reinterpret_cast<int2*>(base + L.seg_off);
@@ -864,8 +968,8 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
 #define FGS_OPT_IN(SHIFT) if (e == cudaSuccess) e = cudaFuncSetAttribute(onesweep_kernel<SHIFT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SORT_SMEM_BYTES);
         FGS_OPT_IN(0) FGS_OPT_IN(8) FGS_OPT_IN(16) FGS_OPT_IN(24) FGS_OPT_IN(32) FGS_OPT_IN(40) FGS_OPT_IN(48) FGS_OPT_IN(56)
 #undef FGS_OPT_IN
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<LOCAL_CAP, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<LOCAL_CAP>());
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<2048, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<2048>());
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<LOCAL_CAP, 256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<LOCAL_CAP>());
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<2048, 256, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<2048>());
         if (e != cudaSuccess) return FGS_ERR_CUDA;
         smem_opt_in[dev] = true;
     }
@@ -887,15 +991,14 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     };
     if (events) cudaEventRecord(events[0], st);
     int hist_blocks = L.parts < 148 * 8 ? L.parts : 148 * 8;
-    // the bucketed path needs the tile digits' counts only; the depth digits' are counted on stand-by
-    histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, n_dev, bucketed ? depth_passes : 0, passes, end_bit, hist, nullptr);
+    // the bucketed path needs the tile digits' counts only
+    histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, n_dev, bucketed ? depth_passes : 0, passes, end_bit, hist);
     mark(LAUNCH_HISTOGRAM);
 
     const int resident = 2 * sm_count[dev];   // persistent blocks, two per SM
     const int grid_blocks = L.parts < resident ? L.parts : resident;
     // one digit pass: digit `p` of the key, bookkeeping slot `slot`
-    auto digit_pass = [&](int p, int slot, const uint64_t* src_k, const uint32_t* src_v, uint64_t* dst_k, uint32_t* dst_v,
-                          const int* run_only_if) -> int {
+    auto digit_pass = [&](int p, int slot, const uint64_t* src_k, const uint32_t* src_v, uint64_t* dst_k, uint32_t* dst_v) -> int {
         const int shift = p * RADIX_BITS;
         const int bits = (end_bit - shift) < RADIX_BITS ? (end_bit - shift) : RADIX_BITS;
         const int use_bulk = aligned16(src_k) && aligned16(src_v);
@@ -903,7 +1006,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     case SHIFT:                                                                                                    \
         onesweep_kernel<SHIFT><<<grid_blocks, PASS_THREADS, SORT_SMEM_BYTES, st>>>(                                \
             src_k, src_v, dst_k, dst_v, n, L.parts, (1u << bits) - 1u, use_bulk, tickets + slot, hist + p * RADIX, \
-            status_words + (size_t)slot * L.parts * RADIX, dev_status, g_debug_skip_publish_part, run_only_if, n_dev); \
+            status_words + (size_t)slot * L.parts * RADIX, dev_status, g_debug_skip_publish_part, n_dev); \
         break;
         switch (shift) {
             FGS_PASS(0) FGS_PASS(8) FGS_PASS(16) FGS_PASS(24) FGS_PASS(32) FGS_PASS(40) FGS_PASS(48) FGS_PASS(56)
@@ -921,7 +1024,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
             const bool to_alt = ((tile_passes - 1 - i) & 1) == 0;
             uint64_t* dst_k = to_alt ? alt_keys : keys_sorted;
             uint32_t* dst_v = to_alt ? alt_vals : values_sorted;
-            if (digit_pass(depth_passes + i, passes + i, src_k, src_v, dst_k, dst_v, nullptr) != FGS_OK) return FGS_ERR_BAD_ARG;
+            if (digit_pass(depth_passes + i, passes + i, src_k, src_v, dst_k, dst_v) != FGS_OK) return FGS_ERR_BAD_ARG;
             mark(LAUNCH_DIGIT_PASS);
             src_k = dst_k;
             src_v = dst_v;
@@ -929,35 +1032,31 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         const int tile_values = 1 << tile_bits;
         int* class_count = reinterpret_cast<int*>(base + L.flag_off) + 1;   // behind the flag, cleared above: three list lengths, three tickets
         uint32_t* class_tiles = reinterpret_cast<uint32_t*>(base + L.class_off);
-        segments_kernel<<<(tile_values + 255) / 256, 256, 0, st>>>(alt_keys, n, n_dev, tile_values, (uint32_t)tile_values - 1u, seg, too_long,
+        segments_kernel<<<(tile_values + 255) / 256, 256, 0, st>>>(alt_keys, n, n_dev, tile_values, (uint32_t)tile_values - 1u, seg,
                                                                   class_count, class_tiles);
         mark(LAUNCH_SEGMENTS);
         const int sms = sm_count[dev];
         auto grid_for = [&](int per_sm) { return tile_values < per_sm * sms ? tile_values : per_sm * sms; };
-        local_sort_kernel<1024, 128><<<grid_for(12), 128, local_smem_bytes<1024>(), st>>>(
-            alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long, class_count + 0, class_tiles, class_count + 3);
+        local_sort_kernel<1024, 128, 9><<<grid_for(12), 128, local_smem_bytes<1024>(), st>>>(
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 0, class_tiles, class_count + 3);
         mark(LAUNCH_LOCAL_SORT);
-        local_sort_kernel<2048, 256><<<grid_for(6), 256, local_smem_bytes<2048>(), st>>>(
-            alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long, class_count + 1, class_tiles + MAX_TILE_VALUES, class_count + 4);
+        local_sort_kernel<2048, 256, 4><<<grid_for(6), 256, local_smem_bytes<2048>(), st>>>(
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 1, class_tiles + MAX_TILE_VALUES, class_count + 4);
         mark(LAUNCH_LOCAL_SORT);
-        local_sort_kernel<LOCAL_CAP, 256><<<grid_for(3), 256, local_smem_bytes<LOCAL_CAP>(), st>>>(
-            alt_keys, alt_vals, keys_sorted, values_sorted, seg, too_long, class_count + 2, class_tiles + 2 * MAX_TILE_VALUES, class_count + 5);
+        local_sort_kernel<LOCAL_CAP, 256, 2><<<grid_for(3), 256, local_smem_bytes<LOCAL_CAP>(), st>>>(
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 2, class_tiles + 2 * MAX_TILE_VALUES, class_count + 5);
         mark(LAUNCH_LOCAL_SORT);
     }
-    // the plain sort: all digits, least significant first; behind the bucketed path it only runs if that gave up
-    if (bucketed) {
-        histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, n_dev, 0, depth_passes, end_bit, hist, too_long);
-        mark(LAUNCH_STANDBY_PASS);
-    }
-    {
+    // the plain sort: all digits, least significant first (images with more tiles than the bucketed path takes)
+    if (!bucketed) {
         const uint64_t* src_k = keys_unsorted;
         const uint32_t* src_v = values_unsorted;
         for (int p = 0; p < passes; p++) {
             const bool to_out = ((passes - 1 - p) & 1) == 0;
             uint64_t* dst_k = to_out ? keys_sorted : alt_keys;
             uint32_t* dst_v = to_out ? values_sorted : alt_vals;
-            if (digit_pass(p, p, src_k, src_v, dst_k, dst_v, bucketed ? too_long : nullptr) != FGS_OK) return FGS_ERR_BAD_ARG;
-            mark(bucketed ? LAUNCH_STANDBY_PASS : LAUNCH_DIGIT_PASS);
+            if (digit_pass(p, p, src_k, src_v, dst_k, dst_v) != FGS_OK) return FGS_ERR_BAD_ARG;
+            mark(LAUNCH_DIGIT_PASS);
             src_k = dst_k;
             src_v = dst_v;
         }

@@ -137,8 +137,7 @@ int fgs_sort_pairs_static(int num_rendered, int width, int height, int block_x, 
 /*
  * fgs_sort_pairs with CUDA events recorded around each of its kernel launches; waits for the stream and
  * fills launch_ms[i] and launch_kind[i] for every launch i (kinds: 0 histogram, 1 digit pass, 2 tile
- * segments, 3 in-block tile sort, 4 stand-by digit pass that returns at once unless a tile list was too
- * long for the in-block sort); *num_launches receives the count (0 when num_rendered is 0). Both arrays
+ * segments, 3 in-block tile sort); *num_launches receives the count (0 when num_rendered is 0). Both arrays
  * must hold `capacity` >= 24 entries. A measurement aid for benchmarks: it creates and destroys events
  * and blocks the host, so it is not for the frame loop. No counterpart in the reference.
  */

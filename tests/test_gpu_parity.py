@@ -326,9 +326,11 @@ def test_bucketed_and_plain_sort_agree(ops):
         tk, ti = torch.sort(ki, stable=True)
         assert (tk == outs[0][0]).all() and (vi[ti] == outs[0][1]).all()
     # one tile whose depths pile up at two values (the bucket sort hands over to the bitonic network), one tile
-    # with all depths equal, and a list too long for the in-block sort (the stand-by digit passes take over)
-    for n, depths in ((3000, [1, 1 << 30]), (3000, [12345]), (6000, [1, 1 << 30]), (4096, list(range(1, 4097)))):
-        keys = rng.choice(np.array(depths, dtype=np.uint64), n)
+    # with all depths equal, and lists too long for the in-block sort (sorted by the block's radix passes in
+    # global memory): two depth values, all depths equal, every depth byte in use, a ragged last chunk
+    for n, depths in ((3000, [1, 1 << 30]), (3000, [12345]), (6000, [1, 1 << 30]), (4096, list(range(1, 4097))),
+                      (4097, [7]), (50000, [12345]), (100003, None), (8192, None), (12289, [3, 1 << 8, 1 << 16, 1 << 24])):
+        keys = rng.integers(0, 1 << 32, n, dtype=np.uint64) if depths is None else rng.choice(np.array(depths, dtype=np.uint64), n)
         ki, vi = _t(keys.view(np.int64)), _t(np.arange(n, dtype=np.int32))
         ko, vo = torch.zeros_like(ki), torch.zeros_like(vi)
         tmp = torch.zeros(ops.get_sort_buffer_size(n), device=DEV, dtype=torch.int8)
@@ -336,6 +338,27 @@ def test_bucketed_and_plain_sort_agree(ops):
         torch.cuda.synchronize()
         tk, ti = torch.sort(ki, stable=True)
         assert (tk == ko).all() and (vi[ti] == vo).all()
+    assert ops.device_status() == 0
+
+
+def test_long_tile_lists_among_short_ones(ops, oracle_lib):
+    """Close-up views pile tens of thousands of splats on some tiles: those lists take the long-list path of the tile
+    sort while their neighbours take the in-block sorts; the result is the stable sort of the whole list, and bits
+    above the sorted width travel with their keys."""
+    rng = np.random.default_rng(11)
+    W, H = 800, 800
+    tiles = 50 * 50
+    n = 600000
+    t = rng.integers(0, tiles, n, dtype=np.uint64)
+    t[:150000] = rng.choice(np.array([3, 4, 1200, 2499], dtype=np.uint64), 150000)   # four lists of about 37500
+    t[150000:160000] = 77                                                             # and one of about 10000
+    depth = rng.integers(0, 1 << 32, n, dtype=np.uint64)
+    depth[rng.random(n) < 0.3] &= np.uint64(0xFFFF0000)                               # many equal depths
+    keys = (t << np.uint64(32)) | depth
+    vals = np.arange(n, dtype=np.uint32)
+    _sort_case(ops, oracle_lib, keys, vals, W, H)
+    junk = keys | (rng.integers(0, 1 << 19, n, dtype=np.uint64) << np.uint64(44))
+    _sort_case(ops, oracle_lib, junk, vals, W, H)
     assert ops.device_status() == 0
 
 
