@@ -48,7 +48,7 @@ constexpr int MAX_PASSES = 8;
 constexpr int MAX_TILE_BITS = 16;                        // tile-bucketed path: at most 2^16 tile values
 constexpr int MAX_TILE_VALUES = 1 << MAX_TILE_BITS;
 constexpr int LOCAL_CAP = 4096;
-constexpr int LOCAL_CLASSES = 3;                        // list-length classes of the in-block sort: <=1024, <=2048, <=LOCAL_CAP                         // longest tile list the in-block sort takes
+constexpr int LOCAL_CLASSES = 4;                        // list-length classes of the tile sort: <=1024, <=2048, <=LOCAL_CAP, longer
 constexpr int HIST_THREADS = 256;
 static_assert(RADIX <= SORT_THREADS, "thread d < RADIX owns digit value d in the scans and the look-back");
 
@@ -536,8 +536,8 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
     const int last = (t + 1 == tile_values) ? n : lower((uint32_t)t + 1u);
     seg[t] = make_int2(first, last);
     const int len = last - first;
-    if (len > 0) {   // queue the tile for the in-block sort of its length class (the last class also takes longer lists)
-        const int c = len <= 1024 ? 0 : (len <= 2048 ? 1 : 2);
+    if (len > 0) {   // queue the tile for the sort of its length class
+        const int c = len <= 1024 ? 0 : (len <= 2048 ? 1 : (len <= LOCAL_CAP ? 2 : 3));
         class_tiles[(size_t)c * MAX_TILE_VALUES + atomicAdd(class_count + c, 1)] = (uint32_t)t;
     }
 }
@@ -547,28 +547,61 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
 // element has the same digit is skipped). The list ping-pongs between its place in the tile-grouped buffers (a)
 // and its place in the output (b) and is copied to the output at the end if it stopped in (a). Stable, so the
 // result is again what a stable sort of the whole pair list gives for this tile.
+constexpr int LONG_THREADS = 512, LONG_ITEMS = 8;
+// bookkeeping (4 histograms, run, lstart, per-warp counts, scan, flag) in front of the reordered chunk
+constexpr int LONG_BOOK_BYTES = (6 * RADIX * 4 + (LONG_THREADS / 32) * RADIX * 2 + (RADIX / 32) * 4 + 16 + 15) / 16 * 16;
+constexpr int LONG_SMEM_BYTES = LONG_BOOK_BYTES + LONG_THREADS * LONG_ITEMS * 12;
+
 template <int THREADS, int ITEMS>
 __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_t* vb, int n, unsigned char* smem)
 {
-    constexpr int WARPS = THREADS / 32, CHUNK = THREADS * ITEMS;
+    constexpr int WARPS = THREADS / 32, CHUNK = THREADS * ITEMS, PASSES = 32 / RADIX_BITS;
     static_assert(THREADS >= RADIX, "thread d owns digit value d");
-    uint32_t* run = reinterpret_cast<uint32_t*>(smem);                      // [RADIX] digit counts, then where each digit's run continues
-    uint16_t* whist = reinterpret_cast<uint16_t*>(smem + RADIX * 4);        // [WARPS][RADIX] per-warp counts of a chunk, then exclusive warp offsets
-    uint32_t* scan = reinterpret_cast<uint32_t*>(smem + RADIX * 4 + WARPS * RADIX * 2);   // [RADIX / 32]
-    int* same = reinterpret_cast<int*>(scan + RADIX / 32);
+    static_assert(THREADS == LONG_THREADS && ITEMS == LONG_ITEMS, "the shared-memory layout is sized for these");
+    uint32_t* hist = reinterpret_cast<uint32_t*>(smem);                     // [PASSES][RADIX] digit counts of the whole list
+    uint32_t* run = hist + PASSES * RADIX;                                  // [RADIX] where each digit's run continues
+    uint16_t* whist = reinterpret_cast<uint16_t*>(run + RADIX);             // [WARPS][RADIX] per-warp counts of a chunk, then exclusive warp offsets
+    uint32_t* scan = reinterpret_cast<uint32_t*>(whist + WARPS * RADIX);    // [RADIX / 32]
+    uint32_t* lstart = scan + RADIX / 32;                                   // [RADIX] where a digit's run starts inside the reordered chunk
+    int* same = reinterpret_cast<int*>(lstart + RADIX);
+    uint64_t* stage_k = reinterpret_cast<uint64_t*>(smem + LONG_BOOK_BYTES);       // [CHUNK] the chunk, reordered by digit
+    uint32_t* stage_v = reinterpret_cast<uint32_t*>(smem + LONG_BOOK_BYTES + CHUNK * 8);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const unsigned lt = lanemask_lt();
+    // all four digit histograms from one read of the list
+    for (int i = tid; i < PASSES * RADIX; i += THREADS) hist[i] = 0;
+    __syncthreads();
+    for (int i0 = 0; i0 < n; i0 += THREADS * 4) {
+        uint32_t dw[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + u * THREADS + tid;
+            dw[u] = i < n ? (uint32_t)ka[i] : 0u;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const bool ok = i0 + u * THREADS + tid < n;
+            const unsigned live = __ballot_sync(FULL_MASK, ok);
+#pragma unroll
+            for (int p = 0; p < PASSES; p++) {
+                const uint32_t d = (dw[u] >> (p * RADIX_BITS)) & (RADIX - 1);
+                // depths of one tile often share their upper digits: one add for the warp instead of 32 colliding ones
+                const uint32_t d0 = __shfl_sync(FULL_MASK, d, __ffs(live | 0x80000000u) - 1);
+                const bool uniform = __all_sync(FULL_MASK, !ok || d == d0);
+                if (uniform) { if (ok && (live & lt) == 0) atomicAdd(&hist[p * RADIX + d], (uint32_t)__popc(live)); }
+                else if (ok) atomicAdd(&hist[p * RADIX + d], 1u);
+            }
+        }
+    }
     uint64_t* src_k = ka; uint32_t* src_v = va; uint64_t* dst_k = kb; uint32_t* dst_v = vb;
-    for (int shift = 0; shift < 32; shift += RADIX_BITS) {
-        __syncthreads();   // the previous pass's stores are visible to the block; its shared memory is free
-        if (tid < RADIX) run[tid] = 0;
+    for (int pass = 0; pass < PASSES; pass++) {
+        const int shift = pass * RADIX_BITS;
+        __syncthreads();   // the histograms are complete; the previous pass's stores are visible to the block
         if (tid == 0) *same = 0;
-        __syncthreads();
-        for (int i = tid; i < n; i += THREADS) atomicAdd(&run[((uint32_t)src_k[i] >> shift) & (RADIX - 1)], 1u);
         __syncthreads();
         uint32_t count = 0, inc = 0;
         if (tid < RADIX) {
-            count = run[tid];
+            count = hist[pass * RADIX + tid];
             if (count == (uint32_t)n) *same = 1;
             inc = count;
 #pragma unroll
@@ -585,7 +618,7 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
             run[tid] = off + inc - count;
         }
         __syncthreads();
-        if (*same) continue;   // nothing would move
+        if (*same) continue;   // every element has the same digit: nothing would move
         for (int c0 = 0; c0 < n; c0 += CHUNK) {
             for (int i = tid; i < WARPS * RADIX / 2; i += THREADS) reinterpret_cast<uint32_t*>(whist)[i] = 0;
             __syncthreads();
@@ -611,23 +644,49 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
                 __syncwarp();
             }
             __syncthreads();
-            uint32_t chunk_count = 0;
+            // thread d: the chunk's count of digit d, the warps' exclusive offsets inside it, and (scan over the
+            // digits) where its run starts in the reordered chunk
+            uint32_t chunk_count = 0, cinc = 0;
             if (tid < RADIX) {
                 for (int w = 0; w < WARPS; w++) {
                     const uint32_t c = whist[w * RADIX + tid];
                     whist[w * RADIX + tid] = (uint16_t)chunk_count;
                     chunk_count += c;
                 }
+                cinc = chunk_count;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t v = __shfl_up_sync(FULL_MASK, cinc, o);
+                    if (lane >= o) cinc += v;
+                }
+                if (lane == 31) scan[warp] = cinc;
             }
             __syncthreads();
+            if (tid < RADIX) {
+                uint32_t off = 0;
+                for (int w = 0; w < warp; w++) off += scan[w];
+                lstart[tid] = off + cinc - chunk_count;
+            }
+            __syncthreads();
+            // reorder the chunk in shared memory, then write each digit's run to its place: neighbouring threads
+            // store to neighbouring addresses (scattering element by element costs a memory transaction each)
 #pragma unroll
             for (int q = 0; q < ITEMS; q++) {
                 if (wb + q * 32 + lane < n) {
                     const uint32_t d = ((uint32_t)key[q] >> shift) & (RADIX - 1);
-                    const uint32_t pos = run[d] + whist[warp * RADIX + d] + rank[q];
-                    dst_k[pos] = key[q];
-                    dst_v[pos] = val[q];
+                    const uint32_t pos = lstart[d] + whist[warp * RADIX + d] + rank[q];
+                    stage_k[pos] = key[q];
+                    stage_v[pos] = val[q];
                 }
+            }
+            __syncthreads();
+            const int valid = min(CHUNK, n - c0);
+            for (int j = tid; j < valid; j += THREADS) {
+                const uint64_t k = stage_k[j];
+                const uint32_t d = ((uint32_t)k >> shift) & (RADIX - 1);
+                const uint32_t pos = run[d] + ((uint32_t)j - lstart[d]);
+                dst_k[pos] = k;
+                dst_v[pos] = stage_v[j];
             }
             __syncthreads();
             if (tid < RADIX) run[tid] += chunk_count;
@@ -638,6 +697,25 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
     __syncthreads();
     if (src_k != kb)
         for (int i = tid; i < n; i += THREADS) { kb[i] = src_k[i]; vb[i] = src_v[i]; }
+}
+
+__global__ void __launch_bounds__(LONG_THREADS, 2)
+long_list_kernel(uint64_t* keys_grouped, uint32_t* vals_grouped, uint64_t* keys_out, uint32_t* vals_out,
+                 const int2* __restrict__ seg, const int* __restrict__ work_count, const uint32_t* __restrict__ work_tiles,
+                 int* __restrict__ work_ticket)
+{
+    extern __shared__ __align__(16) unsigned char s_long[];   // LONG_SMEM_BYTES
+    __shared__ int s_w;
+    const int work = *work_count;
+    for (;;) {   // persistent blocks draw lists from the class's work list
+        __syncthreads();
+        if (threadIdx.x == 0) s_w = atomicAdd(work_ticket, 1);
+        __syncthreads();
+        const int w = s_w;
+        if (w >= work) break;
+        const int2 r = seg[work_tiles[w]];
+        long_list_sort<LONG_THREADS, LONG_ITEMS>(keys_grouped + r.x, vals_grouped + r.x, keys_out + r.x, vals_out + r.x, r.y - r.x, s_long);
+    }
 }
 
 // One block per tile: order the tile's pairs by (depth bits, position inside the tile's list) in shared memory,
@@ -672,10 +750,9 @@ __device__ unsigned long long g_local_cycles[8];
 #endif
 
 // BLOCKS: resident blocks per SM that the shared-memory footprint allows; it caps the registers accordingly.
-// The tile-grouped buffers are not const: the long-list path of the last class uses them as its second buffer.
 template <int CAP, int THREADS, int BLOCKS>
 __global__ void __launch_bounds__(THREADS, BLOCKS)
-local_sort_kernel(uint64_t* keys_grouped, uint32_t* vals_grouped,
+local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __restrict__ vals_grouped,
                   uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
                   const int2* __restrict__ seg,
                   const int* __restrict__ work_count, const uint32_t* __restrict__ work_tiles, int* __restrict__ work_ticket)
@@ -716,17 +793,6 @@ local_sort_kernel(uint64_t* keys_grouped, uint32_t* vals_grouped,
     while (r.y >= r.x) {
     const int n = r.y - r.x;
     __syncthreads();   // the previous list's shared memory, and s_seg, are no longer read
-    if constexpr (CAP == LOCAL_CAP) if (n > CAP) {
-        long_list_sort<THREADS, ITEMS>(keys_grouped + r.x, vals_grouped + r.x, keys_out + r.x, vals_out + r.x, n, s_local);
-        if (tid == 0) {
-            const int w = atomicAdd(work_ticket, 1);
-            s_seg = w < work ? seg[work_tiles[w]] : make_int2(0, -1);
-        }
-        __syncthreads();
-        r = s_seg;
-        fetch(r, kk);
-        continue;
-    }
     int next_ticket = 0;
     if (tid == 0) { s_min = 0xFFFFFFFFu; s_max = 0u; s_piled = 0; next_ticket = atomicAdd(work_ticket, 1); }
     for (int i = tid; i < NB; i += THREADS) cursor[i] = 0;
@@ -946,7 +1012,10 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     // Tile-bucketed path: digit passes over the tile bits only, then an in-block sort of every tile by depth.
     // It needs the ticket/status slots behind the plain passes' own (passes + tile passes <= MAX_PASSES).
     const int tile_passes = passes - depth_passes;
-    const bool bucketed = !g_debug_plain_sort && tile_bits <= MAX_TILE_BITS && tile_passes >= 1 &&
+    // With lists this long on average, the tile passes plus the long lists' own depth passes are no fewer than
+    // the plain sort's (the count is only known here when it is not on the device).
+    const bool very_long_lists = n_dev == nullptr && (int64_t)n > (int64_t)tiles * 16384;
+    const bool bucketed = !g_debug_plain_sort && !very_long_lists && tile_bits <= MAX_TILE_BITS && tile_passes >= 1 &&
                           passes + tile_passes <= MAX_PASSES;
 
     char* base = static_cast<char*>(temp);
@@ -970,6 +1039,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
 #undef FGS_OPT_IN
         if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<LOCAL_CAP, 256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<LOCAL_CAP>());
         if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<2048, 256, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<2048>());
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(long_list_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LONG_SMEM_BYTES);
         if (e != cudaSuccess) return FGS_ERR_CUDA;
         smem_opt_in[dev] = true;
     }
@@ -1030,7 +1100,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
             src_v = dst_v;
         }
         const int tile_values = 1 << tile_bits;
-        int* class_count = reinterpret_cast<int*>(base + L.flag_off) + 1;   // behind the flag, cleared above: three list lengths, three tickets
+        int* class_count = reinterpret_cast<int*>(base + L.flag_off) + 1;   // behind the spare word, cleared above: the classes' list lengths, then their tickets
         uint32_t* class_tiles = reinterpret_cast<uint32_t*>(base + L.class_off);
         segments_kernel<<<(tile_values + 255) / 256, 256, 0, st>>>(alt_keys, n, n_dev, tile_values, (uint32_t)tile_values - 1u, seg,
                                                                   class_count, class_tiles);
@@ -1038,13 +1108,16 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         const int sms = sm_count[dev];
         auto grid_for = [&](int per_sm) { return tile_values < per_sm * sms ? tile_values : per_sm * sms; };
         local_sort_kernel<1024, 128, 9><<<grid_for(12), 128, local_smem_bytes<1024>(), st>>>(
-            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 0, class_tiles, class_count + 3);
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 0, class_tiles, class_count + LOCAL_CLASSES + 0);
         mark(LAUNCH_LOCAL_SORT);
         local_sort_kernel<2048, 256, 4><<<grid_for(6), 256, local_smem_bytes<2048>(), st>>>(
-            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 1, class_tiles + MAX_TILE_VALUES, class_count + 4);
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 1, class_tiles + MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 1);
         mark(LAUNCH_LOCAL_SORT);
         local_sort_kernel<LOCAL_CAP, 256, 2><<<grid_for(3), 256, local_smem_bytes<LOCAL_CAP>(), st>>>(
-            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 2, class_tiles + 2 * MAX_TILE_VALUES, class_count + 5);
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 2, class_tiles + 2 * MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 2);
+        mark(LAUNCH_LOCAL_SORT);
+        long_list_kernel<<<grid_for(2), LONG_THREADS, LONG_SMEM_BYTES, st>>>(
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 3, class_tiles + 3 * MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 3);
         mark(LAUNCH_LOCAL_SORT);
     }
     // the plain sort: all digits, least significant first (images with more tiles than the bucketed path takes)
