@@ -156,6 +156,20 @@ def test_needle_splats_match_oracle(ops, oracle_lib):
     _check_against_oracle(f, o, cam, (16, 16))
 
 
+def test_crowded_tiles_match_oracle(ops, oracle_lib):
+    # a small image of a whole dense scene: a third of the tiles hold far more splats than the in-block sort takes (4096), so the
+    # frame goes through the long-list sort, and the blend's early stop decides almost every tile
+    w = scenes.WORKLOADS["C3"]
+    sc = scenes.make_scene(300000, 16, w.log_scale, seed=5)
+    cam = scenes.look_at_camera(160, 112, 25.0, 50.0, 20.0, 10.0)   # the whole scene in 70 tiles
+    f = Frame(ops, sc, cam)
+    o = oracle_lib.render_frame(sc, cam)
+    lengths = o["ranges"][:, 1] - o["ranges"][:, 0]
+    assert (lengths > 4096).sum() >= 10, lengths.max()
+    _check_against_oracle(f, o, cam, (16, 16))
+    assert ops.device_status() == 0
+
+
 @pytest.mark.parametrize("name,n,size", [("C1", 100000, (800, 800)), ("C4", 300000, (1920, 1080)), ("C3", 200000, (1280, 720))])
 def test_column_culling_changes_nothing(ops, name, n, size):
     """Narrowing each row's column range before the exact tile test must not change the pair set."""
