@@ -38,11 +38,11 @@ constexpr int BLEND_WARPS = FGS_BLEND_WARPS;   // tiles per block (one warp each
 constexpr int BATCH = 32;           // splats per staged batch (one per lane)
 constexpr int STAGES = 2;
 
+constexpr int RANGE_TILES = 256, RANGE_THREADS = RANGE_TILES + 32;
 __global__ void tile_ranges_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict__ n_dev, int num_tiles,
                                    int2* __restrict__ ranges)
 {
-    const int tile = blockIdx.x * blockDim.x + threadIdx.x;
-    if (tile >= num_tiles) return;
+    const int tile = blockIdx.x * RANGE_TILES + threadIdx.x;
     if (n_dev != nullptr) {   // count produced on the device by the same frame (bounded by the buffers' capacity n)
         const int v = *n_dev;
         n = v < 0 ? 0 : (v < n ? v : n);
@@ -56,8 +56,13 @@ __global__ void tile_ranges_kernel(const uint64_t* __restrict__ keys, int n, con
         }
         return lo;
     };
-    const int first = lower((uint32_t)tile);
-    const int last = lower((uint32_t)tile + 1u);
+    // One search per thread: a tile's list ends where the next tile's starts. Threads 0..RANGE_TILES-1 search the
+    // starts of the block's tiles, thread RANGE_TILES the start of the tile behind them.
+    __shared__ int s_first[RANGE_TILES + 1];
+    if (threadIdx.x <= RANGE_TILES) s_first[threadIdx.x] = lower((uint32_t)tile);
+    __syncthreads();
+    if (threadIdx.x >= RANGE_TILES || tile >= num_tiles) return;
+    const int first = s_first[threadIdx.x], last = s_first[threadIdx.x + 1];
     ranges[tile] = (last > first) ? make_int2(first, last) : make_int2(0, 0);
 }
 
@@ -288,7 +293,7 @@ int launch_render(int num_rendered, int width, int height,
     const int num_tiles = grid_x * grid_y;
     if (row_begin < 0) row_begin = 0;
     if (row_end < 0 || row_end > grid_y) row_end = grid_y;
-    tile_ranges_kernel<<<(num_tiles + 255) / 256, 256, 0, st>>>(keys_sorted, num_rendered, n_dev, num_tiles,
+    tile_ranges_kernel<<<(num_tiles + RANGE_TILES - 1) / RANGE_TILES, RANGE_THREADS, 0, st>>>(keys_sorted, num_rendered, n_dev, num_tiles,
                                                                reinterpret_cast<int2*>(ranges));
     if (row_end <= row_begin) return launch_status();
     const int strip_tiles = (row_end - row_begin) * grid_x;
@@ -355,7 +360,7 @@ extern "C" int fgs_render_frame(int P, const float* positions, const float* shs,
 extern "C" int fgs_tile_ranges(int num_rendered, int num_tiles, const uint64_t* keys_sorted, int* ranges, void* stream)
 {
     if (num_rendered < 0 || num_tiles <= 0 || !ranges || (num_rendered > 0 && !keys_sorted)) return FGS_ERR_BAD_ARG;
-    fgs::tile_ranges_kernel<<<(num_tiles + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    fgs::tile_ranges_kernel<<<(num_tiles + fgs::RANGE_TILES - 1) / fgs::RANGE_TILES, fgs::RANGE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
         keys_sorted, num_rendered, nullptr, num_tiles, reinterpret_cast<int2*>(ranges));
     return fgs::launch_status();
 }

@@ -58,6 +58,10 @@ constexpr uint32_t FLAG_MASK = 3u << 30;
 constexpr uint32_t VALUE_MASK = ~FLAG_MASK;
 constexpr int LOOKBACK_MAX_POLLS = 1 << 20;             // x (sleep + one L2 read): gives up after about a second
 constexpr int LOOKBACK_WINDOW = FGS_LOOKBACK_WINDOW;                      // earlier partitions inspected per round trip
+#ifndef FGS_SORT_BLOCKS_PER_SM
+#define FGS_SORT_BLOCKS_PER_SM 2
+#endif
+constexpr int PASS_BLOCKS_PER_SM = FGS_SORT_BLOCKS_PER_SM;   // resident digit-pass blocks per SM (shared memory: two stages each)
 constexpr int STAGE_BYTES = SORT_PART * 12;             // keys + values of one partition
 constexpr int LOOKBACK_SLEEP_NS = FGS_LOOKBACK_SLEEP_NS;
 constexpr int SORT_SMEM_BYTES = 2 * STAGE_BYTES;        // IN stage + OUT stage
@@ -243,7 +247,7 @@ __device__ __forceinline__ uint32_t digit_of(uint64_t key, uint32_t digit_mask)
 }
 
 template <int SHIFT>
-__global__ void __launch_bounds__(PASS_THREADS, 2)
+__global__ void __launch_bounds__(PASS_THREADS, PASS_BLOCKS_PER_SM)
 onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                 uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
                 int n, int num_parts, uint32_t digit_mask, int use_bulk,
@@ -517,13 +521,15 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
 // ---- tile-bucketed path: after the digit passes over the tile bits, every tile's pairs are contiguous ----
 // One thread per tile value: [first, one-past-last) of that tile in the tile-grouped list, by binary search;
 // non-empty tiles are appended to the work list of their length class.
+constexpr int SEG_TILES = 256, SEG_THREADS = SEG_TILES + 32;
 __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict__ n_dev, int tile_values,
                                 uint32_t tile_mask, int2* __restrict__ seg,
                                 int* __restrict__ class_count, uint32_t* __restrict__ class_tiles)
 {
     n = device_count(n, n_dev);
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= tile_values) return;
+    // One search per thread: a tile ends where the next one starts. Threads 0..SEG_TILES-1 of a block search the
+    // starts of the block's tiles, thread SEG_TILES the start of the tile behind them.
+    const int t = blockIdx.x * SEG_TILES + threadIdx.x;
     auto lower = [&](uint32_t v) {
         int lo = 0, hi = n;
         while (lo < hi) {
@@ -532,14 +538,28 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
         }
         return lo;
     };
-    const int first = lower((uint32_t)t);
-    const int last = (t + 1 == tile_values) ? n : lower((uint32_t)t + 1u);
-    seg[t] = make_int2(first, last);
-    const int len = last - first;
-    if (len > 0) {   // queue the tile for the sort of its length class
-        const int c = len <= 1024 ? 0 : (len <= 2048 ? 1 : (len <= LOCAL_CAP ? 2 : 3));
-        class_tiles[(size_t)c * MAX_TILE_VALUES + atomicAdd(class_count + c, 1)] = (uint32_t)t;
+    __shared__ int s_first[SEG_TILES + 1];
+    __shared__ int s_class_count[LOCAL_CLASSES], s_class_base[LOCAL_CLASSES];
+    if (threadIdx.x < LOCAL_CLASSES) s_class_count[threadIdx.x] = 0;
+    if (threadIdx.x <= SEG_TILES) s_first[threadIdx.x] = t < tile_values ? lower((uint32_t)t) : n;
+    __syncthreads();
+    int c = -1, slot = 0;
+    if (threadIdx.x < SEG_TILES && t < tile_values) {
+        const int first = s_first[threadIdx.x], last = s_first[threadIdx.x + 1];
+        seg[t] = make_int2(first, last);
+        const int len = last - first;
+        if (len > 0) {   // queue the tile for the sort of its length class
+            c = len <= 1024 ? 0 : (len <= 2048 ? 1 : (len <= LOCAL_CAP ? 2 : 3));
+            slot = atomicAdd(&s_class_count[c], 1);
+        }
     }
+    // the block reserves its places in the classes' work lists with one atomic per class (tens of thousands of
+    // threads adding to the same four counters take longer than the searches)
+    __syncthreads();
+    if (threadIdx.x < LOCAL_CLASSES && s_class_count[threadIdx.x] > 0)
+        s_class_base[threadIdx.x] = atomicAdd(class_count + threadIdx.x, s_class_count[threadIdx.x]);
+    __syncthreads();
+    if (c >= 0) class_tiles[(size_t)c * MAX_TILE_VALUES + s_class_base[c] + slot] = (uint32_t)t;
 }
 
 // A list longer than the in-block sort's capacity: the block sorts it where it lies, in global memory, by a
@@ -1065,7 +1085,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, n_dev, bucketed ? depth_passes : 0, passes, end_bit, hist);
     mark(LAUNCH_HISTOGRAM);
 
-    const int resident = 2 * sm_count[dev];   // persistent blocks, two per SM
+    const int resident = PASS_BLOCKS_PER_SM * sm_count[dev];   // persistent blocks
     const int grid_blocks = L.parts < resident ? L.parts : resident;
     // one digit pass: digit `p` of the key, bookkeeping slot `slot`
     auto digit_pass = [&](int p, int slot, const uint64_t* src_k, const uint32_t* src_v, uint64_t* dst_k, uint32_t* dst_v) -> int {
@@ -1102,7 +1122,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         const int tile_values = 1 << tile_bits;
         int* class_count = reinterpret_cast<int*>(base + L.flag_off) + 1;   // behind the spare word, cleared above: the classes' list lengths, then their tickets
         uint32_t* class_tiles = reinterpret_cast<uint32_t*>(base + L.class_off);
-        segments_kernel<<<(tile_values + 255) / 256, 256, 0, st>>>(alt_keys, n, n_dev, tile_values, (uint32_t)tile_values - 1u, seg,
+        segments_kernel<<<(tile_values + SEG_TILES - 1) / SEG_TILES, SEG_THREADS, 0, st>>>(alt_keys, n, n_dev, tile_values, (uint32_t)tile_values - 1u, seg,
                                                                   class_count, class_tiles);
         mark(LAUNCH_SEGMENTS);
         const int sms = sm_count[dev];
