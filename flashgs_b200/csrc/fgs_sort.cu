@@ -1030,13 +1030,11 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     const int tile_bits = end_bit - 32;
     const int depth_passes = 32 / RADIX_BITS;
     // Tile-bucketed path: digit passes over the tile bits only, then an in-block sort of every tile by depth.
-    // It needs the ticket/status slots behind the plain passes' own (passes + tile passes <= MAX_PASSES).
     const int tile_passes = passes - depth_passes;
     // With lists this long on average, the tile passes plus the long lists' own depth passes are no fewer than
     // the plain sort's (the count is only known here when it is not on the device).
     const bool very_long_lists = n_dev == nullptr && (int64_t)n > (int64_t)tiles * 16384;
-    const bool bucketed = !g_debug_plain_sort && !very_long_lists && tile_bits <= MAX_TILE_BITS && tile_passes >= 1 &&
-                          passes + tile_passes <= MAX_PASSES;
+    const bool bucketed = !g_debug_plain_sort && !very_long_lists && tile_bits <= MAX_TILE_BITS && tile_passes >= 1;
 
     char* base = static_cast<char*>(temp);
     uint32_t* tickets = reinterpret_cast<uint32_t*>(base + L.tickets_off);
@@ -1064,7 +1062,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         smem_opt_in[dev] = true;
     }
 
-    const int slots = passes + (bucketed ? tile_passes : 0);
+    const int slots = bucketed ? tile_passes : passes;   // ticket counters and look-back regions in use: one per digit pass
     if (n_dev == nullptr) {
         const size_t clear_bytes = L.status_off + (size_t)slots * L.parts * RADIX * 4;
         if (cudaMemsetAsync(base, 0, clear_bytes, st) != cudaSuccess) return FGS_ERR_CUDA;
@@ -1114,7 +1112,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
             const bool to_alt = ((tile_passes - 1 - i) & 1) == 0;
             uint64_t* dst_k = to_alt ? alt_keys : keys_sorted;
             uint32_t* dst_v = to_alt ? alt_vals : values_sorted;
-            if (digit_pass(depth_passes + i, passes + i, src_k, src_v, dst_k, dst_v) != FGS_OK) return FGS_ERR_BAD_ARG;
+            if (digit_pass(depth_passes + i, i, src_k, src_v, dst_k, dst_v) != FGS_OK) return FGS_ERR_BAD_ARG;
             mark(LAUNCH_DIGIT_PASS);
             src_k = dst_k;
             src_v = dst_v;
