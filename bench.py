@@ -79,6 +79,13 @@ class ClockSampler:
         except Exception:
             self.p = None
 
+    def mark(self):
+        """Start of the timed region: samples written from here on are the ones that count."""
+        try:
+            self.mark_at = os.path.getsize(self.f.name)
+        except OSError:
+            self.mark_at = 0
+
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if self.p is None:
@@ -89,8 +96,14 @@ class ClockSampler:
         except Exception:
             self.p.kill()
         self.f.flush()
-        rows = [r.strip().split(", ") for r in open(self.f.name).read().strip().splitlines() if r.strip()]
+        text = open(self.f.name).read()
         os.unlink(self.f.name)
+        parse = lambda t: [r.strip().split(", ") for r in t.strip().splitlines() if r.strip()]  # noqa: E731
+        rows = parse(text[getattr(self, "mark_at", 0):])
+        if len([r for r in rows if len(r) >= 8]) < 2:
+            # a timed region shorter than two sampling periods: take the warm-up's samples (same load) as well
+            rows = parse(text)
+            out["window"] = "warm-up and timed region"
         sm, reasons = [], set()
         for r in rows:
             if len(r) < 8:
@@ -292,13 +305,17 @@ def main():
         return float(t[0])
 
     # ---- device-resident throughput ----
+    sampler = ClockSampler(local_rank)
+    sampler.start()   # before the warm-up: the tool needs a moment before its first sample
+    t_warm = time.perf_counter()
     for _ in range(args.warmup):
+        frame(rows)
+    while time.perf_counter() - t_warm < 0.3:   # keep the GPU under the same load until the sampler is running
         frame(rows)
     K = args.steps
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(K)]
-    sampler = ClockSampler(local_rank)
     barrier()
-    sampler.start()
+    sampler.mark()
     e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_begin.record()
     for k in range(K):
