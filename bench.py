@@ -223,6 +223,8 @@ def main():
     def stage_pre(rows=None):
         ras.curr_offset.fill_(0)
         extra = {} if rows is None else dict(tile_row_begin=rows[0], tile_row_end=rows[1])
+        if args.impl == "ours" and ras.cull_scratch is not None:
+            extra["cull_scratch"] = ras.cull_scratch   # the head of the sort's scratch, idle at this point
         ops.preprocess(ds.position, ds.shs, ds.opacity, ds.cov3d, W, H, 16, 16, tc.position, tc.rotation,
                        tc.focal_x, tc.focal_y, tc.zFar, tc.zNear, ras.points_xy, ras.rgb_depth, ras.conic_opacity,
                        ras.gaussian_keys_unsorted, ras.gaussian_values_unsorted, ras.curr_offset, **extra)

@@ -28,6 +28,8 @@ SIGNATURES = {
                             _p, _p, _p, _p, _p, _i64, _p, _p]),
     "fgs_preprocess_strip": (_i, [_i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _f, _f, _f, _f, _i, _i,
                                   _p, _p, _p, _p, _p, _i64, _p, _p]),
+    "fgs_preprocess_strip_culled": (_i, [_i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _f, _f, _f, _f, _i, _i,
+                                         _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p]),
     "fgs_sort_temp_bytes": (C.c_size_t, [_i64]),
     "fgs_sort_pairs": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p]),
     "fgs_sort_static_max_pairs": (_i, []),

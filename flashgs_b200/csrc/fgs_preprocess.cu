@@ -211,6 +211,79 @@ __device__ __forceinline__ void stage_floats(float* dst, const float* src, int n
     }
 }
 
+// True when a splat certainly has no tile in the strip of tile rows [cam.row_begin, cam.row_end).
+// The vertical screen variance is at most |row y of J|^2 * trace(Sigma) + 0.3 (J's row has norm
+// focal_y/z * sqrt(1 + (y/z)^2) with y/z clamped, the view rotation preserves norms, the largest eigenvalue of a
+// PSD matrix is at most its trace); the bound is padded by 2 % and a whole tile, so nothing the exact rectangle
+// would keep is dropped. Written so that a NaN (degenerate input) is never dropped.
+__device__ __forceinline__ bool misses_strip(const PreCam& cam, float view_z, float opacity, const float* c3, float projy)
+{
+    const float fz = cam.focal_y / view_z;
+    const float ly = 1.3f * cam.tan_fovy;
+    const float var = fz * fz * (1.0f + ly * ly) * (c3[0] + c3[3] + c3[5]) * 1.02f + 0.3f;
+    const float pw_strip = fmaxf(kLn2 * 8.0f + kLn2 * approx_lg2(opacity), 0.0f);
+    const float reach = 1.414214f * sqrtf(var * pw_strip) * 1.02f + 2.0f + (float)cam.block_y;
+    const float py_strip = ndc_to_pix(projy, cam.H);
+    return py_strip + reach < (float)(cam.row_begin * cam.block_y) || py_strip - reach > (float)(cam.row_end * cam.block_y);
+}
+
+// The same bound for the image's columns: true when the splat certainly lies left or right of the image.
+__device__ __forceinline__ bool misses_columns(const PreCam& cam, float view_z, float opacity, const float* c3, float projx)
+{
+    const float fz = cam.focal_x / view_z;
+    const float lx = 1.3f * cam.tan_fovx;
+    const float var = fz * fz * (1.0f + lx * lx) * (c3[0] + c3[3] + c3[5]) * 1.02f + 0.3f;
+    const float pw = fmaxf(kLn2 * 8.0f + kLn2 * approx_lg2(opacity), 0.0f);
+    const float reach = 1.414214f * sqrtf(var * pw) * 1.02f + 2.0f + (float)cam.block_x;
+    const float px = ndc_to_pix(projx, cam.W);
+    return px + reach < 0.0f || px - reach > (float)(cam.grid_x * cam.block_x);
+}
+
+// Strip rendering, first step: the indices of the Gaussians that pass the near and opacity culls and can reach the
+// strip, appended to list[1...] (list[0] counts them; any order). A rank that renders one strip of N then runs the
+// expensive kernel below on about 1/N of the scene instead of on all of it.
+__global__ void __launch_bounds__(PRE_THREADS)
+strip_cull_kernel(int P, const float* __restrict__ positions, const float* __restrict__ opacities,
+                  const float* __restrict__ cov3ds, const __grid_constant__ PreCam cam, int* __restrict__ list)
+{
+    __shared__ int s_count[PRE_WARPS];
+    __shared__ int s_base;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int i = blockIdx.x * PRE_THREADS + tid;
+    bool keep = false;
+    if (i < P) {
+        const f3 p = { __ldg(positions + 3 * (size_t)i), __ldg(positions + 3 * (size_t)i + 1), __ldg(positions + 3 * (size_t)i + 2) };
+        const f3 p_view = xform4x3(p, cam.view);
+        const float opacity = __ldg(opacities + i);
+        if (!(p_view.z <= 0.2f) && !(255.0f * opacity < 1.0f)) {
+            const float* pm = cam.proj;
+            const float hy = pm[1] * p.x + pm[5] * p.y + pm[9] * p.z + pm[13];
+            const float hw = pm[3] * p.x + pm[7] * p.y + pm[11] * p.z + pm[15];
+            const float projy = hy * (1.0f / (hw + 0.0000001f));
+            float c3[6];
+#pragma unroll
+            for (int q = 0; q < 6; q++) c3[q] = __ldg(cov3ds + 6 * (size_t)i + q);
+            const float hx = pm[0] * p.x + pm[4] * p.y + pm[8] * p.z + pm[12];
+            const float projx = hx * (1.0f / (hw + 0.0000001f));
+            keep = !misses_strip(cam, p_view.z, opacity, c3, projy) && !misses_columns(cam, p_view.z, opacity, c3, projx);
+        }
+    }
+    const unsigned kept = __ballot_sync(FULL_MASK, keep);
+    if (lane == 0) s_count[warp] = __popc(kept);
+    __syncthreads();
+    if (tid == 0) {
+        int total = 0;
+        for (int w = 0; w < PRE_WARPS; w++) total += s_count[w];
+        s_base = total > 0 ? atomicAdd(list, total) : 0;   // one atomic per block
+    }
+    __syncthreads();
+    if (keep) {
+        int at = s_base + __popc(kept & lanemask_lt());
+        for (int w = 0; w < warp; w++) at += s_count[w];
+        list[1 + at] = i;
+    }
+}
+
 // Optional per-phase cycle accounting (compile with -DFGS_PRE_TIMING): thread 0 of every block adds the SM
 // cycles spent in each phase to g_pre_cycles; read with fgs_debug_pre_phase_cycles.
 #ifdef FGS_PRE_TIMING
@@ -228,7 +301,7 @@ preprocess_kernel(int P,
                   const __grid_constant__ PreCam cam,
                   float2* __restrict__ points_xy, float4* __restrict__ rgb_depth, float4* __restrict__ conic_opacity,
                   uint64_t* __restrict__ keys, uint32_t* __restrict__ values, long long capacity,
-                  int* __restrict__ curr_offset, int* __restrict__ status)
+                  int* __restrict__ curr_offset, int* __restrict__ status, const int* __restrict__ list)
 {
     __shared__ __align__(16) float s_pos[PRE_THREADS * 3];
     __shared__ __align__(16) float s_cov[PRE_THREADS * 6];
@@ -245,21 +318,38 @@ preprocess_kernel(int P,
     __shared__ int s_wsum[PRE_WARPS];
     __shared__ int s_wcnt[PRE_WARPS];
     __shared__ int s_tail_base;
+    __shared__ int s_idx[PRE_THREADS];         // scene index of the block's Gaussians
 
 #ifdef FGS_PRE_TIMING
     long long t_prev_ = clock64();
 #endif
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
+    // The block's Gaussians: 256 consecutive ones of the scene, or (strip rendering behind strip_cull_kernel)
+    // 256 consecutive entries of the list of those that can reach the strip.
     const int base = blockIdx.x * PRE_THREADS;
-    const int n_here = min(PRE_THREADS, P - base);
-    if (VEC) {
+    const int total_here = list != nullptr ? min(P, max(list[0], 0)) : P;
+    if (base >= total_here) return;
+    const int n_here = min(PRE_THREADS, total_here - base);
+    if (list != nullptr) {
+        const int i = tid < n_here ? list[1 + base + tid] : 0;
+        s_idx[tid] = i;
+        if (tid < n_here) {
+#pragma unroll
+            for (int q = 0; q < 3; q++) s_pos[3 * tid + q] = __ldg(positions + 3 * (size_t)i + q);
+#pragma unroll
+            for (int q = 0; q < 6; q++) s_cov[6 * tid + q] = __ldg(cov3ds + 6 * (size_t)i + q);
+            s_opa[tid] = __ldg(opacities + i);
+        }
+    } else if (VEC) {
+        s_idx[tid] = base + tid;
         stage_floats_async(s_pos, positions + (size_t)base * 3, n_here * 3);
         stage_floats_async(s_cov, cov3ds + (size_t)base * 6, n_here * 6);
         stage_floats_async(s_opa, opacities + base, n_here);
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else {
+        s_idx[tid] = base + tid;
         stage_floats<false>(s_pos, positions + (size_t)base * 3, n_here * 3);
         stage_floats<false>(s_cov, cov3ds + (size_t)base * 6, n_here * 6);
         stage_floats<false>(s_opa, opacities + base, n_here);
@@ -291,22 +381,8 @@ preprocess_kernel(int P,
             const float p_w = 1.0f / (hw + 0.0000001f);
             const float projx = hx * p_w, projy = hy * p_w;
 
-            if (cam.row_begin > 0 || cam.row_end < cam.grid_y) {
-                // Rendering a strip of tile rows: drop, before the covariance work, splats that cannot reach it.
-                // The vertical screen variance is at most |row y of J|^2 * trace(Sigma) + 0.3 (J's row has norm
-                // focal_y/z * sqrt(1 + (y/z)^2) with y/z clamped, the view rotation preserves norms, the largest
-                // eigenvalue of a PSD matrix is at most its trace); the bound is padded by 2 % and a whole tile,
-                // so nothing the exact rectangle would keep is dropped.
-                const float* c3 = s_cov + 6 * tid;
-                const float fz = cam.focal_y / p_view.z;
-                const float ly = 1.3f * cam.tan_fovy;
-                const float var = fz * fz * (1.0f + ly * ly) * (c3[0] + c3[3] + c3[5]) * 1.02f + 0.3f;
-                const float pw_strip = fmaxf(kLn2 * 8.0f + kLn2 * approx_lg2(opacity), 0.0f);
-                const float reach = 1.414214f * sqrtf(var * pw_strip) * 1.02f + 2.0f + (float)cam.block_y;
-                const float py_strip = ndc_to_pix(projy, cam.H);
-                // written so that a NaN (degenerate input) is never dropped here
-                if (py_strip + reach < (float)(cam.row_begin * cam.block_y) || py_strip - reach > (float)(cam.row_end * cam.block_y)) break;
-            }
+            // rendering a strip of tile rows: drop, before the covariance work, splats that cannot reach it
+            if ((cam.row_begin > 0 || cam.row_end < cam.grid_y) && misses_strip(cam, p_view.z, opacity, s_cov + 6 * tid, projy)) break;
 
             const f3 cov = cov2d(p_orig, cam, s_cov + 6 * tid);
             const float det = (cov.x * cov.z - cov.y * cov.y);
@@ -385,7 +461,7 @@ preprocess_kernel(int P,
             const long long o = first + i;
             if (o >= 0 && o < capacity) {
                 keys[o] = ((uint64_t)e.x << 32) | (uint32_t)s_rect[e.y].w;
-                values[o] = (uint32_t)(base + (int)e.y);
+                values[o] = (uint32_t)s_idx[e.y];
             } else {
                 atomicOr(status, FGS_ERR_PAIR_OVERFLOW);
             }
@@ -503,7 +579,7 @@ preprocess_kernel(int P,
 
     // ---- features of visible Gaussians (preprocess.cu:411-417) ----
     if (tid < n_here && s_vis[tid]) {
-        const int idx = base + tid;
+        const int idx = s_idx[tid];
         float sh[48];
         if (VEC) {
             const float4* s4 = reinterpret_cast<const float4*>(shs + (size_t)idx * 48);
@@ -555,16 +631,17 @@ extern "C" int fgs_debug_pre_phase_cycles(unsigned long long* out8, int reset)
 // range. Both settings must produce the same pair set; the tests compare them.
 extern "C" void fgs_debug_preprocess_no_column_cull(int on) { fgs::g_debug_no_column_cull = on; }
 
-extern "C" int fgs_preprocess_strip(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
-                                    int width, int height, int block_x, int block_y,
-                                    const float* cam_position, const float* cam_rotation,
-                                    float focal_x, float focal_y, float zFar, float zNear,
-                                    int tile_row_begin, int tile_row_end,
-                                    float* points_xy, float* rgb_depth, float* conic_opacity,
-                                    uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
-                                    int* curr_offset, void* stream)
+extern "C" int fgs_preprocess_strip_culled(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                                           int width, int height, int block_x, int block_y,
+                                           const float* cam_position, const float* cam_rotation,
+                                           float focal_x, float focal_y, float zFar, float zNear,
+                                           int tile_row_begin, int tile_row_end,
+                                           float* points_xy, float* rgb_depth, float* conic_opacity,
+                                           uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                                           int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream)
 {
     using namespace fgs;
+    if (cull_scratch != nullptr && cull_scratch_ints < (int64_t)P + 1) return FGS_ERR_TEMP_TOO_SMALL;
     if (P < 0 || width <= 0 || height <= 0 || block_x <= 0 || block_y <= 0 || pair_capacity < 0) return FGS_ERR_BAD_ARG;
     if (!cam_position || !cam_rotation || !curr_offset) return FGS_ERR_BAD_ARG;
     if (P == 0) return FGS_OK;
@@ -589,17 +666,40 @@ extern "C" int fgs_preprocess_strip(int P, const float* positions, const float* 
 
     const bool vec = aligned16(positions) && aligned16(shs) && aligned16(opacities) && aligned16(cov3ds);
     const int groups = (P + PRE_THREADS - 1) / PRE_THREADS;
-    const int blocks = groups;   // one block per 256 Gaussians
+    const int blocks = groups;   // one block per 256 Gaussians (with a list: blocks past its end return at once)
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // A strip with scratch for the index list: first the cheap pass that lists the Gaussians reaching the strip.
+    const bool strip = cam.row_begin > 0 || cam.row_end < cam.grid_y;
+    const int* list = nullptr;
+    if (cull_scratch != nullptr) {
+        if (cudaMemsetAsync(cull_scratch, 0, sizeof(int), st) != cudaSuccess) return FGS_ERR_CUDA;
+        strip_cull_kernel<<<groups, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, cam, cull_scratch);
+        list = cull_scratch;
+    }
     if (vec)
         preprocess_kernel<true><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,
             reinterpret_cast<float2*>(points_xy), reinterpret_cast<float4*>(rgb_depth), reinterpret_cast<float4*>(conic_opacity),
-            keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status);
+            keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status, list);
     else
         preprocess_kernel<false><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,
             reinterpret_cast<float2*>(points_xy), reinterpret_cast<float4*>(rgb_depth), reinterpret_cast<float4*>(conic_opacity),
-            keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status);
+            keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status, list);
     return launch_status();
+}
+
+extern "C" int fgs_preprocess_strip(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                                    int width, int height, int block_x, int block_y,
+                                    const float* cam_position, const float* cam_rotation,
+                                    float focal_x, float focal_y, float zFar, float zNear,
+                                    int tile_row_begin, int tile_row_end,
+                                    float* points_xy, float* rgb_depth, float* conic_opacity,
+                                    uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                                    int* curr_offset, void* stream)
+{
+    return fgs_preprocess_strip_culled(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y,
+                                       cam_position, cam_rotation, focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end,
+                                       points_xy, rgb_depth, conic_opacity, keys_unsorted, values_unsorted, pair_capacity,
+                                       curr_offset, nullptr, 0, stream);
 }
 
 extern "C" int fgs_preprocess(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,

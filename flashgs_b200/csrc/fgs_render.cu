@@ -338,9 +338,14 @@ extern "C" int fgs_render_frame(int P, const float* positions, const float* shs,
     if (pair_capacity <= 0 || pair_capacity >= (1 << 30) || !curr_offset || !out_color || !bg_color || !ranges) return FGS_ERR_BAD_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (cudaMemsetAsync(curr_offset, 0, sizeof(int), st) != cudaSuccess) return FGS_ERR_CUDA;
-    int rc = fgs_preprocess_strip(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y, cam_position, cam_rotation,
-                                  focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end, points_xy, rgb_depth, conic_opacity,
-                                  keys_unsorted, values_unsorted, pair_capacity, curr_offset, stream);
+    // The sort's scratch is idle while preprocess runs: its first P + 1 ints hold the list of the Gaussians that can
+    // reach the image (or the strip); the sort clears its bookkeeping itself before it starts.
+    int* cull_list = (sort_temp != nullptr && aligned16(sort_temp) && sort_temp_bytes >= ((size_t)P + 1) * sizeof(int))
+                         ? static_cast<int*>(sort_temp) : nullptr;
+    int rc = fgs_preprocess_strip_culled(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y, cam_position,
+                                         cam_rotation, focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end, points_xy,
+                                         rgb_depth, conic_opacity, keys_unsorted, values_unsorted, pair_capacity, curr_offset,
+                                         cull_list, cull_list ? (int64_t)P + 1 : 0, stream);
     if (rc != FGS_OK) return rc;
     rc = sort_pairs_device_count((int)pair_capacity, curr_offset, width, height, block_x, block_y, sort_temp, sort_temp_bytes,
                                  keys_unsorted, values_unsorted, keys_sorted, values_sorted, stream);

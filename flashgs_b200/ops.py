@@ -73,8 +73,10 @@ def preprocess(orig_points, shs, opacities, cov3Ds, width, height, block_x, bloc
                position, rotation, focal_x, focal_y, zFar, zNear,
                points_xy, rgb_depth, conic_opacity,
                gaussian_keys_unsorted, gaussian_values_unsorted, curr_offset,
-               tile_row_begin: int = 0, tile_row_end: int = -1) -> None:
-    """csrc/pybind.cpp:122-150. The two trailing keyword arguments restrict the pairs to a strip of tile rows."""
+               tile_row_begin: int = 0, tile_row_end: int = -1, cull_scratch=None) -> None:
+    """csrc/pybind.cpp:122-150. The trailing keyword arguments restrict the pairs to a strip of tile rows;
+    ``cull_scratch`` (int32 CUDA tensor, at least P + 1 elements) lets a strip list the Gaussians that can reach it
+    first and run the expensive kernel on those only."""
     f32 = torch.float32
     pts = _in(orig_points, "orig_points", f32)
     sh = _in(shs, "shs", f32)
@@ -90,13 +92,16 @@ def preprocess(orig_points, shs, opacities, cov3Ds, width, height, block_x, bloc
     off = _out(curr_offset, "curr_offset", torch.int32)
     P = int(op.size(0))
     cap = min(int(keys.numel()), int(vals.numel()))
-    st = _L.fgs_preprocess_strip(P, pts.data_ptr(), sh.data_ptr(), op.data_ptr(), cov.data_ptr(),
-                                 int(width), int(height), int(block_x), int(block_y),
-                                 pos.data_ptr(), rot.data_ptr(),
-                                 float(focal_x), float(focal_y), float(zFar), float(zNear),
-                                 int(tile_row_begin), int(tile_row_end),
-                                 xy.data_ptr(), rd.data_ptr(), co.data_ptr(),
-                                 keys.data_ptr(), vals.data_ptr(), cap, off.data_ptr(), _stream())
+    scratch = None if cull_scratch is None else _out(cull_scratch, "cull_scratch", torch.int32)
+    st = _L.fgs_preprocess_strip_culled(P, pts.data_ptr(), sh.data_ptr(), op.data_ptr(), cov.data_ptr(),
+                                        int(width), int(height), int(block_x), int(block_y),
+                                        pos.data_ptr(), rot.data_ptr(),
+                                        float(focal_x), float(focal_y), float(zFar), float(zNear),
+                                        int(tile_row_begin), int(tile_row_end),
+                                        xy.data_ptr(), rd.data_ptr(), co.data_ptr(),
+                                        keys.data_ptr(), vals.data_ptr(), cap, off.data_ptr(),
+                                        None if scratch is None else scratch.data_ptr(),
+                                        0 if scratch is None else int(scratch.numel()), _stream())
     _lib.check("preprocess", st)
 
 

@@ -63,6 +63,11 @@ class Rasterizer:
         self.rgb_depth = z((scene.num_vertex, 4), torch.float32)
         self.conic_opacity = z((scene.num_vertex, 4), torch.float32)
         self.num_rendered = 0
+        # The sort's scratch is idle while preprocess runs: its head holds preprocess's list of the Gaussians that can
+        # reach the image (P + 1 ints), so that the expensive kernel only runs on those.
+        need = 4 * (scene.num_vertex + 1)
+        ours = hasattr(ops, "render_frame")   # another operator module (the reference's) has no such argument
+        self.cull_scratch = (self.list_sorting_space[:need].view(torch.int32) if ours and self.SORT_BUFFER_SIZE >= need else None)
         self._render = {(16, 16): "render_16x16", (32, 16): "render_32x16", (32, 32): "render_32x32"}[tuple(block)]
 
     def forward(self, scene: DeviceScene, camera, bg_color, out_color=None, rows=None):
@@ -70,6 +75,8 @@ class Rasterizer:
         ops, (bx, by) = self.ops, self.block
         self.curr_offset.fill_(0)
         extra = {} if rows is None else dict(tile_row_begin=rows[0], tile_row_end=rows[1])
+        if self.cull_scratch is not None:
+            extra["cull_scratch"] = self.cull_scratch
         ops.preprocess(scene.position, scene.shs, scene.opacity, scene.cov3d,
                        camera.width, camera.height, bx, by,
                        camera.position, camera.rotation,

@@ -36,7 +36,7 @@ def _t(a, dtype=None):
 class Frame:
     """Runs the three ops stage by stage and keeps every intermediate on the host."""
 
-    def __init__(self, ops, scene, cam, block=(16, 16), capacity=None, rows=None, bg=(0.0, 0.0, 0.0), floats=True):
+    def __init__(self, ops, scene, cam, block=(16, 16), capacity=None, rows=None, bg=(0.0, 0.0, 0.0), floats=True, cull=False):
         P = scene.num_vertex
         bx, by = block
         gx, gy = scenes.tile_grid(cam.width, cam.height, bx, by)
@@ -50,6 +50,8 @@ class Frame:
         self.off = z(1, torch.int32)
         self.cpos, self.crot = torch.from_numpy(cam.position.copy()), torch.from_numpy(cam.rotation.copy())
         extra = {} if rows is None else dict(tile_row_begin=rows[0], tile_row_end=rows[1])
+        if cull:   # scratch for the index list of the Gaussians that reach the strip; its contents do not matter
+            extra["cull_scratch"] = torch.full((P + 1,), 0x7F7F7F7F, device=DEV, dtype=torch.int32)
         ops.preprocess(self.pos, self.shs, self.opa, self.cov, cam.width, cam.height, bx, by, self.cpos, self.crot,
                        cam.focal_x, cam.focal_y, cam.zFar, cam.zNear, self.xy, self.rd, self.co,
                        self.ku, self.vu, self.off, **extra)
@@ -417,25 +419,33 @@ def test_bounded_lookback_wait_reports_timeout(ops):
     assert (torch.sort(ki, stable=True)[0] == ko).all()
 
 
-def test_strips_union_equals_frame(ops):
-    w, sc, cams = scenes.make_workload("C1", 60000)
-    cam = cams[0]
+@pytest.mark.parametrize("name,n,strips,cull", [("C1", 60000, 3, False), ("C1", 60000, 3, True), ("C4", 200000, 8, True)])
+def test_strips_union_equals_frame(ops, name, n, strips, cull):
+    """One frame split into strips of tile rows: the strips' pairs together are the frame's pairs, and the strips'
+    pixels are the frame's pixels -- with and without the index list of the Gaussians that reach a strip."""
+    w, sc, cams = scenes.make_workload(name, n)
+    cam = cams[0] if name == "C1" else scenes.look_at_camera(1280, 720, 12.0, 50.0, 34.0, 17.0)
     full = Frame(ops, sc, cam)
     gy = scenes.tile_grid(cam.width, cam.height)[1]
     from flashgs_b200.parallel import strip_rows
     keys, vals = [], []
     img = np.zeros_like(full.np("img"))
-    for r in range(3):
-        rows = strip_rows(gy, 3, r)
-        part = Frame(ops, sc, cam, rows=rows)
+    for r in range(strips):
+        rows = strip_rows(gy, strips, r)
+        part = Frame(ops, sc, cam, rows=rows, cull=cull)
         keys.append(part.np("ku", part.R)); vals.append(part.np("vu", part.R))
         img[rows[0] * 16: rows[1] * 16] = part.np("img")[rows[0] * 16: rows[1] * 16]
+        vis = np.unique(part.np("vu", part.R))   # feature records of the strip's visible Gaussians are the frame's
+        assert (part.np("xy")[vis].view(np.uint32) == full.np("xy")[vis].view(np.uint32)).all()
+        assert (part.np("rd")[vis].view(np.uint32) == full.np("rd")[vis].view(np.uint32)).all()
+        assert (part.np("co")[vis].view(np.uint32) == full.np("co")[vis].view(np.uint32)).all()
     ka, va = canonical_pairs(np.concatenate(keys), np.concatenate(vals))
     kb, vb = canonical_pairs(full.np("ku", full.R), full.np("vu", full.R))
     assert (ka == kb).all() and (va == vb).all()
     # same per-tile lists -> same pixels (splats of identical depth may swap: allow a few 1-level differences)
     d = np.abs(img.astype(int) - full.np("img").astype(int))
     assert d.max() <= 1 and (d > 0).mean() <= 1e-5
+    assert ops.device_status() == 0
 
 
 def test_rasterizer_loop_matches_stage_calls(ops):
