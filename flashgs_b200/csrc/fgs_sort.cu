@@ -261,7 +261,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
     }
     extern __shared__ __align__(128) unsigned char s_dyn[];   // IN stage | OUT stage, each keys 8*PART | values 4*PART
     __shared__ __align__(8) uint64_t s_bar;                   // completion of the bulk copy into IN
-    __shared__ uint16_t s_whist[SORT_WARPS][RADIX];           // per-warp digit counts, then exclusive warp offsets
+    __shared__ uint32_t s_whist[SORT_WARPS][RADIX];           // per-warp digit counts, then exclusive warp offsets
     __shared__ __align__(16) uint32_t s_count[2][RADIX];      // block digit counts of a partition (by parity)
     __shared__ __align__(16) uint32_t s_gstart[2][RADIX];     // global index where the partition's run of a digit starts
     __shared__ uint32_t s_local_start[2][RADIX];              // where that run starts inside the reordered partition
@@ -416,7 +416,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
         // round trip of the atomic never stalls the block.
         uint32_t ticket_after_next = 0;
         if (tid == 0) ticket_after_next = atomicAdd(ticket, 1u);
-        for (int i = tid; i < SORT_WARPS * RADIX / 2; i += SORT_THREADS) reinterpret_cast<uint32_t*>(&s_whist[0][0])[i] = 0;
+        for (int i = tid; i < SORT_WARPS * RADIX; i += SORT_THREADS) (&s_whist[0][0])[i] = 0;
 
         uint64_t key[SORT_ITEMS];
         uint32_t val[SORT_ITEMS];
@@ -436,23 +436,38 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
             }
         }
         bar_sync(BAR_SORTERS, SORT_THREADS);   // s_whist zeroed; every thread holds its items, IN is free again
-        if (tid == 0) prefetch(it + 1, s_tickets[(it + 1) & 3]);
         FGS_T(0);
 
-        // rank within the warp, item by item, so equal digits keep their input order
+        // Rank within the warp, item by item, so equal digits keep their input order. The lanes holding the same
+        // digit find one another through shared memory: every lane ORs its bit into the warp's word of its digit
+        // and reads the word back (two instructions instead of eight votes and their logic). The words live in
+        // the IN stage, which is free until the next partition's copy is started after this phase; two sets are
+        // used in turn, and the lowest lane of a group clears its word after use, so that a set is clean again
+        // when its turn comes. That lane also adds the group's size to the warp's counter of the digit and hands
+        // the old value to the group.
+        uint32_t* my_masks = reinterpret_cast<uint32_t*>(s_dyn) + warp * (2 * RADIX);
+#pragma unroll
+        for (int i = 0; i < 2 * RADIX / 32; i++) my_masks[i * 32 + lane] = 0;
+        __syncwarp();
         uint32_t rank[SORT_ITEMS];
 #pragma unroll
         for (int i = 0; i < SORT_ITEMS; i++) {
             const uint32_t d = digit_of<SHIFT>(key[i], digit_mask);
-            const unsigned peers = match_digit(d);
-            // every lane of a peer group reads the group's running count, then its lowest lane adds the group
-            const uint32_t pre = s_whist[warp][d];
+            volatile uint32_t* word = my_masks + (i & 1) * RADIX + d;
+            atomicOr(const_cast<uint32_t*>(word), 1u << lane);
             __syncwarp();
-            if ((peers & lt) == 0) s_whist[warp][d] = (uint16_t)(pre + __popc(peers));
+            const unsigned peers = *word;
+            __syncwarp();
+            uint32_t pre = 0;
+            if ((peers & lt) == 0) {
+                *word = 0;
+                pre = atomicAdd(&s_whist[warp][d], (uint32_t)__popc(peers));
+            }
+            pre = __shfl_sync(FULL_MASK, pre, __ffs(peers) - 1);
             rank[i] = pre + __popc(peers & lt);
-            __syncwarp();
         }
         bar_sync(BAR_SORTERS, SORT_THREADS);
+        if (tid == 0) prefetch(it + 1, s_tickets[(it + 1) & 3]);   // IN is no longer used by the ranking
         FGS_T(1);
 
         // thread d owns digit value d: block count, exclusive warp offsets, start of the run inside the partition
@@ -460,7 +475,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
 #pragma unroll
         for (int w = 0; w < SORT_WARPS; w++) {
             const uint32_t c = s_whist[w][tid];
-            s_whist[w][tid] = (uint16_t)count;
+            s_whist[w][tid] = count;
             count += c;
         }
         s_count[b][tid] = count;
