@@ -36,7 +36,7 @@ namespace {
 #define FGS_LOOKBACK_SLEEP_NS 200
 #endif
 #ifndef FGS_LOOKBACK_WINDOW
-#define FGS_LOOKBACK_WINDOW 8
+#define FGS_LOOKBACK_WINDOW 6
 #endif
 constexpr int SORT_THREADS = FGS_SORT_THREADS;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
