@@ -417,6 +417,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
         uint32_t ticket_after_next = 0;
         if (tid == 0) ticket_after_next = atomicAdd(ticket, 1u);
         for (int i = tid; i < SORT_WARPS * RADIX; i += SORT_THREADS) (&s_whist[0][0])[i] = 0;
+        s_count[b][tid] = 0;
 
         uint64_t key[SORT_ITEMS];
         uint32_t val[SORT_ITEMS];
@@ -436,6 +437,17 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
             }
         }
         bar_sync(BAR_SORTERS, SORT_THREADS);   // s_whist zeroed; every thread holds its items, IN is free again
+        // The block's digit counts first, by shared-memory adds, so that they can be published and the look-back of
+        // this partition can start before the ranking instead of after it: the look-back's latency is what the
+        // pass waits for.
+#pragma unroll
+        for (int i = 0; i < SORT_ITEMS; i++) atomicAdd(&s_count[b][digit_of<SHIFT>(key[i], digit_mask)], 1u);
+        bar_sync(BAR_SORTERS, SORT_THREADS);
+        // published by the sorting thread itself, at once: later partitions wait for exactly this word, and the
+        // look-back warps may still be busy with the previous partition
+        if ((int)part != skip_publish_part)
+            st_relaxed(status_words + (size_t)part * RADIX + tid, (part == 0 ? FLAG_INCLUSIVE : FLAG_AGGREGATE) | s_count[b][tid]);
+        bar_arrive(BAR_COUNTS + b, PASS_THREADS);   // the look-back warps take it from here
         FGS_T(0);
 
         // Rank within the warp, item by item, so equal digits keep their input order. The lanes holding the same
@@ -478,11 +490,6 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
             s_whist[w][tid] = count;
             count += c;
         }
-        s_count[b][tid] = count;
-        // published by the sorting thread itself, at once: later partitions wait for exactly this word, and the
-        // look-back warps may still be busy with the previous partition
-        if ((int)part != skip_publish_part)
-            st_relaxed(status_words + (size_t)part * RADIX + tid, (part == 0 ? FLAG_INCLUSIVE : FLAG_AGGREGATE) | count);
         uint32_t inc_l = count;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -490,7 +497,6 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
             if (lane >= o) inc_l += a;
         }
         if (lane == 31) s_scan[warp] = inc_l;
-        bar_arrive(BAR_COUNTS + b, PASS_THREADS);   // the look-back warps take it from here
         bar_sync(BAR_SORTERS, SORT_THREADS);
         {
             uint32_t off_l = 0;
