@@ -124,6 +124,8 @@ __global__ void clear_bookkeeping_kernel(uint32_t* __restrict__ base_words, size
     }
 }
 
+__device__ __forceinline__ bool aligned16_dev(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 // ---- digit histograms of passes [first_pass, last_pass) in one read of the keys ----
 __global__ void __launch_bounds__(HIST_THREADS)
 histogram_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict__ n_dev, int first_pass, int last_pass,
@@ -135,11 +137,23 @@ histogram_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict
     for (int i = threadIdx.x; i < np * RADIX; i += HIST_THREADS) s_hist[i] = 0;
     __syncthreads();
     const uint64_t live = end_bit >= 64 ? ~0ull : ((1ull << end_bit) - 1ull);
-    for (int64_t i = (int64_t)blockIdx.x * HIST_THREADS + threadIdx.x; i < n; i += (int64_t)gridDim.x * HIST_THREADS) {
-        const uint64_t k = (__ldg(keys + i) & live) >> (first_pass * RADIX_BITS);
+    auto count = [&](uint64_t key) {
+        const uint64_t k = (key & live) >> (first_pass * RADIX_BITS);
         for (int p = 0; p < np; p++)
             atomicAdd(&s_hist[p * RADIX + (uint32_t)((k >> (p * RADIX_BITS)) & (RADIX - 1))], 1u);
+    };
+    // two keys per 16-byte load, two loads in flight per thread; the ragged end (and an unaligned array) key by key
+    const int64_t stride = (int64_t)gridDim.x * HIST_THREADS, me = (int64_t)blockIdx.x * HIST_THREADS + threadIdx.x;
+    const int64_t pairs = aligned16_dev(keys) ? n / 2 : 0;
+    const ulonglong2* keys2 = reinterpret_cast<const ulonglong2*>(keys);
+    for (int64_t i = me; i < pairs; i += 2 * stride) {
+        const ulonglong2 a = __ldg(keys2 + i);
+        const bool second = i + stride < pairs;
+        const ulonglong2 c = second ? __ldg(keys2 + i + stride) : make_ulonglong2(0, 0);
+        count(a.x); count(a.y);
+        if (second) { count(c.x); count(c.y); }
     }
+    for (int64_t i = 2 * pairs + me; i < n; i += stride) count(__ldg(keys + i));
     __syncthreads();
     for (int i = threadIdx.x; i < np * RADIX; i += HIST_THREADS) {
         const uint32_t c = s_hist[i];
