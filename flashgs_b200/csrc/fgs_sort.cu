@@ -889,9 +889,11 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
         }
         gathered = true;
     } else {
-        // bucket of a depth: monotone in the depth (conversion and multiplication round monotonically)
-        const float scale = (float)NB / ((float)span + 1.0f);
-        auto bucket_of = [&](uint32_t dd) { return min((int)((float)(dd - dmin) * scale), NB - 1); };
+        // bucket of a depth: the high word of (depth - nearest depth) * mult, with mult about NB * 2^32 / (span + 1)
+        // (rounded in float, hence the clamp): integer arithmetic, monotone in the depth
+        const float ratio = 4294967296.0f * (float)NB / ((float)span + 1.0f);
+        const uint32_t mult = ratio >= 4294967040.0f ? 0xFFFFFFFFu : (uint32_t)ratio;
+        auto bucket_of = [&](uint32_t dd) { return min((int)__umulhi(dd - dmin, mult), NB - 1); };
         // one atomic per element: it counts the bucket and hands the element its arrival number inside it
         uint32_t where[ITEMS];   // bucket | arrival number << 16 (both below 65536)
 #pragma unroll
