@@ -146,6 +146,64 @@ def tile_grid(cam, block=16):
     return (cam.width + block - 1) // block, (cam.height + block - 1) // block
 
 
+def run_view_batch(args, emit, wl, scene, cams, config, rank, local_rank, world):
+    """Independent views of one scene dealt out to the GPUs (scene replicated, no traffic between GPUs): a step is one
+    pass over all views; value = views per second over all GPUs; latency = time of one view on its GPU."""
+    import torch
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    from flashgs_b200 import ops
+    from flashgs_b200.rasterizer import DeviceScene, Rasterizer, TorchCamera
+    ds = DeviceScene(scene, dev)
+    mine = [TorchCamera(c) for c in cams[rank::world]]
+    ras = Rasterizer(ds, 1 << 26 if scene.num_vertex > 2_000_000 else 1 << 24, 1 << 20, ops=ops)
+    bg = torch.zeros(3, dtype=torch.float32)
+    img = torch.zeros((cams[0].height, cams[0].width, 3), device=dev, dtype=torch.int8)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(1, args.warmup // 3)):
+        for tc in mine:
+            ras.forward(ds, tc, bg, out_color=img)
+    K = max(1, args.steps // 10)
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in mine] for _ in range(K)]
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    sampler.mark()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for k in range(K):
+        for i, tc in enumerate(mine):
+            ev[k][i][0].record()
+            ras.forward(ds, tc, bg, out_color=img)
+            ev[k][i][1].record()
+    b.record()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = a.elapsed_time(b)
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t[0])
+    lat = np.array([e[0].elapsed_time(e[1]) for row in ev for e in row])
+    if rank == 0:
+        emit({"metric": "views/sec, %d views of %d Gaussians at %dx%d" % (len(cams), scene.num_vertex, cams[0].width, cams[0].height),
+              "value": K * len(cams) / (total_ms * 1e-3), "unit": "views/s", "n_gpus": world, "steps": K, "warmup": max(1, args.warmup // 3),
+              "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+              "data": "synthetic", "config": dict(config, partition="%d views per GPU, scene replicated, no traffic between GPUs" % len(mine)),
+              "view_latency_ms": {"median": float(np.median(lat)), "max": float(lat.max())}, "clocks": clocks,
+              "gpu_launches": 13 * K * len(mine)})
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     # Libraries (NCCL's version banner, for one) write to stdout; the contract is ONE JSON line there. Everything
     # but that line is sent to stderr: fd 1 is pointed at stderr and the line goes to a saved copy of the real stdout.
@@ -163,6 +221,8 @@ def main():
     ap.add_argument("--cpu-sample", type=float, default=1.0, help="fraction of the frame's tile rows the CPU baseline renders")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--view-batch", action="store_true",
+                    help="render all views of the workload (C5: 64), dealt out to the ranks; a step is one pass over them")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, local_rank, world = dist_env()
@@ -176,6 +236,9 @@ def main():
                         % (wl.radius, wl.hfov_deg),
               "partition": "whole frame" if world == 1 else "%d strips of tile rows, scene replicated" % world,
               "l2": "inputs (%.2f GB scene) larger than L2" % (scene.num_vertex * 232 / 1e9)}
+
+    if args.view_batch:
+        return run_view_batch(args, emit, wl, scene, cams, config, rank, local_rank, world)
 
     if args.impl == "port":
         if rank == 0:
