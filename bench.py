@@ -158,7 +158,8 @@ def run_view_batch(args, emit, wl, scene, cams, config, rank, local_rank, world)
     from flashgs_b200 import ops
     from flashgs_b200.rasterizer import DeviceScene, Rasterizer, TorchCamera
     ds = DeviceScene(scene, dev)
-    mine = [TorchCamera(c) for c in cams[rank::world]]
+    from flashgs_b200 import parallel
+    mine = [TorchCamera(cams[i]) for i in parallel.views_of_rank(len(cams), world, rank)]
     ras = Rasterizer(ds, 1 << 26 if scene.num_vertex > 2_000_000 else 1 << 24, 1 << 20, ops=ops)
     bg = torch.zeros(3, dtype=torch.float32)
     img = torch.zeros((cams[0].height, cams[0].width, 3), device=dev, dtype=torch.int8)

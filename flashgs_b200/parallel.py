@@ -25,6 +25,12 @@ def strip_rows(grid_y: int, world_size: int, rank: int) -> Tuple[int, int]:
     return begin, begin + base + (1 if rank < rem else 0)
 
 
+def views_of_rank(num_views: int, world_size: int, rank: int) -> List[int]:
+    """Independent views of one scene dealt out round-robin (view batches: every rank holds the scene and renders its
+    views alone; nothing crosses between ranks)."""
+    return list(range(rank, num_views, world_size))
+
+
 def balanced_strip_rows(row_cost: List[float], world_size: int) -> List[Tuple[int, int]]:
     """Contiguous strips whose summed cost (e.g. pairs per tile row of the previous frame) is about equal.
 

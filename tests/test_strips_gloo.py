@@ -42,6 +42,11 @@ def _worker(rank, world, port, out_path):
         full = parallel.gather_strips(local, rows, 16, cam.height, dst=0)
         counts = torch.tensor([mine["keys"].size], dtype=torch.int64)
         dist.all_reduce(counts)
+        # view batches: the ranks' views together are every view exactly once
+        seen = torch.zeros(7, dtype=torch.int64)
+        seen[parallel.views_of_rank(7, world, rank)] += 1
+        dist.all_reduce(seen)
+        assert (seen == 1).all()
         if rank == 0:
             ref = oracle.render_frame(sc, cam, floats=False)
             ok = bool((full.numpy() == ref["u8"]).all()) and int(counts[0]) == ref["keys"].size
