@@ -501,6 +501,19 @@ def main():
         done = [torch.cuda.Event() for _ in range(2)]
         keep = [None, None]
         bufs = [out_img, torch.zeros_like(out_img)] if args.impl == "ours" else [out_img, out_img]
+        # Several GPUs: the blend kernels store their strips straight into rank 0's frame buffer (peer memory over
+        # NVLink) when the symmetric-memory mapping can be set up; otherwise the strips are gathered with NCCL.
+        peer = None
+        if use_dist and os.environ.get("FLASHGS_PEER_FRAMES", "1") != "0":
+            try:
+                peer = parallel.PeerFrames(2, H, W, dev, dst=0)
+            except Exception as exc:
+                print("peer frame buffers unavailable (%r): gathering strips with NCCL" % (exc,), file=sys.stderr)
+                peer = None
+            ok = torch.tensor([1 if peer is not None else 0], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok[0]) == 0:
+                peer = None
 
         def e2e_frame(k):
             # the camera of this step comes from pinned host memory
@@ -511,8 +524,23 @@ def main():
                 # the copy of frame k overlaps the kernels of frame k+1: two output buffers
                 done[k % 2].synchronize()
                 out_img = bufs[k % 2]
+            if peer is not None:
+                out_img = peer.frames[k % 2]          # rank 0's buffer, mapped here
             frame(rows)
-            if use_dist:
+            if peer is not None:
+                # Frame k+1 will be written into the buffer of frame k-1: rank 0 joins the barrier only when that
+                # buffer's copy to the host is over, so nobody overwrites it early.
+                if rank == 0:
+                    torch.cuda.current_stream().wait_event(done[(k - 1) % 2])
+                peer.barrier()                        # every strip of frame k has landed in rank 0's buffer
+                if rank == 0:
+                    ready = torch.cuda.Event()
+                    ready.record()
+                    with torch.cuda.stream(copy_stream):
+                        copy_stream.wait_event(ready)
+                        host_img.copy_(peer.frames[k % 2], non_blocking=True)
+                        done[k % 2].record(copy_stream)
+            elif use_dist:
                 # strips -> rank 0 over NCCL, then the copy to the host overlaps the next frame like on one GPU
                 done[k % 2].synchronize()
                 full = parallel.gather_strips(out_img[:H], all_rows, 16, H, dst=0)
@@ -554,8 +582,20 @@ def main():
                "note": "camera (12 floats) read from pinned host memory and handed to the kernel as a parameter block; "
                        "8-bit image copied to pinned host memory every frame"
                        + ("; copy of frame k overlaps frame k+1" if args.impl == "ours" else "")
-                       + ("; strips gathered on rank 0 with one NCCL gather per frame" if use_dist else "")}
+                       + ("; the blend kernels store their strips straight into rank 0's frame buffer (peer memory over "
+                          "NVLink), one device-side barrier per frame" if peer is not None else
+                          ("; strips gathered on rank 0 with one NCCL gather per frame" if use_dist else ""))}
         out_img = bufs[0]
+        if peer is not None:
+            # the image assembled through peer stores against the same frame's strips gathered with NCCL
+            frame(rows)
+            full = parallel.gather_strips(out_img[:H], all_rows, 16, H, dst=0)
+            torch.cuda.synchronize()
+            if rank == 0:
+                same = bool((full.cpu() == host_img).all())
+                e2e["peer_frames_check"] = "identical to the NCCL-gathered strips" if same else "MISMATCH against the NCCL-gathered strips"
+                if not same:
+                    raise RuntimeError("peer frame buffers: image differs from the gathered strips")
 
     status = ops.device_status() if args.impl == "ours" else 0
     # preprocess (+ its cull kernel when it is given scratch), tile ranges, blend + the sort's kernels

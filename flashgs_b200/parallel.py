@@ -89,3 +89,25 @@ def gather_strips(local_image: torch.Tensor, all_rows: List[Tuple[int, int]], bl
         if b > a:
             out[a:b] = recv[r][: b - a]
     return out
+
+
+class PeerFrames:
+    """``count`` frame buffers that live on rank ``dst`` and are mapped into every rank of the group (torch symmetric
+    memory: peer mappings over NVLink). A rank passes ``frames[i]`` as the output image of its strip, so its blend
+    kernel stores the strip's pixels straight into the destination's buffer with ordinary stores; ``barrier()``
+    (device side, on the current stream) then tells the destination that every strip has landed. No gather follows.
+    Raises whatever the symmetric-memory set-up raises when peer mappings are not available; callers fall back to
+    ``gather_strips``."""
+
+    def __init__(self, count: int, height: int, width: int, device, dst: int = 0, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        shape = (count, height, width, 3)
+        self.local = symm_mem.empty(shape, dtype=torch.int8, device=device)
+        self.handle = symm_mem.rendezvous(self.local, group)
+        target = self.handle.get_buffer(dst, shape, torch.int8)
+        self.frames = [target[i] for i in range(count)]
+        self.dst = dst
+
+    def barrier(self) -> None:
+        self.handle.barrier(channel=0)
