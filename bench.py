@@ -43,10 +43,10 @@ FALLBACK_HBM_GBS = 6650.0
 # 1.5 M-Gaussian case of the same distribution (profiles/*_C4dist_1p5M_4K.txt); traffic grows in proportion
 # to the unit, so the full-size figure is this times the launch's units.
 NCU_DRAM_BYTES_PER_UNIT = {
-    "onesweep_kernel": (145.3e6 / 7.349e6, "R"),      # per pair and pass
-    "preprocess_kernel": (288.8e6 / 1.5e6, "P"),      # per Gaussian
+    "onesweep_kernel": (128.6e6 / 7.349e6, "R"),      # per pair and pass
+    "preprocess_kernel": ((287.9e6 + 60.2e6) / 1.5e6, "P"),   # per Gaussian: the kernel on the index list + the cull kernel
     "blend_kernel": (117.3e6 / 7.161e6, "S"),         # per blended pair
-    "local_sort_kernel": (133.0e6 / 7.349e6, "R"),    # per pair
+    "local_sort_kernel": (133.3e6 / 7.349e6, "R"),    # per pair
 }
 
 
