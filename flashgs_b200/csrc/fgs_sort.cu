@@ -7,11 +7,14 @@
 // Structure:
 //   * one histogram kernel reads the keys once and counts every 8-bit digit of the live
 //     bits (ceil(end_bit / 8) digits; bits at or above end_bit are never looked at);
-//   * one "onesweep" kernel per digit: a block (512 threads) takes the next partition of 4096 pairs from a
-//     ticket counter, ranks its keys by digit (warp match + per-warp counters, which keeps the
-//     sort stable), publishes its per-digit counts and obtains the counts of all earlier
-//     partitions by decoupled look-back, then moves keys and values through shared memory so
-//     that every digit's run leaves as contiguous global stores.
+//   * one "onesweep" kernel per digit: a block (256 sorting threads and 64 look-back threads) takes the next
+//     partition of 4096 pairs from a ticket counter, ranks its keys by digit (lanes with equal digits meet
+//     through bit masks in shared memory; per-warp counters keep the sort stable), publishes its per-digit
+//     counts and obtains the counts of all earlier partitions by decoupled look-back, then moves keys and
+//     values through shared memory so that every digit's run leaves as contiguous global stores;
+//   * when the tile id fits 16 bits only the tile digits go through such passes; the pairs of every tile are
+//     then put in depth order by an in-block sort in shared memory (a block-wide radix sort in global memory
+//     for lists longer than 4096).
 //   Each pass reads 12 bytes and writes 12 bytes per pair once; passes ping-pong between the
 //   output buffers and an alternate pair buffer inside the caller's scratch.
 //
@@ -159,20 +162,6 @@ histogram_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict
         const uint32_t c = s_hist[i];
         if (c) atomicAdd(hist + first_pass * RADIX + i, c);
     }
-}
-
-// Lanes of the warp that hold the same 8-bit digit: one vote per bit (the match.any instruction gives the
-// same mask but measured several hundred cycles per call here; eight votes are an order of magnitude cheaper).
-__device__ __forceinline__ unsigned match_digit(uint32_t d)
-{
-    unsigned peers = FULL_MASK;
-#pragma unroll
-    for (int b = 0; b < RADIX_BITS; b++) {
-        const bool bit = (d >> b) & 1u;
-        const unsigned vote = __ballot_sync(FULL_MASK, bit);
-        peers &= bit ? vote : ~vote;
-    }
-    return peers;
 }
 
 // ---- asynchronous bulk copies (TMA, 1-D, into this block only) and their mbarrier ----
@@ -604,7 +593,7 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
 // result is again what a stable sort of the whole pair list gives for this tile.
 constexpr int LONG_THREADS = 512, LONG_ITEMS = 8;
 // bookkeeping (4 histograms, run, lstart, per-warp counts, scan, flag) in front of the reordered chunk
-constexpr int LONG_BOOK_BYTES = (6 * RADIX * 4 + (LONG_THREADS / 32) * RADIX * 2 + (RADIX / 32) * 4 + 16 + 15) / 16 * 16;
+constexpr int LONG_BOOK_BYTES = (6 * RADIX * 4 + (LONG_THREADS / 32) * RADIX * 4 + (RADIX / 32) * 4 + 16 + 15) / 16 * 16;
 constexpr int LONG_SMEM_BYTES = LONG_BOOK_BYTES + LONG_THREADS * LONG_ITEMS * 12;
 
 template <int THREADS, int ITEMS>
@@ -615,8 +604,8 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
     static_assert(THREADS == LONG_THREADS && ITEMS == LONG_ITEMS, "the shared-memory layout is sized for these");
     uint32_t* hist = reinterpret_cast<uint32_t*>(smem);                     // [PASSES][RADIX] digit counts of the whole list
     uint32_t* run = hist + PASSES * RADIX;                                  // [RADIX] where each digit's run continues
-    uint16_t* whist = reinterpret_cast<uint16_t*>(run + RADIX);             // [WARPS][RADIX] per-warp counts of a chunk, then exclusive warp offsets
-    uint32_t* scan = reinterpret_cast<uint32_t*>(whist + WARPS * RADIX);    // [RADIX / 32]
+    uint32_t* whist = run + RADIX;                                          // [WARPS][RADIX] per-warp counts of a chunk, then exclusive warp offsets
+    uint32_t* scan = whist + WARPS * RADIX;                                 // [RADIX / 32]
     uint32_t* lstart = scan + RADIX / 32;                                   // [RADIX] where a digit's run starts inside the reordered chunk
     int* same = reinterpret_cast<int*>(lstart + RADIX);
     uint64_t* stage_k = reinterpret_cast<uint64_t*>(smem + LONG_BOOK_BYTES);       // [CHUNK] the chunk, reordered by digit
@@ -675,7 +664,7 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
         __syncthreads();
         if (*same) continue;   // every element has the same digit: nothing would move
         for (int c0 = 0; c0 < n; c0 += CHUNK) {
-            for (int i = tid; i < WARPS * RADIX / 2; i += THREADS) reinterpret_cast<uint32_t*>(whist)[i] = 0;
+            for (int i = tid; i < WARPS * RADIX; i += THREADS) whist[i] = 0;
             __syncthreads();
             uint64_t key[ITEMS];
             uint32_t val[ITEMS], rank[ITEMS];
@@ -687,16 +676,30 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
                 key[q] = ok ? src_k[i] : 0ull;
                 val[q] = ok ? src_v[i] : 0u;
             }
+            // ranking as in the digit pass: equal digits meet through bit masks in shared memory (two sets of words per
+            // warp in the reorder buffer, which is free at this point), the group's lowest lane adds the group to the
+            // warp's counter and hands the old value on
+            static_assert(WARPS * 2 * RADIX * 4 <= CHUNK * 8, "mask words fit the reorder buffer");
+            uint32_t* my_masks = reinterpret_cast<uint32_t*>(stage_k) + warp * (2 * RADIX);
+#pragma unroll
+            for (int i = 0; i < 2 * RADIX / 32; i++) my_masks[i * 32 + lane] = 0;
+            __syncwarp();
 #pragma unroll
             for (int q = 0; q < ITEMS; q++) {
                 const bool ok = wb + q * 32 + lane < n;
                 const uint32_t d = ((uint32_t)key[q] >> shift) & (RADIX - 1);
-                const unsigned peers = match_digit(d) & __ballot_sync(FULL_MASK, ok);
-                const uint32_t pre = whist[warp * RADIX + d];
+                volatile uint32_t* word = my_masks + (q & 1) * RADIX + d;
+                if (ok) atomicOr(const_cast<uint32_t*>(word), 1u << lane);
                 __syncwarp();
-                if (ok && (peers & lt) == 0) whist[warp * RADIX + d] = (uint16_t)(pre + __popc(peers));
+                const unsigned peers = ok ? *word : (1u << lane);
+                __syncwarp();
+                uint32_t pre = 0;
+                if (ok && (peers & lt) == 0) {
+                    *word = 0;
+                    pre = atomicAdd(&whist[warp * RADIX + d], (uint32_t)__popc(peers));
+                }
+                pre = __shfl_sync(FULL_MASK, pre, __ffs(peers) - 1);
                 rank[q] = pre + __popc(peers & lt);
-                __syncwarp();
             }
             __syncthreads();
             // thread d: the chunk's count of digit d, the warps' exclusive offsets inside it, and (scan over the
@@ -705,7 +708,7 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
             if (tid < RADIX) {
                 for (int w = 0; w < WARPS; w++) {
                     const uint32_t c = whist[w * RADIX + tid];
-                    whist[w * RADIX + tid] = (uint16_t)chunk_count;
+                    whist[w * RADIX + tid] = chunk_count;
                     chunk_count += c;
                 }
                 cinc = chunk_count;
