@@ -222,12 +222,12 @@ __device__ __forceinline__ void st_relaxed_v4(uint32_t* p, uint4 v)
 // Persistent blocks (two per SM) of SORT_THREADS "sorting" threads plus LB_THREADS "look-back" threads.
 //
 // Sorting warps, per partition of SORT_PART pairs: wait for the bulk copy (TMA) that brought the partition
-// into the IN stage, pull it into registers and immediately start the copy of the next partition into the
-// same stage; rank by digit; hand the per-digit counts to the look-back warps; write out the PREVIOUS
-// partition, whose global digit offsets the look-back warps have produced meanwhile; reorder the current
-// partition into the OUT stage.
-// Look-back warps, per partition: publish the counts, walk back over earlier partitions' status words until
-// an inclusive prefix is found, publish this partition's inclusive prefix, hand the offsets back.
+// into the IN stage and pull it into registers; count the digits (shared-memory adds), publish the counts and
+// hand them to the look-back warps; rank by digit (the IN stage serves as scratch for the bit masks); start
+// the copy of the next partition into the IN stage; write out the PREVIOUS partition, whose global digit
+// offsets the look-back warps have produced meanwhile; reorder the current partition into the OUT stage.
+// Look-back warps, per partition: walk back over earlier partitions' status words until an inclusive prefix
+// is found, publish this partition's inclusive prefix, hand the offsets back.
 // The look-back of partition i therefore runs while the sorting warps write out partition i-1 and rank
 // partition i+1: persistent blocks advance in lock-step, which makes the walk long (it crosses the partitions
 // of all blocks that started together), and this keeps that wait off the sorting warps' path.
@@ -777,19 +777,21 @@ long_list_kernel(uint64_t* keys_grouped, uint32_t* vals_grouped, uint64_t* keys_
 }
 
 // One block per tile: order the tile's pairs by (depth bits, position inside the tile's list) in shared memory,
-// then gather keys and values in that order. The position makes equal depths keep their input order, i.e. the
-// result is what a stable sort of the whole list gives.
+// then write keys and values in that order (the keys are rebuilt from the tile word and the sorted depths, the
+// values are gathered). The position makes equal depths keep their input order, i.e. the result is what a
+// stable sort of the whole list gives.
 //
 // The order is found by a bucket sort: depths of one tile are spread fairly evenly between the tile's nearest
-// and farthest splat, so CAP/2 equal-width depth buckets receive about one element each; the elements
-// are counted, placed bucket by bucket (shared-memory atomics) and every bucket is then put in order by one
-// thread. A tile whose depths pile up in one bucket (more than LOCAL_BUCKET_LIMIT elements) is sorted by a
-// bitonic network over the whole tile instead, so the cost stays bounded for any input.
+// and farthest splat, so CAP equal-width depth buckets receive about one element each. The depths stay in
+// registers; one shared-memory add per element counts its bucket and returns its arrival number; after a scan
+// of the counts the elements are stored bucket by bucket, and one thread per ELEMENT counts the smaller keys of
+// its bucket, which is its final place. A tile whose depths pile up in one bucket (more than LOCAL_BUCKET_LIMIT
+// elements) is sorted by a bitonic network over the whole tile instead, so the cost stays bounded for any input.
 //
 // Three instantiations cover list lengths (0,1024], (1024,2048] and (2048,LOCAL_CAP] with shared-memory
 // footprints that grow with the class, so that the many short lists run with many blocks per SM; each is a
 // small grid of persistent blocks that walks the work list segments_kernel built for its class (an empty
-// class costs one launch of blocks that return at once).
+// class costs one launch of blocks that return at once). Longer lists go to long_list_kernel.
 #ifndef FGS_LOCAL_BUCKET_LIMIT
 #define FGS_LOCAL_BUCKET_LIMIT 192
 #endif
