@@ -5,7 +5,8 @@
 // iso-ellipse, exact ellipse-vs-tile test, (tile|depth) key emission, degree-3 SH colour
 // and the feature records the blend stage reads.
 //
-// Design (B200): a block of 256 threads owns 256 consecutive Gaussians.
+// Design (B200): a block of 256 threads owns 256 consecutive Gaussians -- of the scene, or, when the caller gives
+// scratch for it, of the list of Gaussians that a first streaming kernel found able to reach the image or strip.
 //   1. position / opacity / covariance of the block are fetched with 16-byte loads into
 //      shared memory (the [P,3] and [P,6] rows are 12 and 24 bytes, so per-thread loads
 //      could not be vectorised); each thread then projects its own Gaussian.

@@ -213,7 +213,9 @@ int fgs_render_ex(int block_x, int block_y, int num_rendered, int width, int hei
  * host read-back between the stages as the reference's operator signatures force (example.py:79 reads the
  * counter because csrc/ops.h:41,49 take it as a host int); the caller may read curr_offset afterwards, at its
  * own pace, to learn the count. All buffers as in the per-stage entry points; pair_capacity is the length of the
- * four pair buffers and sort_temp must hold fgs_sort_temp_bytes(pair_capacity). If the frame produces more
+ * four pair buffers and sort_temp must hold fgs_sort_temp_bytes(pair_capacity) (when it also holds P + 1 ints,
+ * its head carries preprocess's index list of the Gaussians that can reach the image, see
+ * fgs_preprocess_strip_culled: the sort does not need its scratch until preprocess is done). If the frame produces more
  * pairs than pair_capacity the surplus is dropped, the image is built from the pairs that fit and
  * FGS_ERR_PAIR_OVERFLOW is raised in the device status word. No counterpart in the reference.
  */
