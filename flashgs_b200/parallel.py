@@ -100,6 +100,9 @@ class PeerFrames:
     ``gather_strips``."""
 
     def __init__(self, count: int, height: int, width: int, device, dst: int = 0, group=None):
+        import os
+        # only plain peer stores are used: ask the allocator not to bind the buffers to an NVLink multicast object
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         group = group if group is not None else dist.group.WORLD
         shape = (count, height, width, 3)

@@ -63,6 +63,10 @@ def test_argument_checks_need_no_gpu():
     assert lib.fgs_preprocess(-1, *([None] * 4), 64, 64, 16, 16, None, None, 1.0, 1.0, 100.0, 0.01,
                               *([None] * 5), 0, None, None) == _lib.ERR_BAD_ARG
     assert lib.fgs_tile_ranges(0, 0, None, None, None) == _lib.ERR_BAD_ARG
+    # scratch for the index list of the Gaussians that reach a strip must hold P + 1 ints (checked before anything runs)
+    dummy = (C.c_int * 4)()
+    assert lib.fgs_preprocess_strip_culled(10, *([None] * 4), 64, 64, 16, 16, None, None, 1.0, 1.0, 100.0, 0.01, 0, 2,
+                                           *([None] * 5), 0, None, C.addressof(dummy), 4, None) == _lib.ERR_TEMP_TOO_SMALL
 
 
 def test_sort_temp_bytes_is_monotone_and_covers_alternate_buffers():

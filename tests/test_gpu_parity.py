@@ -301,6 +301,19 @@ def test_sort_random_sizes(ops, oracle_lib, n):
     _sort_case(ops, oracle_lib, keys, vals, W, H)
 
 
+def test_sort_images_with_more_tiles_than_the_bucketed_path_takes(ops, oracle_lib):
+    # 8192 x 8192: 262 144 tiles = 18 tile bits, 51 sorted bits -> seven plain digit passes, no in-block tile sorts
+    rng = np.random.default_rng(5)
+    n = 300000
+    W = H = 8192
+    tiles = 512 * 512
+    keys = (rng.integers(0, tiles, n, dtype=np.uint64) << np.uint64(32)) | rng.integers(0, 1 << 32, n, dtype=np.uint64)
+    keys[::7] = keys[3]   # runs of equal keys: stability
+    vals = np.arange(n, dtype=np.uint32)
+    _sort_case(ops, oracle_lib, keys, vals, W, H)
+    assert ops.device_status() == 0
+
+
 def test_sort_adversarial(ops, oracle_lib):
     rng = np.random.default_rng(1)
     n = 50000
