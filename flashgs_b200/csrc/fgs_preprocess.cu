@@ -116,13 +116,19 @@ __device__ __forceinline__ f3 cov2d(const f3& p, const PreCam& cam, const float*
     return { C[0][0], C[0][1], C[1][1] };
 }
 
-// preprocess.cu:187-194
+// preprocess.cu:187-194. Which multiply-add pairs are fused decides the outcome for splats tangent to a tile edge,
+// and the reference's build (its setup.py compiles with -O1) does not fuse the same way at its two call sites:
+// against it, on 29.4 M pairs, the forms below reproduce every pair -- t1 as a separate multiply and add in the
+// test of the vertical edge (VERTICAL) and fused in the test of the horizontal edge, everything else fused as
+// written. Explicit intrinsics pin the choice so that it does not depend on this file's optimisation level.
+template <bool VERTICAL>
 __device__ __forceinline__ bool segment_hits_ellipse(float a, float b, float c, float d, float l, float r)
 {
-    float delta = b * b - 4.0f * a * c;
-    float t1 = (l - d) * (2.0f * a) + b;
-    float t2 = (r - d) * (2.0f * a) + b;
-    return delta >= 0.0f && (t1 <= 0.0f || t1 * t1 <= delta) && (t2 >= 0.0f || t2 * t2 <= delta);
+    const float delta = __fmaf_rn(b, b, -__fmul_rn(__fmul_rn(4.0f, a), c));
+    const float a2 = __fmul_rn(2.0f, a);
+    const float t1 = VERTICAL ? __fadd_rn(__fmul_rn(l - d, a2), b) : __fmaf_rn(l - d, a2, b);
+    const float t2 = __fmaf_rn(r - d, a2, b);
+    return delta >= 0.0f && (t1 <= 0.0f || __fmul_rn(t1, t1) <= delta) && (t2 >= 0.0f || __fmul_rn(t2, t2) <= delta);
 }
 
 // preprocess.cu:196-241: centre inside the tile's pixel box, or the iso-ellipse crosses the
@@ -135,18 +141,18 @@ __device__ __forceinline__ bool tile_hit(int tx, int ty, int bx, int by, float c
     if (cx_pix >= minx && cx_pix <= maxx && cy_pix >= miny && cy_pix <= maxy) return true;
 
     float a, b, c, dx, dy;
-    const float w = 2.0f * power;
+    const float w = __fmul_rn(2.0f, power);
     if (cx_pix * 2.0f < minx + maxx) dx = cx_pix - minx; else dx = cx_pix - maxx;
     a = conz;
-    b = -2.0f * cony * dx;
-    c = conx * dx * dx - w;
-    if (segment_hits_ellipse(a, b, c, cy_pix, miny, maxy)) return true;
+    b = __fmul_rn(__fmul_rn(-2.0f, cony), dx);
+    c = __fmaf_rn(__fmul_rn(conx, dx), dx, -w);
+    if (segment_hits_ellipse<true>(a, b, c, cy_pix, miny, maxy)) return true;
 
     if (cy_pix * 2.0f < miny + maxy) dy = cy_pix - miny; else dy = cy_pix - maxy;
     a = conx;
-    b = -2.0f * cony * dy;
-    c = conz * dy * dy - w;
-    return segment_hits_ellipse(a, b, c, cx_pix, minx, maxx);
+    b = __fmul_rn(__fmul_rn(-2.0f, cony), dy);
+    c = __fmaf_rn(__fmul_rn(conz, dy), dy, -w);
+    return segment_hits_ellipse<false>(a, b, c, cx_pix, minx, maxx);
 }
 
 // preprocess.cu:145-185; sh holds the 16 coefficients as [coef][rgb]
