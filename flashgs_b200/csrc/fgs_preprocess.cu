@@ -33,7 +33,9 @@
 //
 // The float expressions keep the operation order of the reference so that the device
 // compiler's FMA contraction sees the same expression trees: the tile lists depend on
-// float comparisons and (int) truncations of these values.
+// float comparisons and (int) truncations of these values. In the exact tile test, where a
+// splat tangent to a tile edge flips on a single rounding, every operation is pinned with
+// intrinsics to what the reference's build does (see segment_hits_ellipse).
 
 #include "fgs_common.cuh"
 
