@@ -192,11 +192,23 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
 #pragma unroll
                         for (int i = 0; i < TY; i++) {
                             const f32x2 dy2 = sub2(sy2, py2[i]);
+                            // The exponent in the reference's operation order (render.cu:44): w + (x*dx)*dx, then + (z*dy)*dy,
+                            // then + (y*dx)*dy, each step one fused multiply-add. With it the 8-bit image of the headline
+                            // workload is byte for byte the reference's. Folding z*dy into the last step saves one multiply
+                            // per row and splat (8 % of the kernel) but rounds differently: about 1 byte in 17 000 then
+                            // differs by one level (FGS_BLEND_FOLDED_EXPONENT selects that form).
+#ifndef FGS_BLEND_FOLDED_EXPONENT
+                            const f32x2 rz2 = mul2(cz2, dy2);
+#endif
 #pragma unroll
                             for (int p = 0; p < PX; p++) {
-                                const f32x2 t2 = fma2(cz2, dy2, B2[p]);
                                 float p0, p1;
+#ifndef FGS_BLEND_FOLDED_EXPONENT
+                                unpack2(fma2(B2[p], dy2, fma2(rz2, dy2, A2[p])), p0, p1);
+#else
+                                const f32x2 t2 = fma2(cz2, dy2, B2[p]);
                                 unpack2(fma2(t2, dy2, A2[p]), p0, p1);
+#endif
                                 const f32x2 aT2 = mul2(pack2(ex2_approx_ftz(p0), ex2_approx_ftz(p1)), T2[i][p]);
                                 Cr2[i][p] = fma2(r2, aT2, Cr2[i][p]);
                                 Cg2[i][p] = fma2(g2, aT2, Cg2[i][p]);
