@@ -475,7 +475,7 @@ def main():
             if "gbs" in s:
                 s["frac"] = s["gbs"] / peak
         # the dominant HBM-bound kernel: the one with the largest total time per frame. blend_kernel takes as long
-        # but is bound by the FP32 pipe (FMA pipe 71 % busy under ncu, DRAM 2 %), for which the schema has no roofline;
+        # but is bound by the FP32 pipe (FMA pipe 73 % busy under ncu, DRAM 2 %), for which the schema has no roofline;
         # its rate is in stages["ranges_blend"].
         cand = {"preprocess": pre_ms, "sort_digit_pass": mean_pass * len(pass_ms), "sort_tile_local": local_ms}
         dom = max(cand, key=cand.get)
