@@ -233,10 +233,13 @@ def main():
     cam = cams[0]
     config = {"workload": "%s: %s" % (wl.name, wl.notes), "gaussians": scene.num_vertex,
               "image": "%dx%d" % (cam.width, cam.height), "tile": "16x16",
-              "camera": "radius %.0f, %.0f deg horizontal FoV (the workload states no camera; the 1080p workload's is used)"
-                        % (wl.radius, wl.hfov_deg),
+              "camera": "radius %.0f, %.0f deg horizontal FoV%s" % (
+                  wl.radius, wl.hfov_deg,
+                  " (the workload states no camera; the 1080p workload's is used)" if wl.name in ("C3", "C4") else
+                  (" (the workload states no field of view; 50 deg is used)" if wl.name == "C5" else "")),
               "partition": "whole frame" if world == 1 else "%d strips of tile rows, scene replicated" % world,
-              "l2": "inputs (%.2f GB scene) larger than L2" % (scene.num_vertex * 232 / 1e9)}
+              "l2": ("inputs (%.2f GB scene) larger than L2" if scene.num_vertex * 232 > 126e6 else
+                     "inputs (%.2f GB scene) fit in L2 and L2 is not flushed: not the headline workload") % (scene.num_vertex * 232 / 1e9)}
 
     if args.view_batch:
         return run_view_batch(args, emit, wl, scene, cams, config, rank, local_rank, world)
