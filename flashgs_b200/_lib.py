@@ -32,6 +32,7 @@ SIGNATURES = {
                                          _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p]),
     "fgs_sort_temp_bytes": (C.c_size_t, [_i64]),
     "fgs_sort_pairs": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p]),
+    "fgs_sort_pairs_stable": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p]),
     "fgs_sort_static_max_pairs": (_i, []),
     "fgs_sort_pairs_static": (_i, [_i, _i, _i, _i, _i, _p, _p, _p, _p, _p]),
     "fgs_sort_pairs_profile": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p, _p, _p, _i, _p]),

@@ -26,6 +26,8 @@
 
 #include "fgs_common.cuh"
 
+#include <mutex>
+
 namespace fgs {
 namespace {
 
@@ -76,11 +78,34 @@ __device__ __forceinline__ void st_relaxed(uint32_t* p, uint32_t v)
 }
 
 struct SortLayout {
-    size_t tickets_off, flag_off, hist_off, status_off, seg_off, class_off, alt_keys_off, alt_vals_off, total;
+    size_t tickets_off, flag_off, hist_off, tilecnt_off, status_off, seg_off, class_off, cursor_off, bucket_off, alt_keys_off, alt_vals_off, total;
     int parts;
 };
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Words of the small tables of the tile-grouping passes (behind bucket_off): the cursors of the coarse buckets,
+// where each coarse bucket starts (one more entry: the pair count), and the running number of second-pass units.
+constexpr int MAX_BUCKETS = 256;
+constexpr size_t BUCKET_TABLE_WORDS = MAX_BUCKETS + 2 * (MAX_BUCKETS + 1) + 2;
+
+constexpr size_t LAYOUT_HIST_OFF = 256;
+constexpr size_t LAYOUT_TILECNT_OFF = LAYOUT_HIST_OFF + (size_t)MAX_PASSES * RADIX * 4;
+constexpr size_t LAYOUT_STATUS_OFF = LAYOUT_TILECNT_OFF + (size_t)MAX_TILE_VALUES * 4;
+
+// Everything in front of status_off starts at zero in every sort (one memset, or the clearing kernel when the
+// pair count lives on the device): tickets, class counts and tickets, digit counts, per-tile pair counts.
+constexpr size_t layout_total(size_t n)
+{
+    const size_t parts = (n + SORT_PART - 1) / SORT_PART;
+    const size_t seg_off = (LAYOUT_STATUS_OFF + (size_t)MAX_PASSES * parts * RADIX * 4 + 255) / 256 * 256;
+    const size_t class_off = (seg_off + (size_t)MAX_TILE_VALUES * 8 + 255) / 256 * 256;
+    const size_t cursor_off = (class_off + (size_t)LOCAL_CLASSES * MAX_TILE_VALUES * 4 + 255) / 256 * 256;
+    const size_t bucket_off = (cursor_off + (size_t)MAX_TILE_VALUES * 4 + 255) / 256 * 256;
+    const size_t alt_keys_off = (bucket_off + BUCKET_TABLE_WORDS * 4 + 255) / 256 * 256;
+    const size_t alt_vals_off = (alt_keys_off + n * 8 + 255) / 256 * 256;
+    return (alt_vals_off + n * 4 + 255) / 256 * 256;
+}
 
 inline SortLayout make_layout(int64_t n)
 {
@@ -89,11 +114,14 @@ inline SortLayout make_layout(int64_t n)
     L.parts = (int)((n + SORT_PART - 1) / SORT_PART);
     L.tickets_off = 0;                                           // MAX_PASSES tickets
     L.flag_off = 128;                                            // one spare word, then the class counts and tickets
-    L.hist_off = 256;                                            // MAX_PASSES x RADIX counts
-    L.status_off = L.hist_off + (size_t)MAX_PASSES * RADIX * 4;  // passes x parts x RADIX words
+    L.hist_off = LAYOUT_HIST_OFF;                                // MAX_PASSES x RADIX counts
+    L.tilecnt_off = LAYOUT_TILECNT_OFF;                          // pairs per tile value
+    L.status_off = LAYOUT_STATUS_OFF;                            // passes x parts x RADIX look-back words
     L.seg_off = align_up(L.status_off + (size_t)MAX_PASSES * L.parts * RADIX * 4, 256);   // [first, last) per tile value
     L.class_off = align_up(L.seg_off + (size_t)MAX_TILE_VALUES * 8, 256);                 // tile ids per length class
-    L.alt_keys_off = align_up(L.class_off + (size_t)LOCAL_CLASSES * MAX_TILE_VALUES * 4, 256);
+    L.cursor_off = align_up(L.class_off + (size_t)LOCAL_CLASSES * MAX_TILE_VALUES * 4, 256);   // next free place per tile
+    L.bucket_off = align_up(L.cursor_off + (size_t)MAX_TILE_VALUES * 4, 256);             // tables of the coarse buckets
+    L.alt_keys_off = align_up(L.bucket_off + BUCKET_TABLE_WORDS * 4, 256);
     L.alt_vals_off = align_up(L.alt_keys_off + (size_t)n * 8, 256);
     L.total = align_up(L.alt_vals_off + (size_t)n * 4, 256);
     return L;
@@ -586,24 +614,315 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
     if (c >= 0) class_tiles[(size_t)c * MAX_TILE_VALUES + s_class_base[c] + slot] = (uint32_t)t;
 }
 
+// ---- tile grouping without any wait between blocks ----
+// The in-block tile sorts need every tile's pairs contiguous, in ANY order (they order a tile's pairs themselves).
+// That weaker requirement is met without look-back: count the pairs of every tile value (tile_hist_kernel), turn
+// the counts into each tile's [first, last) and a cursor per tile (tile_scan_kernel), then move the pairs in two
+// passes (multisplit_kernel). The first pass splits by the upper half of the tile bits into coarse buckets, the
+// second splits every coarse bucket by the lower half into its tiles. A block takes one partition, counts its
+// digits in shared memory, reserves room for each digit's run with ONE atomicAdd on that destination's cursor,
+// reorders the partition in shared memory and writes the runs as contiguous stores. Blocks never wait for one
+// another, so there is no look-back chain, no ordering between blocks and nothing that can time out; the price is
+// that the order inside a tile is the order in which blocks happened to reserve their runs, which is why the
+// tile sorts of this path order by (depth bits, value) and not by (depth bits, position).
+#ifndef FGS_MS_BLOCKS_PER_SM
+#define FGS_MS_BLOCKS_PER_SM 3
+#endif
+#ifndef FGS_MS_ITEMS
+#define FGS_MS_ITEMS 16
+#endif
+#ifndef FGS_MS_LATE_VALUES
+#define FGS_MS_LATE_VALUES 0   // 1: read a partition's values after the ranking instead of with its keys
+#endif
+constexpr int MS_THREADS = 256;                       // thread d owns digit value d (at most 8 bits per pass)
+constexpr int MS_ITEMS = FGS_MS_ITEMS;
+constexpr int MS_PART = MS_THREADS * MS_ITEMS;        // pairs per partition
+constexpr int MS_SMEM_BYTES = MS_PART * 12;           // the partition reordered by digit: keys, then values
+constexpr int MS_BLOCKS_PER_SM = FGS_MS_BLOCKS_PER_SM;
+constexpr int TILE_HIST_THREADS = 1024;
+constexpr int TILE_HIST_SMEM_VALUES = 49152;          // tile values whose counters fit one block's shared memory
+constexpr int TILE_SCAN_THREADS = 1024;
+static_assert(MS_THREADS == MAX_BUCKETS, "a pass has at most as many digit values as the block has threads");
+
+// Pairs per tile value, added to tile_count[] (zero on entry). With `in_smem` a block counts into shared memory
+// (tile_values * 4 bytes of dynamic shared memory) and adds its non-zero counters to the global ones at the end;
+// otherwise every key adds to the global counter directly (more tile values than fit, or very few keys).
+__global__ void __launch_bounds__(TILE_HIST_THREADS, 1)
+tile_hist_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict__ n_dev, uint32_t tile_mask, int tile_values,
+                 int in_smem, uint32_t* __restrict__ tile_count)
+{
+    extern __shared__ __align__(16) uint32_t s_tiles[];
+    n = device_count(n, n_dev);
+    if (in_smem) {
+        for (int i = threadIdx.x; i < tile_values; i += TILE_HIST_THREADS) s_tiles[i] = 0;
+        __syncthreads();
+    }
+    auto count = [&](uint64_t key) {
+        const uint32_t t = (uint32_t)(key >> 32) & tile_mask;
+        if (in_smem) atomicAdd(&s_tiles[t], 1u); else atomicAdd(tile_count + t, 1u);
+    };
+    const int64_t stride = (int64_t)gridDim.x * TILE_HIST_THREADS, me = (int64_t)blockIdx.x * TILE_HIST_THREADS + threadIdx.x;
+    const int64_t pairs = aligned16_dev(keys) ? n / 2 : 0;
+    const ulonglong2* keys2 = reinterpret_cast<const ulonglong2*>(keys);
+    for (int64_t i = me; i < pairs; i += 2 * stride) {
+        const ulonglong2 a = __ldg(keys2 + i);
+        const bool second = i + stride < pairs;
+        const ulonglong2 c = second ? __ldg(keys2 + i + stride) : make_ulonglong2(0, 0);
+        count(a.x); count(a.y);
+        if (second) { count(c.x); count(c.y); }
+    }
+    for (int64_t i = 2 * pairs + me; i < n; i += stride) count(__ldg(keys + i));
+    if (in_smem) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < tile_values; i += TILE_HIST_THREADS) {
+            const uint32_t c = s_tiles[i];
+            if (c) atomicAdd(tile_count + i, c);
+        }
+    }
+}
+
+// One block. From the pairs per tile value: every tile's [first, last) in the tile-grouped list and its cursor
+// (= first), the work lists of the tile sorts' length classes, and the tables of the coarse buckets (a bucket is
+// the run of 2^lo_bits consecutive tile values that share their upper bits): where each bucket starts, its cursor,
+// and the running count of the second pass's units (partitions cut inside a bucket).
+__global__ void __launch_bounds__(TILE_SCAN_THREADS, 1)
+tile_scan_kernel(const uint32_t* __restrict__ tile_count, int tile_values, int lo_bits,
+                 int2* __restrict__ seg, uint32_t* __restrict__ cursor, uint32_t* __restrict__ bucket_tables,
+                 int* __restrict__ class_count, uint32_t* __restrict__ class_tiles)
+{
+    constexpr int WARPS = TILE_SCAN_THREADS / 32;
+    __shared__ uint32_t s_wsum[5][WARPS];
+    __shared__ uint32_t s_bucket_first[MAX_BUCKETS + 1];
+    __shared__ uint32_t s_units[MAX_BUCKETS];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per = (tile_values + TILE_SCAN_THREADS - 1) / TILE_SCAN_THREADS;   // tile values per thread, consecutive
+    const int t0 = tid * per, t1 = min(tile_values, t0 + per);
+    auto length_class = [](uint32_t len) { return len <= 1024u ? 0 : (len <= 2048u ? 1 : (len <= (uint32_t)LOCAL_CAP ? 2 : 3)); };
+    // pass A: this thread's totals -- pairs, and non-empty tiles per length class
+    uint32_t v[5] = { 0, 0, 0, 0, 0 };
+    for (int t = t0; t < t1; t++) {
+        const uint32_t c = tile_count[t];
+        v[0] += c;
+        const int k = c ? length_class(c) : -1;
+#pragma unroll
+        for (int q = 0; q < LOCAL_CLASSES; q++) v[1 + q] += (k == q) ? 1u : 0u;
+    }
+    uint32_t inc[5];
+#pragma unroll
+    for (int q = 0; q < 5; q++) {
+        inc[q] = v[q];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t a = __shfl_up_sync(FULL_MASK, inc[q], o);
+            if (lane >= o) inc[q] += a;
+        }
+        if (lane == 31) s_wsum[q][warp] = inc[q];
+    }
+    __syncthreads();
+    uint32_t run[5];
+#pragma unroll
+    for (int q = 0; q < 5; q++) {
+        uint32_t off = 0;
+        for (int w = 0; w < warp; w++) off += s_wsum[q][w];
+        run[q] = off + inc[q] - v[q];   // exclusive prefix of this thread's chunk
+    }
+    // pass B: per tile
+    const int buckets = max(1, tile_values >> lo_bits);
+    const uint32_t lo_mask = (1u << lo_bits) - 1u;
+    for (int t = t0; t < t1; t++) {
+        const uint32_t c = tile_count[t];
+        seg[t] = make_int2((int)run[0], (int)(run[0] + c));
+        cursor[t] = run[0];
+        if (((uint32_t)t & lo_mask) == 0) s_bucket_first[t >> lo_bits] = run[0];
+        if (c) {
+            const int k = length_class(c);
+            uint32_t place = 0;
+#pragma unroll
+            for (int q = 0; q < LOCAL_CLASSES; q++)
+                if (k == q) place = run[1 + q]++;
+            class_tiles[(size_t)k * MAX_TILE_VALUES + place] = (uint32_t)t;
+        }
+        run[0] += c;
+    }
+    if (tid == TILE_SCAN_THREADS - 1) {
+        uint32_t total = 0;
+        for (int w = 0; w < WARPS; w++) total += s_wsum[0][w];
+        s_bucket_first[buckets] = total;
+#pragma unroll
+        for (int k = 0; k < LOCAL_CLASSES; k++) {
+            uint32_t cnt = 0;
+            for (int w = 0; w < WARPS; w++) cnt += s_wsum[1 + k][w];
+            class_count[k] = (int)cnt;
+        }
+    }
+    __syncthreads();
+    // bucket tables: [0, B) cursors, [B, 2B+1) firsts, [2B+1, 3B+2) exclusive unit counts (+ their total)
+    uint32_t* hi_cursor = bucket_tables;
+    uint32_t* bucket_first = bucket_tables + MAX_BUCKETS;
+    uint32_t* unit_prefix = bucket_first + MAX_BUCKETS + 1;
+    if (tid < buckets) {
+        const uint32_t first = s_bucket_first[tid], size = s_bucket_first[tid + 1] - first;
+        hi_cursor[tid] = first;
+        bucket_first[tid] = first;
+        s_units[tid] = (size + MS_PART - 1) / MS_PART;
+    }
+    if (tid == 0) bucket_first[buckets] = s_bucket_first[buckets];
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t acc = 0;
+        for (int h = 0; h < buckets; h++) { unit_prefix[h] = acc; acc += s_units[h]; }
+        unit_prefix[buckets] = acc;
+    }
+}
+
+// One pass of the tile grouping. SECOND == false: unit = partition `blockIdx.x` of the whole list, digit = upper
+// tile bits, destination cursors = the coarse buckets'. SECOND == true: unit = one partition cut inside one coarse
+// bucket (found from the running unit counts), digit = lower tile bits, destination cursors = the tiles' of that
+// bucket. Every destination index comes from cursors that were derived from counts of these very keys, so it lies
+// inside the list; `n` (or the device count) bounds the reads.
+template <bool SECOND>
+__global__ void __launch_bounds__(MS_THREADS, MS_BLOCKS_PER_SM)
+multisplit_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
+                  uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
+                  int n, const int* __restrict__ n_dev, uint32_t tile_mask, int lo_bits, int buckets,
+                  const uint32_t* bucket_tables, uint32_t* cursors)
+{
+    extern __shared__ __align__(16) unsigned char s_ms[];      // reordered partition: keys [MS_PART], values [MS_PART]
+    __shared__ uint32_t s_cnt[MS_THREADS];                      // pairs per digit value in this partition
+    __shared__ uint32_t s_lstart[MS_THREADS];                   // where a digit's run starts in the reordered partition
+    __shared__ uint32_t s_delta[MS_THREADS];                    // destination index minus index in the reordered partition
+    __shared__ uint32_t s_wsum[MS_THREADS / 32];
+    __shared__ uint32_t s_units[SECOND ? MAX_BUCKETS + 1 : 1];
+    uint64_t* st_keys = reinterpret_cast<uint64_t*>(s_ms);
+    uint32_t* st_vals = reinterpret_cast<uint32_t*>(s_ms + MS_PART * 8);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    n = device_count(n, n_dev);
+
+    int64_t base;
+    int count;
+    uint32_t cursor_base = 0;
+    if (!SECOND) {
+        base = (int64_t)blockIdx.x * MS_PART;
+        if (base >= n) return;
+        count = (int)min((int64_t)MS_PART, (int64_t)n - base);
+    } else {
+        const uint32_t* bucket_first = bucket_tables + MAX_BUCKETS;
+        const uint32_t* unit_prefix = bucket_first + MAX_BUCKETS + 1;
+        for (int i = tid; i <= buckets; i += MS_THREADS) s_units[i] = unit_prefix[i];
+        __syncthreads();
+        const uint32_t u = blockIdx.x;
+        if (u >= s_units[buckets]) return;
+        int lo = 0, hi = buckets;   // largest h with s_units[h] <= u
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_units[mid] <= u) lo = mid; else hi = mid;
+        }
+        const uint32_t first = bucket_first[lo], last = bucket_first[lo + 1];
+        base = (int64_t)first + (int64_t)(u - s_units[lo]) * MS_PART;
+        count = (int)min((int64_t)MS_PART, (int64_t)last - base);
+        if (count <= 0 || base + count > (int64_t)n) return;   // inconsistent tables: touch nothing
+        cursor_base = (uint32_t)lo << lo_bits;
+    }
+    const uint32_t lo_mask = (1u << lo_bits) - 1u;
+    auto digit_of_key = [&](uint64_t key) {
+        const uint32_t t = (uint32_t)(key >> 32) & tile_mask;
+        return SECOND ? (t & lo_mask) : (t >> lo_bits);
+    };
+
+    s_cnt[tid] = 0;
+    uint64_t key[MS_ITEMS];
+#pragma unroll
+    for (int i = 0; i < MS_ITEMS; i++) {
+        const int j = i * MS_THREADS + tid;
+        key[i] = j < count ? __ldg(keys_in + base + j) : 0ull;
+    }
+#if !FGS_MS_LATE_VALUES
+    uint32_t val[MS_ITEMS];
+#pragma unroll
+    for (int i = 0; i < MS_ITEMS; i++) {
+        const int j = i * MS_THREADS + tid;
+        val[i] = j < count ? __ldg(vals_in + base + j) : 0u;
+    }
+#endif
+    __syncthreads();
+    // place inside the digit's run: the arrival number of a shared-memory add (any order will do)
+    uint32_t slot[MS_ITEMS];
+#pragma unroll
+    for (int i = 0; i < MS_ITEMS; i++) {
+        const int j = i * MS_THREADS + tid;
+        slot[i] = j < count ? atomicAdd(&s_cnt[digit_of_key(key[i])], 1u) : 0u;
+    }
+    __syncthreads();
+    // thread d: exclusive scan of the counts (start of digit d's run in the reordered partition), and the
+    // reservation of the run's place at its destination
+    const uint32_t c = s_cnt[tid];
+    uint32_t inc = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t a = __shfl_up_sync(FULL_MASK, inc, o);
+        if (lane >= o) inc += a;
+    }
+    if (lane == 31) s_wsum[warp] = inc;
+    __syncthreads();
+    uint32_t off = 0;
+#pragma unroll
+    for (int w = 0; w < MS_THREADS / 32; w++) off += (w < warp) ? s_wsum[w] : 0;
+    const uint32_t lstart = off + inc - c;
+    s_lstart[tid] = lstart;
+    uint32_t gstart = 0;
+    if (c) gstart = atomicAdd(cursors + cursor_base + tid, c);   // its round trip overlaps the reordering below
+#if FGS_MS_LATE_VALUES
+    // the values are not needed before this point: fetched now, they do not hold registers during the ranking
+    uint32_t val[MS_ITEMS];
+#pragma unroll
+    for (int i = 0; i < MS_ITEMS; i++) {
+        const int j = i * MS_THREADS + tid;
+        val[i] = j < count ? __ldg(vals_in + base + j) : 0u;
+    }
+#endif
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < MS_ITEMS; i++) {
+        const int j = i * MS_THREADS + tid;
+        if (j < count) {
+            const uint32_t pos = s_lstart[digit_of_key(key[i])] + slot[i];
+            st_keys[pos] = key[i];
+            st_vals[pos] = val[i];
+        }
+    }
+    s_delta[tid] = gstart - lstart;
+    __syncthreads();
+    for (int j = tid; j < count; j += MS_THREADS) {
+        const uint64_t k = st_keys[j];
+        const uint32_t dst = s_delta[digit_of_key(k)] + (uint32_t)j;
+        if (dst < (uint32_t)n) {   // always true for consistent tables
+            keys_out[dst] = k;
+            vals_out[dst] = st_vals[j];
+        }
+    }
+}
+
 // A list longer than the in-block sort's capacity: the block sorts it where it lies, in global memory, by a
 // least-significant-digit radix sort over the 32 depth bits (four stable 8-bit passes; a pass in which every
 // element has the same digit is skipped). The list ping-pongs between its place in the tile-grouped buffers (a)
 // and its place in the output (b) and is copied to the output at the end if it stopped in (a). Stable, so the
 // result is again what a stable sort of the whole pair list gives for this tile.
 constexpr int LONG_THREADS = 512, LONG_ITEMS = 8;
-// bookkeeping (4 histograms, run, lstart, per-warp counts, scan, flag) in front of the reordered chunk
-constexpr int LONG_BOOK_BYTES = (6 * RADIX * 4 + (LONG_THREADS / 32) * RADIX * 4 + (RADIX / 32) * 4 + 16 + 15) / 16 * 16;
+constexpr int LONG_MAX_PASSES = 8;   // four depth digits, preceded by four value digits when ties go by value
+// bookkeeping (the digit histograms, run, lstart, per-warp counts, scan, flag) in front of the reordered chunk
+constexpr int LONG_BOOK_BYTES = ((LONG_MAX_PASSES + 2) * RADIX * 4 + (LONG_THREADS / 32) * RADIX * 4 + (RADIX / 32) * 4 + 16 + 15) / 16 * 16;
 constexpr int LONG_SMEM_BYTES = LONG_BOOK_BYTES + LONG_THREADS * LONG_ITEMS * 12;
 
-template <int THREADS, int ITEMS>
+// BY_VALUE: pairs with equal depth bits end up in ascending order of their values (four more digit passes, over
+// the value, run first); otherwise they keep the order they have in the tile-grouped list.
+template <int THREADS, int ITEMS, bool BY_VALUE>
 __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_t* vb, int n, unsigned char* smem)
 {
-    constexpr int WARPS = THREADS / 32, CHUNK = THREADS * ITEMS, PASSES = 32 / RADIX_BITS;
+    constexpr int WARPS = THREADS / 32, CHUNK = THREADS * ITEMS, PASSES = BY_VALUE ? 8 : 4, FIRST_DEPTH_PASS = PASSES - 4;
     static_assert(THREADS >= RADIX, "thread d owns digit value d");
-    static_assert(THREADS == LONG_THREADS && ITEMS == LONG_ITEMS, "the shared-memory layout is sized for these");
+    static_assert(THREADS == LONG_THREADS && ITEMS == LONG_ITEMS && PASSES <= LONG_MAX_PASSES, "the shared-memory layout is sized for these");
     uint32_t* hist = reinterpret_cast<uint32_t*>(smem);                     // [PASSES][RADIX] digit counts of the whole list
-    uint32_t* run = hist + PASSES * RADIX;                                  // [RADIX] where each digit's run continues
+    uint32_t* run = hist + LONG_MAX_PASSES * RADIX;                         // [RADIX] where each digit's run continues
     uint32_t* whist = run + RADIX;                                          // [WARPS][RADIX] per-warp counts of a chunk, then exclusive warp offsets
     uint32_t* scan = whist + WARPS * RADIX;                                 // [RADIX / 32]
     uint32_t* lstart = scan + RADIX / 32;                                   // [RADIX] where a digit's run starts inside the reordered chunk
@@ -612,15 +931,21 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
     uint32_t* stage_v = reinterpret_cast<uint32_t*>(smem + LONG_BOOK_BYTES + CHUNK * 8);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const unsigned lt = lanemask_lt();
-    // all four digit histograms from one read of the list
+    // digit of pass `pass`: a byte of the value (the first passes, when ties go by value) or of the depth bits
+    auto digit_of_pair = [&](uint64_t key, uint32_t val, int pass) {
+        const uint32_t word = pass < FIRST_DEPTH_PASS ? val : (uint32_t)key;
+        return (word >> ((pass & 3) * RADIX_BITS)) & (RADIX - 1);
+    };
+    // all digit histograms from one read of the list
     for (int i = tid; i < PASSES * RADIX; i += THREADS) hist[i] = 0;
     __syncthreads();
     for (int i0 = 0; i0 < n; i0 += THREADS * 4) {
-        uint32_t dw[4];
+        uint32_t dw[4], vw[4];
 #pragma unroll
         for (int u = 0; u < 4; u++) {
             const int i = i0 + u * THREADS + tid;
             dw[u] = i < n ? (uint32_t)ka[i] : 0u;
+            vw[u] = (BY_VALUE && i < n) ? va[i] : 0u;
         }
 #pragma unroll
         for (int u = 0; u < 4; u++) {
@@ -628,7 +953,7 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
             const unsigned live = __ballot_sync(FULL_MASK, ok);
 #pragma unroll
             for (int p = 0; p < PASSES; p++) {
-                const uint32_t d = (dw[u] >> (p * RADIX_BITS)) & (RADIX - 1);
+                const uint32_t d = digit_of_pair(dw[u], vw[u], p);
                 // depths of one tile often share their upper digits: one add for the warp instead of 32 colliding ones
                 const uint32_t d0 = __shfl_sync(FULL_MASK, d, __ffs(live | 0x80000000u) - 1);
                 const bool uniform = __all_sync(FULL_MASK, !ok || d == d0);
@@ -639,7 +964,6 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
     }
     uint64_t* src_k = ka; uint32_t* src_v = va; uint64_t* dst_k = kb; uint32_t* dst_v = vb;
     for (int pass = 0; pass < PASSES; pass++) {
-        const int shift = pass * RADIX_BITS;
         __syncthreads();   // the histograms are complete; the previous pass's stores are visible to the block
         if (tid == 0) *same = 0;
         __syncthreads();
@@ -687,7 +1011,7 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
 #pragma unroll
             for (int q = 0; q < ITEMS; q++) {
                 const bool ok = wb + q * 32 + lane < n;
-                const uint32_t d = ((uint32_t)key[q] >> shift) & (RADIX - 1);
+                const uint32_t d = digit_of_pair(key[q], val[q], pass);
                 volatile uint32_t* word = my_masks + (q & 1) * RADIX + d;
                 if (ok) atomicOr(const_cast<uint32_t*>(word), 1u << lane);
                 __syncwarp();
@@ -731,7 +1055,7 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
 #pragma unroll
             for (int q = 0; q < ITEMS; q++) {
                 if (wb + q * 32 + lane < n) {
-                    const uint32_t d = ((uint32_t)key[q] >> shift) & (RADIX - 1);
+                    const uint32_t d = digit_of_pair(key[q], val[q], pass);
                     const uint32_t pos = lstart[d] + whist[warp * RADIX + d] + rank[q];
                     stage_k[pos] = key[q];
                     stage_v[pos] = val[q];
@@ -741,10 +1065,11 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
             const int valid = min(CHUNK, n - c0);
             for (int j = tid; j < valid; j += THREADS) {
                 const uint64_t k = stage_k[j];
-                const uint32_t d = ((uint32_t)k >> shift) & (RADIX - 1);
+                const uint32_t v = stage_v[j];
+                const uint32_t d = digit_of_pair(k, v, pass);
                 const uint32_t pos = run[d] + ((uint32_t)j - lstart[d]);
                 dst_k[pos] = k;
-                dst_v[pos] = stage_v[j];
+                dst_v[pos] = v;
             }
             __syncthreads();
             if (tid < RADIX) run[tid] += chunk_count;
@@ -757,6 +1082,7 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
         for (int i = tid; i < n; i += THREADS) { kb[i] = src_k[i]; vb[i] = src_v[i]; }
 }
 
+template <bool BY_VALUE>
 __global__ void __launch_bounds__(LONG_THREADS, 2)
 long_list_kernel(uint64_t* keys_grouped, uint32_t* vals_grouped, uint64_t* keys_out, uint32_t* vals_out,
                  const int2* __restrict__ seg, const int* __restrict__ work_count, const uint32_t* __restrict__ work_tiles,
@@ -772,25 +1098,31 @@ long_list_kernel(uint64_t* keys_grouped, uint32_t* vals_grouped, uint64_t* keys_
         const int w = s_w;
         if (w >= work) break;
         const int2 r = seg[work_tiles[w]];
-        long_list_sort<LONG_THREADS, LONG_ITEMS>(keys_grouped + r.x, vals_grouped + r.x, keys_out + r.x, vals_out + r.x, r.y - r.x, s_long);
+        long_list_sort<LONG_THREADS, LONG_ITEMS, BY_VALUE>(keys_grouped + r.x, vals_grouped + r.x, keys_out + r.x, vals_out + r.x, r.y - r.x, s_long);
     }
 }
 
-// One block per tile: order the tile's pairs by (depth bits, position inside the tile's list) in shared memory,
-// then write keys and values in that order (the keys are rebuilt from the tile word and the sorted depths, the
-// values are gathered). The position makes equal depths keep their input order, i.e. the result is what a
-// stable sort of the whole list gives.
+// One block per tile: order the tile's pairs in shared memory, then write keys and values in that order (the keys
+// are rebuilt from the tile word and the sorted depths). Two orders, chosen at compile time:
+//   BY_VALUE == false: by (depth bits, position inside the tile's list). The position makes equal depths keep
+//     their input order, i.e. the result is what a stable sort of the whole list gives when the tile-grouped list
+//     is in input order (the stable path); the values are gathered by position at the end.
+//   BY_VALUE == true: by (depth bits, value). The result no longer depends on the order inside the tile-grouped
+//     list at all (the wait-free tile grouping leaves it arbitrary): the sorted list is a function of the SET of
+//     pairs. The values are read up front with the keys (coalesced) and travel inside the sort entries, so nothing
+//     is gathered at the end. A list whose keys carry bits above the sorted width (never the case for keys built
+//     by the preprocess stage) falls back to positions as the entries' low words, with ties in list order.
 //
 // The order is found by a bucket sort: depths of one tile are spread fairly evenly between the tile's nearest
 // and farthest splat, so CAP equal-width depth buckets receive about one element each. The depths stay in
 // registers; one shared-memory add per element counts its bucket and returns its arrival number; after a scan
-// of the counts the elements are stored bucket by bucket, and one thread per ELEMENT counts the smaller keys of
+// of the counts the elements are stored bucket by bucket, and one thread per ELEMENT counts the smaller entries of
 // its bucket, which is its final place. A tile whose depths pile up in one bucket (more than LOCAL_BUCKET_LIMIT
 // elements) is sorted by a bitonic network over the whole tile instead, so the cost stays bounded for any input.
 //
 // Three instantiations cover list lengths (0,1024], (1024,2048] and (2048,LOCAL_CAP] with shared-memory
 // footprints that grow with the class, so that the many short lists run with many blocks per SM; each is a
-// small grid of persistent blocks that walks the work list segments_kernel built for its class (an empty
+// small grid of persistent blocks that walks the work list built for its class (an empty
 // class costs one launch of blocks that return at once). Longer lists go to long_list_kernel.
 #ifndef FGS_LOCAL_BUCKET_LIMIT
 #define FGS_LOCAL_BUCKET_LIMIT 192
@@ -810,7 +1142,7 @@ __device__ unsigned long long g_local_cycles[8];
 #endif
 
 // BLOCKS: resident blocks per SM that the shared-memory footprint allows; it caps the registers accordingly.
-template <int CAP, int THREADS, int BLOCKS>
+template <int CAP, int THREADS, int BLOCKS, bool BY_VALUE>
 __global__ void __launch_bounds__(THREADS, BLOCKS)
 local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __restrict__ vals_grouped,
                   uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
@@ -820,8 +1152,8 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     constexpr int NB = local_buckets(CAP);   // depth buckets
     constexpr int ITEMS = CAP / THREADS;     // elements per thread: positions tid + q * THREADS of the list
     extern __shared__ __align__(16) unsigned char s_local[];
-    uint64_t* a = reinterpret_cast<uint64_t*>(s_local);                         // [CAP] depth << 32 | position, sorted
-    uint64_t* bk = reinterpret_cast<uint64_t*>(s_local + CAP * 8);              // [CAP] the same keys, bucket by bucket
+    uint64_t* a = reinterpret_cast<uint64_t*>(s_local);                         // [CAP] depth << 32 | low word, sorted
+    uint64_t* bk = reinterpret_cast<uint64_t*>(s_local + CAP * 8);              // [CAP] the same entries, bucket by bucket
     uint32_t* start = reinterpret_cast<uint32_t*>(s_local + CAP * 16);          // [NB + 1]
     uint32_t* cursor = start + NB + 1;                                          // [NB]
     __shared__ uint32_t s_min, s_max, s_tile_word, s_wsum[THREADS / 32];
@@ -833,13 +1165,16 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     long long lt_prev_ = clock64();
 #endif
     const int work = *work_count;
-    // Persistent blocks draw lists of the class's work list from a ticket counter. The keys of the NEXT list are
-    // requested while the current one is ranked and written out, so their latency is not waited for.
-    auto fetch = [&](const int2 rr, uint64_t (&kk)[ITEMS]) {
+    // Persistent blocks draw lists of the class's work list from a ticket counter. The keys (and values) of the NEXT
+    // list are requested while the current one is ranked and written out, so their latency is not waited for.
+    uint64_t kk[ITEMS];
+    uint32_t vv[BY_VALUE ? ITEMS : 1];
+    auto fetch = [&](const int2 rr) {
 #pragma unroll
         for (int q = 0; q < ITEMS; q++) {
             const int i = tid + q * THREADS;
             kk[q] = i < rr.y - rr.x ? __ldg(keys_grouped + rr.x + i) : 0ull;
+            if (BY_VALUE) vv[q] = i < rr.y - rr.x ? __ldg(vals_grouped + rr.x + i) : 0u;
         }
     };
     if (tid == 0) {
@@ -848,13 +1183,12 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     }
     __syncthreads();
     int2 r = s_seg;
-    uint64_t kk[ITEMS];
-    fetch(r, kk);
+    fetch(r);
     while (r.y >= r.x) {
     const int n = r.y - r.x;
     __syncthreads();   // the previous list's shared memory, and s_seg, are no longer read
     int next_ticket = 0;
-    if (tid == 0) { s_min = 0xFFFFFFFFu; s_max = 0u; s_piled = 0; next_ticket = atomicAdd(work_ticket, 1); }
+    if (tid == 0) { s_min = 0xFFFFFFFFu; s_max = 0u; s_piled = 0; s_tile_word = (uint32_t)(kk[0] >> 32); next_ticket = atomicAdd(work_ticket, 1); }
     for (int i = tid; i < NB; i += THREADS) cursor[i] = 0;
     FGS_LT(0);
     // The depths stay in registers until they are placed. The high words of a list's keys all hold the tile,
@@ -869,31 +1203,34 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
             high_and &= (uint32_t)(kk[q] >> 32); high_or |= (uint32_t)(kk[q] >> 32);
         }
     }
-    if (tid == 0) s_tile_word = (uint32_t)(kk[0] >> 32);
-    __syncthreads();   // cursor[] is zero, s_min / s_max are set up
+    __syncthreads();   // cursor[] is zero, s_min / s_max / s_tile_word are set up
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         lo = min(lo, __shfl_xor_sync(FULL_MASK, lo, o));
         hi = max(hi, __shfl_xor_sync(FULL_MASK, hi, o));
     }
     if (lane == 0) { atomicMin(&s_min, lo); atomicMax(&s_max, hi); }
-    __syncthreads();
+    const uint32_t tile_word = s_tile_word;
+    const int mixed = __syncthreads_or(n > tid && (high_and != tile_word || high_or != tile_word));
     FGS_LT(1);
+    // low word of the sort entries: the value (ties by value, nothing to gather later) or the position in the list
+    const bool by_value = BY_VALUE && !mixed;
+    uint32_t low[ITEMS];
+#pragma unroll
+    for (int q = 0; q < ITEMS; q++) low[q] = by_value ? vv[BY_VALUE ? q : 0] : (uint32_t)(tid + q * THREADS);
     uint32_t next_tile = 0;
     if (tid == 0 && next_ticket < work) next_tile = __ldg(work_tiles + next_ticket);
-    const uint32_t tile_word = s_tile_word;
-    const int mixed_here = n > tid && (high_and != tile_word || high_or != tile_word);
     const uint32_t dmin = s_min, span = s_max - s_min;
     bool gathered = false, fetched = false;
-    if (span == 0) {
-        // all depths equal: the input order is the sorted order
+    if (span == 0 && !by_value) {
+        // all depths equal and ties in list order: the input order is the sorted order
 #pragma unroll
         for (int q = 0; q < ITEMS; q++) {
             const int i = tid + q * THREADS;
-            if (i < n) a[i] = ((uint64_t)d[q] << 32) | (uint32_t)i;
+            if (i < n) a[i] = ((uint64_t)d[q] << 32) | low[q];
         }
         gathered = true;
-    } else {
+    } else if (span != 0) {
         // bucket of a depth: the high word of (depth - nearest depth) * mult, with mult about NB * 2^32 / (span + 1)
         // (rounded in float, hence the clamp): integer arithmetic, monotone in the depth
         const float ratio = 4294967296.0f * (float)NB / ((float)span + 1.0f);
@@ -939,21 +1276,24 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
 #pragma unroll
             for (int q = 0; q < ITEMS; q++) {
                 const int i = tid + q * THREADS;
-                if (i < n) bk[start[where[q] & 0xFFFFu] + (where[q] >> 16)] = ((uint64_t)d[q] << 32) | (uint32_t)i;
+                if (i < n) bk[start[where[q] & 0xFFFFu] + (where[q] >> 16)] = ((uint64_t)d[q] << 32) | low[q];
             }
-            fetch(s_seg, kk);   // the registers are free again: request the next list's keys
+            fetch(s_seg);   // the registers are free again: request the next list's keys
             fetched = true;
             __syncthreads();
             FGS_LT(4);
-            // every bucket in order of (depth, position): one thread per ELEMENT counts the smaller keys of its
-            // bucket (keys are unique), so a bucket of L elements costs L steps on L threads, not L^2 on one;
-            // the element then goes to its final place in a[]
+            // every bucket in order: one thread per ELEMENT counts the smaller entries of its bucket, so a bucket of
+            // L elements costs L steps on L threads, not L^2 on one; the element then goes to its final place in
+            // a[]. Entries that are equal as a whole (the same key AND value twice in the input) go in bucket order.
             for (int x = tid; x < n; x += THREADS) {
                 const uint64_t kc = bk[x];
                 const int bkt = bucket_of((uint32_t)(kc >> 32));
                 const int s0 = (int)start[bkt], s1 = (int)start[bkt + 1];
                 int rank = 0;
-                for (int y = s0; y < s1; y++) rank += bk[y] < kc;
+                for (int y = s0; y < s1; y++) {
+                    const uint64_t other = bk[y];
+                    rank += (other < kc) || (other == kc && y < x);
+                }
                 a[s0 + rank] = kc;
             }
             FGS_LT(5);
@@ -962,8 +1302,15 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
 #pragma unroll
             for (int q = 0; q < ITEMS; q++) {
                 const int i = tid + q * THREADS;
-                if (i < n) a[i] = ((uint64_t)d[q] << 32) | (uint32_t)i;
+                if (i < n) a[i] = ((uint64_t)d[q] << 32) | low[q];
             }
+        }
+    } else {
+        // all depths equal, ties by value: the network below orders the values
+#pragma unroll
+        for (int q = 0; q < ITEMS; q++) {
+            const int i = tid + q * THREADS;
+            if (i < n) a[i] = ((uint64_t)d[q] << 32) | low[q];
         }
     }
     if (span == 0 && tid == 0) s_seg = next_ticket < work ? seg[next_tile] : make_int2(0, -1);
@@ -988,15 +1335,19 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
         }
     }
     const int2 r_next = s_seg;
-    if (!fetched) fetch(r_next, kk);
-    const int mixed = __syncthreads_or(mixed_here);
-    // a[i] = depth << 32 | position of the i-th smallest key
+    if (!fetched) fetch(r_next);
+    // a[i] = depth << 32 | low word of the i-th smallest entry
     for (int i = tid; i < n; i += THREADS) {
         const uint64_t k = a[i];
-        const uint32_t from = (uint32_t)k;
-        const uint32_t high = mixed ? (uint32_t)(__ldg(keys_grouped + r.x + from) >> 32) : tile_word;
-        keys_out[r.x + i] = ((uint64_t)high << 32) | (k >> 32);
-        vals_out[r.x + i] = __ldg(vals_grouped + r.x + from);
+        const uint32_t low_word = (uint32_t)k;
+        if (by_value) {
+            keys_out[r.x + i] = ((uint64_t)tile_word << 32) | (k >> 32);
+            vals_out[r.x + i] = low_word;
+        } else {
+            const uint32_t high = mixed ? (uint32_t)(__ldg(keys_grouped + r.x + low_word) >> 32) : tile_word;
+            keys_out[r.x + i] = ((uint64_t)high << 32) | (k >> 32);
+            vals_out[r.x + i] = __ldg(vals_grouped + r.x + low_word);
+        }
     }
     FGS_LT(6);
     r = r_next;
@@ -1043,13 +1394,56 @@ int g_debug_plain_sort = 0;
 enum { LAUNCH_HISTOGRAM = 0, LAUNCH_DIGIT_PASS = 1, LAUNCH_SEGMENTS = 2, LAUNCH_LOCAL_SORT = 3 };
 constexpr int MAX_LAUNCHES = 2 * MAX_PASSES + 8;
 
+// Order of pairs whose sorted key bits are equal.
+enum { ORDER_BY_VALUE = 0,   // ascending value: the wait-free tile grouping (images of at most 2^16 tile values)
+       ORDER_STABLE = 1 };   // input order, as the reference's library sort leaves them: look-back digit passes
+
+// Per-device facts and one-time kernel attribute settings, filled under a lock on the first sort of a device.
+struct SortDevice { bool ready; int sm_count; };
+static SortDevice g_sort_device[64];
+static std::mutex g_sort_device_mutex;
+
+static int sort_device(int* dev_out, int* sm_count_out)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FGS_ERR_CUDA;
+    std::lock_guard<std::mutex> guard(g_sort_device_mutex);
+    SortDevice& d = g_sort_device[dev];
+    if (!d.ready) {
+        if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || d.sm_count <= 0)
+            return FGS_ERR_CUDA;
+        cudaError_t e = cudaSuccess;
+#define FGS_OPT_IN(SHIFT) if (e == cudaSuccess) e = cudaFuncSetAttribute(onesweep_kernel<SHIFT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SORT_SMEM_BYTES);
+        FGS_OPT_IN(0) FGS_OPT_IN(8) FGS_OPT_IN(16) FGS_OPT_IN(24) FGS_OPT_IN(32) FGS_OPT_IN(40) FGS_OPT_IN(48) FGS_OPT_IN(56)
+#undef FGS_OPT_IN
+        auto opt_in = [&](const void* fn, int bytes) {
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        };
+        opt_in((const void*)local_sort_kernel<LOCAL_CAP, 256, 2, false>, local_smem_bytes<LOCAL_CAP>());
+        opt_in((const void*)local_sort_kernel<LOCAL_CAP, 256, 2, true>, local_smem_bytes<LOCAL_CAP>());
+        opt_in((const void*)local_sort_kernel<2048, 256, 4, false>, local_smem_bytes<2048>());
+        opt_in((const void*)local_sort_kernel<2048, 256, 4, true>, local_smem_bytes<2048>());
+        opt_in((const void*)long_list_kernel<false>, LONG_SMEM_BYTES);
+        opt_in((const void*)long_list_kernel<true>, LONG_SMEM_BYTES);
+        opt_in((const void*)multisplit_kernel<false>, MS_SMEM_BYTES);
+        opt_in((const void*)multisplit_kernel<true>, MS_SMEM_BYTES);
+        opt_in((const void*)tile_hist_kernel, TILE_HIST_SMEM_VALUES * 4);
+        if (e != cudaSuccess) return FGS_ERR_CUDA;
+        d.ready = true;
+    }
+    *dev_out = dev;
+    *sm_count_out = d.sm_count;
+    return FGS_OK;
+}
+
 // `events`, when given, receives one recorded event before the first kernel and one after every kernel;
 // `kinds` the kind of each kernel; `num_launches` how many there were.
 static int sort_pairs_impl(int num_rendered, int width, int height, int block_x, int block_y,
                            void* temp, size_t temp_bytes,
                            const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
                            uint64_t* keys_sorted, uint32_t* values_sorted, void* stream,
-                           cudaEvent_t* events, int* kinds, int* num_launches, const int* n_dev = nullptr)
+                           cudaEvent_t* events, int* kinds, int* num_launches, const int* n_dev = nullptr,
+                           int order = ORDER_BY_VALUE)
 {
     // With n_dev the count lives on the device (clamped to num_rendered, which is then the buffers' capacity).
     if (num_launches) *num_launches = 0;
@@ -1071,46 +1465,36 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
     if (passes > MAX_PASSES) return FGS_ERR_BAD_ARG;
     const int tile_bits = end_bit - 32;
     const int depth_passes = 32 / RADIX_BITS;
-    // Tile-bucketed path: digit passes over the tile bits only, then an in-block sort of every tile by depth.
+    // Tile-bucketed path: the pairs are grouped by tile first, then every tile is sorted by depth inside a block.
     const int tile_passes = passes - depth_passes;
     // With lists this long on average, the tile passes plus the long lists' own depth passes are no fewer than
     // the plain sort's (the count is only known here when it is not on the device).
     const bool very_long_lists = n_dev == nullptr && (int64_t)n > (int64_t)tiles * 16384;
     const bool bucketed = !g_debug_plain_sort && !very_long_lists && tile_bits <= MAX_TILE_BITS && tile_passes >= 1;
+    const bool by_value = bucketed && order == ORDER_BY_VALUE;
 
     char* base = static_cast<char*>(temp);
     uint32_t* tickets = reinterpret_cast<uint32_t*>(base + L.tickets_off);
     uint32_t* hist = reinterpret_cast<uint32_t*>(base + L.hist_off);
+    uint32_t* tile_count = reinterpret_cast<uint32_t*>(base + L.tilecnt_off);
     uint32_t* status_words = reinterpret_cast<uint32_t*>(base + L.status_off);
     int2* seg = reinterpret_cast<int2*>(base + L.seg_off);
+    uint32_t* tile_cursor = reinterpret_cast<uint32_t*>(base + L.cursor_off);
+    uint32_t* bucket_tables = reinterpret_cast<uint32_t*>(base + L.bucket_off);
     uint64_t* alt_keys = reinterpret_cast<uint64_t*>(base + L.alt_keys_off);
     uint32_t* alt_vals = reinterpret_cast<uint32_t*>(base + L.alt_vals_off);
 
-    static bool smem_opt_in[64];
-    static int sm_count[64];
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FGS_ERR_CUDA;
-    if (!smem_opt_in[dev]) {
-        if (cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count[dev] <= 0)
-            return FGS_ERR_CUDA;
-        cudaError_t e = cudaSuccess;
-#define FGS_OPT_IN(SHIFT) if (e == cudaSuccess) e = cudaFuncSetAttribute(onesweep_kernel<SHIFT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SORT_SMEM_BYTES);
-        FGS_OPT_IN(0) FGS_OPT_IN(8) FGS_OPT_IN(16) FGS_OPT_IN(24) FGS_OPT_IN(32) FGS_OPT_IN(40) FGS_OPT_IN(48) FGS_OPT_IN(56)
-#undef FGS_OPT_IN
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<LOCAL_CAP, 256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<LOCAL_CAP>());
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(local_sort_kernel<2048, 256, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, local_smem_bytes<2048>());
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(long_list_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LONG_SMEM_BYTES);
-        if (e != cudaSuccess) return FGS_ERR_CUDA;
-        smem_opt_in[dev] = true;
-    }
+    int dev = 0, sms = 0;
+    if (sort_device(&dev, &sms) != FGS_OK) return FGS_ERR_CUDA;
 
-    const int slots = bucketed ? tile_passes : passes;   // ticket counters and look-back regions in use: one per digit pass
+    // ticket counters and look-back regions in use: one per look-back digit pass (none on the wait-free path)
+    const int slots = by_value ? 0 : (bucketed ? tile_passes : passes);
     if (n_dev == nullptr) {
         const size_t clear_bytes = L.status_off + (size_t)slots * L.parts * RADIX * 4;
         if (cudaMemsetAsync(base, 0, clear_bytes, st) != cudaSuccess) return FGS_ERR_CUDA;
     } else {
-        clear_bookkeeping_kernel<<<sm_count[dev] * 8, 256, 0, st>>>(reinterpret_cast<uint32_t*>(base), L.status_off / 4, status_words,
-                                                                slots, L.parts, n, n_dev);
+        clear_bookkeeping_kernel<<<sms * 8, 256, 0, st>>>(reinterpret_cast<uint32_t*>(base), L.status_off / 4, status_words,
+                                                          slots, L.parts, n, n_dev);
     }
 
     int launches = 0;
@@ -1120,14 +1504,10 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         launches++;
     };
     if (events) cudaEventRecord(events[0], st);
-    int hist_blocks = L.parts < 148 * 8 ? L.parts : 148 * 8;
-    // the bucketed path needs the tile digits' counts only
-    histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, n_dev, bucketed ? depth_passes : 0, passes, end_bit, hist);
-    mark(LAUNCH_HISTOGRAM);
 
-    const int resident = PASS_BLOCKS_PER_SM * sm_count[dev];   // persistent blocks
+    const int resident = PASS_BLOCKS_PER_SM * sms;   // persistent blocks
     const int grid_blocks = L.parts < resident ? L.parts : resident;
-    // one digit pass: digit `p` of the key, bookkeeping slot `slot`
+    // one look-back digit pass: digit `p` of the key, bookkeeping slot `slot`
     auto digit_pass = [&](int p, int slot, const uint64_t* src_k, const uint32_t* src_v, uint64_t* dst_k, uint32_t* dst_v) -> int {
         const int shift = p * RADIX_BITS;
         const int bits = (end_bit - shift) < RADIX_BITS ? (end_bit - shift) : RADIX_BITS;
@@ -1146,6 +1526,61 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         return FGS_OK;
     };
 
+    const int tile_values = 1 << (tile_bits < MAX_TILE_BITS ? tile_bits : MAX_TILE_BITS);
+    int* class_count = reinterpret_cast<int*>(base + L.flag_off) + 1;   // behind the spare word, cleared above: the classes' list lengths, then their tickets
+    uint32_t* class_tiles = reinterpret_cast<uint32_t*>(base + L.class_off);
+    auto grid_for = [&](int per_sm) { return tile_values < per_sm * sms ? tile_values : per_sm * sms; };
+
+    if (by_value) {
+        // ---- wait-free tile grouping, then tile sorts by (depth bits, value) ----
+        const int in_smem = tile_values <= TILE_HIST_SMEM_VALUES && n >= 4 * tile_values;
+        int hist_blocks = (int)(((int64_t)n + 65535) / 65536);
+        hist_blocks = hist_blocks < 1 ? 1 : (hist_blocks > sms ? sms : hist_blocks);
+        tile_hist_kernel<<<hist_blocks, TILE_HIST_THREADS, in_smem ? (size_t)tile_values * 4 : 0, st>>>(
+            keys_unsorted, n, n_dev, (uint32_t)tile_values - 1u, tile_values, in_smem, tile_count);
+        mark(LAUNCH_HISTOGRAM);
+        // lower and upper halves of the tile bits: at most 8 bits each
+        const int lo_bits = tile_bits <= RADIX_BITS ? tile_bits : tile_bits / 2;
+        const int buckets = tile_values >> lo_bits;
+        tile_scan_kernel<<<1, TILE_SCAN_THREADS, 0, st>>>(tile_count, tile_values, lo_bits, seg, tile_cursor, bucket_tables,
+                                                          class_count, class_tiles);
+        mark(LAUNCH_SEGMENTS);
+        const int ms_parts = (int)(((int64_t)n + MS_PART - 1) / MS_PART);
+        const uint64_t* src_k = keys_unsorted;
+        const uint32_t* src_v = values_unsorted;
+        if (buckets > 1) {
+            multisplit_kernel<false><<<ms_parts, MS_THREADS, MS_SMEM_BYTES, st>>>(
+                src_k, src_v, keys_sorted, values_sorted, n, n_dev, (uint32_t)tile_values - 1u, lo_bits, buckets,
+                bucket_tables, bucket_tables /* the coarse buckets' cursors lead the tables */);
+            mark(LAUNCH_DIGIT_PASS);
+            src_k = keys_sorted;
+            src_v = values_sorted;
+        }
+        // every coarse bucket is cut into partitions of its own: at most one ragged partition more per bucket
+        multisplit_kernel<true><<<ms_parts + buckets, MS_THREADS, MS_SMEM_BYTES, st>>>(
+            src_k, src_v, alt_keys, alt_vals, n, n_dev, (uint32_t)tile_values - 1u, lo_bits, buckets, bucket_tables, tile_cursor);
+        mark(LAUNCH_DIGIT_PASS);
+        local_sort_kernel<1024, 128, 8, true><<<grid_for(12), 128, local_smem_bytes<1024>(), st>>>(
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 0, class_tiles, class_count + LOCAL_CLASSES + 0);
+        mark(LAUNCH_LOCAL_SORT);
+        local_sort_kernel<2048, 256, 4, true><<<grid_for(6), 256, local_smem_bytes<2048>(), st>>>(
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 1, class_tiles + MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 1);
+        mark(LAUNCH_LOCAL_SORT);
+        local_sort_kernel<LOCAL_CAP, 256, 2, true><<<grid_for(3), 256, local_smem_bytes<LOCAL_CAP>(), st>>>(
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 2, class_tiles + 2 * MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 2);
+        mark(LAUNCH_LOCAL_SORT);
+        long_list_kernel<true><<<grid_for(2), LONG_THREADS, LONG_SMEM_BYTES, st>>>(
+            alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 3, class_tiles + 3 * MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 3);
+        mark(LAUNCH_LOCAL_SORT);
+        if (num_launches) *num_launches = launches;
+        return launch_status();
+    }
+
+    int hist_blocks = L.parts < sms * 8 ? L.parts : sms * 8;
+    // the bucketed path needs the tile digits' counts only
+    histogram_kernel<<<hist_blocks, HIST_THREADS, 0, st>>>(keys_unsorted, n, n_dev, bucketed ? depth_passes : 0, passes, end_bit, hist);
+    mark(LAUNCH_HISTOGRAM);
+
     if (bucketed) {
         // tile digits, least significant first; the last one leaves the tile-grouped list in the alternate buffers
         const uint64_t* src_k = keys_unsorted;
@@ -1159,24 +1594,19 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
             src_k = dst_k;
             src_v = dst_v;
         }
-        const int tile_values = 1 << tile_bits;
-        int* class_count = reinterpret_cast<int*>(base + L.flag_off) + 1;   // behind the spare word, cleared above: the classes' list lengths, then their tickets
-        uint32_t* class_tiles = reinterpret_cast<uint32_t*>(base + L.class_off);
         segments_kernel<<<(tile_values + SEG_TILES - 1) / SEG_TILES, SEG_THREADS, 0, st>>>(alt_keys, n, n_dev, tile_values, (uint32_t)tile_values - 1u, seg,
                                                                   class_count, class_tiles);
         mark(LAUNCH_SEGMENTS);
-        const int sms = sm_count[dev];
-        auto grid_for = [&](int per_sm) { return tile_values < per_sm * sms ? tile_values : per_sm * sms; };
-        local_sort_kernel<1024, 128, 9><<<grid_for(12), 128, local_smem_bytes<1024>(), st>>>(
+        local_sort_kernel<1024, 128, 9, false><<<grid_for(12), 128, local_smem_bytes<1024>(), st>>>(
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 0, class_tiles, class_count + LOCAL_CLASSES + 0);
         mark(LAUNCH_LOCAL_SORT);
-        local_sort_kernel<2048, 256, 4><<<grid_for(6), 256, local_smem_bytes<2048>(), st>>>(
+        local_sort_kernel<2048, 256, 4, false><<<grid_for(6), 256, local_smem_bytes<2048>(), st>>>(
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 1, class_tiles + MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 1);
         mark(LAUNCH_LOCAL_SORT);
-        local_sort_kernel<LOCAL_CAP, 256, 2><<<grid_for(3), 256, local_smem_bytes<LOCAL_CAP>(), st>>>(
+        local_sort_kernel<LOCAL_CAP, 256, 2, false><<<grid_for(3), 256, local_smem_bytes<LOCAL_CAP>(), st>>>(
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 2, class_tiles + 2 * MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 2);
         mark(LAUNCH_LOCAL_SORT);
-        long_list_kernel<<<grid_for(2), LONG_THREADS, LONG_SMEM_BYTES, st>>>(
+        long_list_kernel<false><<<grid_for(2), LONG_THREADS, LONG_SMEM_BYTES, st>>>(
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 3, class_tiles + 3 * MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 3);
         mark(LAUNCH_LOCAL_SORT);
     }
@@ -1211,7 +1641,7 @@ int sort_pairs_device_count(int capacity, const int* n_dev, int width, int heigh
 }
 } // namespace fgs
 
-// Test hook: non-zero makes the next sorts skip the tile-bucketed path and run the plain digit passes only.
+// Test hook: non-zero makes the next sorts skip the tile-bucketed paths and run the plain digit passes only.
 extern "C" void fgs_debug_sort_plain(int on) { fgs::g_debug_plain_sort = on; }
 
 extern "C" int fgs_sort_pairs(int num_rendered, int width, int height, int block_x, int block_y,
@@ -1221,6 +1651,16 @@ extern "C" int fgs_sort_pairs(int num_rendered, int width, int height, int block
 {
     return fgs::sort_pairs_impl(num_rendered, width, height, block_x, block_y, temp, temp_bytes, keys_unsorted,
                                 values_unsorted, keys_sorted, values_sorted, stream, nullptr, nullptr, nullptr);
+}
+
+extern "C" int fgs_sort_pairs_stable(int num_rendered, int width, int height, int block_x, int block_y,
+                                     void* temp, size_t temp_bytes,
+                                     const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                                     uint64_t* keys_sorted, uint32_t* values_sorted, void* stream)
+{
+    return fgs::sort_pairs_impl(num_rendered, width, height, block_x, block_y, temp, temp_bytes, keys_unsorted,
+                                values_unsorted, keys_sorted, values_sorted, stream, nullptr, nullptr, nullptr, nullptr,
+                                fgs::ORDER_STABLE);
 }
 
 extern "C" int fgs_sort_pairs_profile(int num_rendered, int width, int height, int block_x, int block_y,
@@ -1254,19 +1694,10 @@ extern "C" int fgs_sort_pairs_profile(int num_rendered, int width, int height, i
 #define FGS_STATIC_SORT_MAX_PAIRS (1 << 18)
 namespace fgs {
 namespace {
-constexpr size_t static_sort_bytes()
-{
-    // the layout of make_layout(FGS_STATIC_SORT_MAX_PAIRS), spelled out so that it is a compile-time constant
-    constexpr size_t parts = (FGS_STATIC_SORT_MAX_PAIRS + SORT_PART - 1) / SORT_PART;
-    constexpr size_t status_off = 256 + (size_t)MAX_PASSES * RADIX * 4;
-    constexpr size_t seg_off = (status_off + (size_t)MAX_PASSES * parts * RADIX * 4 + 255) / 256 * 256;
-    constexpr size_t class_off = (seg_off + (size_t)MAX_TILE_VALUES * 8 + 255) / 256 * 256;
-    constexpr size_t alt_keys_off = (class_off + (size_t)LOCAL_CLASSES * MAX_TILE_VALUES * 4 + 255) / 256 * 256;
-    constexpr size_t alt_vals_off = (alt_keys_off + (size_t)FGS_STATIC_SORT_MAX_PAIRS * 8 + 255) / 256 * 256;
-    return (alt_vals_off + (size_t)FGS_STATIC_SORT_MAX_PAIRS * 4 + 255) / 256 * 256;
-}
+constexpr size_t static_sort_bytes() { return layout_total(FGS_STATIC_SORT_MAX_PAIRS); }
 static __device__ __align__(256) unsigned char g_static_sort_scratch[static_sort_bytes()];
-void* g_static_sort_ptr[64];   // device address of the array, per device, resolved on first use
+void* g_static_sort_ptr[64];   // device address of the array, per device, resolved on first use (under the lock below)
+std::mutex g_static_sort_mutex;
 } // namespace
 } // namespace fgs
 
@@ -1277,17 +1708,23 @@ extern "C" int fgs_sort_pairs_static(int num_rendered, int width, int height, in
                                      uint64_t* keys_sorted, uint32_t* values_sorted, void* stream)
 {
     using namespace fgs;
-    if (num_rendered < 0 || num_rendered > FGS_STATIC_SORT_MAX_PAIRS) return FGS_ERR_TEMP_TOO_SMALL;
+    if (num_rendered < 0) return FGS_ERR_BAD_ARG;
+    if (num_rendered > FGS_STATIC_SORT_MAX_PAIRS) return FGS_ERR_TEMP_TOO_SMALL;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FGS_ERR_CUDA;
-    if (!g_static_sort_ptr[dev]) {
-        // In host code the array's name is only a handle; the address kernels can use comes from the runtime,
-        // asked for with this device current.
-        void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_static_sort_scratch) != cudaSuccess || !p) return FGS_ERR_CUDA;
-        g_static_sort_ptr[dev] = p;
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(g_static_sort_mutex);
+        if (!g_static_sort_ptr[dev]) {
+            // In host code the array's name is only a handle; the address kernels can use comes from the runtime,
+            // asked for with this device current.
+            void* p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_static_sort_scratch) != cudaSuccess || !p) return FGS_ERR_CUDA;
+            g_static_sort_ptr[dev] = p;
+        }
+        scratch = g_static_sort_ptr[dev];
     }
     if (make_layout(FGS_STATIC_SORT_MAX_PAIRS).total > static_sort_bytes()) return FGS_ERR_TEMP_TOO_SMALL;
-    return sort_pairs_impl(num_rendered, width, height, block_x, block_y, g_static_sort_ptr[dev], static_sort_bytes(),
+    return sort_pairs_impl(num_rendered, width, height, block_x, block_y, scratch, static_sort_bytes(),
                            keys_unsorted, values_unsorted, keys_sorted, values_sorted, stream, nullptr, nullptr, nullptr);
 }

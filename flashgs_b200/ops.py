@@ -112,8 +112,10 @@ def get_sort_buffer_size(num_rendered: int) -> int:
 
 def sort_gaussian(num_rendered, width, height, block_x, block_y, list_sorting_space,
                   gaussian_keys_unsorted, gaussian_values_unsorted,
-                  gaussian_keys_sorted, gaussian_values_sorted) -> None:
-    """csrc/pybind.cpp:152-163."""
+                  gaussian_keys_sorted, gaussian_values_sorted, stable: bool = False) -> None:
+    """csrc/pybind.cpp:152-163. Pairs with identical sorted key bits come out in ascending order of their values
+    (the frame is then the same bytes every run); ``stable=True`` keeps them in input order, which is the reference's
+    library-sort contract, through the slower look-back passes (see ``fgs_sort_pairs`` in include/flashgs_b200.h)."""
     n = int(num_rendered)
     ki = _in(gaussian_keys_unsorted, "gaussian_keys_unsorted", torch.int64)
     vi = _in(gaussian_values_unsorted, "gaussian_values_unsorted", torch.int32)
@@ -124,9 +126,9 @@ def sort_gaussian(num_rendered, width, height, block_x, block_y, list_sorting_sp
     tmp = list_sorting_space
     if not tmp.is_cuda or not tmp.is_contiguous():
         raise RuntimeError("list_sorting_space must be a contiguous CUDA tensor")
-    st = _L.fgs_sort_pairs(n, int(width), int(height), int(block_x), int(block_y),
-                           tmp.data_ptr(), tmp.numel() * tmp.element_size(),
-                           ki.data_ptr(), vi.data_ptr(), ko.data_ptr(), vo.data_ptr(), _stream())
+    st = (_L.fgs_sort_pairs_stable if stable else _L.fgs_sort_pairs)(n, int(width), int(height), int(block_x), int(block_y),
+        tmp.data_ptr(), tmp.numel() * tmp.element_size(),
+        ki.data_ptr(), vi.data_ptr(), ko.data_ptr(), vo.data_ptr(), _stream())
     _lib.check("sort_gaussian", st)
 
 

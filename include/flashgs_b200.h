@@ -123,27 +123,43 @@ int fgs_preprocess_strip_culled(int P, const float* positions, const float* shs,
 size_t fgs_sort_temp_bytes(int64_t num_rendered);
 
 /*
- * Stable radix sort of (key, value) pairs on key bits [0, 32 + bit_length(#tiles)).
- * Replaces flashgs::sort_gaussian (csrc/ops.h:41-45, csrc/cuda_rasterizer/sort.cu:28-44).
- * Inputs are left intact; outputs go to keys_sorted / values_sorted; `temp` must be
- * 16-byte aligned and at least fgs_sort_temp_bytes(num_rendered) bytes.
+ * Sort of (key, value) pairs on key bits [0, 32 + bit_length(#tiles)); bits at or above that width travel with
+ * their keys and are never compared. Replaces flashgs::sort_gaussian (csrc/ops.h:41-45,
+ * csrc/cuda_rasterizer/sort.cu:28-44). Inputs are left intact; outputs go to keys_sorted / values_sorted; `temp`
+ * must be 16-byte aligned and at least fgs_sort_temp_bytes(num_rendered) bytes.
+ *
+ * Pairs whose sorted bits are EQUAL (two Gaussians of one tile at exactly the same depth): the reference's
+ * library sort is stable, so it leaves them in input order -- and the input order of the raster path is the
+ * arrival order of preprocess's atomics, which changes from run to run. fgs_sort_pairs returns them in ascending
+ * order of their values (Gaussian indices) instead, for images of at most 65536 tile values: that is the stable
+ * result for one of the possible arrival orders, it makes the sorted list a function of the SET of pairs (the same
+ * frame twice gives the same bytes), and it lets the sort group the pairs by tile without any block waiting for
+ * another. (Keys that carry bits above the sorted width, and images with more tiles, keep input order.)
+ * fgs_sort_pairs_stable has the same signature and the library sort's exact contract -- equal keys in input
+ * order, always -- at the price of look-back digit passes; use it where the pair list does not come from
+ * fgs_preprocess and its order matters.
  */
 int fgs_sort_pairs(int num_rendered, int width, int height, int block_x, int block_y,
                    void* temp, size_t temp_bytes,
                    const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
                    uint64_t* keys_sorted, uint32_t* values_sorted, void* stream);
+int fgs_sort_pairs_stable(int num_rendered, int width, int height, int block_x, int block_y,
+                          void* temp, size_t temp_bytes,
+                          const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                          uint64_t* keys_sorted, uint32_t* values_sorted, void* stream);
 
 /*
  * fgs_sort_pairs for callers that have no scratch buffer to give and must not allocate one: code that runs
  * where device allocation is off limits (inside another framework's memory plan, in a callback, in a process
  * whose allocator is owned by someone else). It has no counterpart in the reference, whose sort always takes
- * caller scratch. The scratch lives in a fixed array inside the library (about 5.3 MB that every GPU loading
+ * caller scratch. The scratch lives in a fixed array inside the library (about 5.9 MB that every GPU loading
  * the library holds until the process ends), so the call is limited to fgs_sort_static_max_pairs() = 262144
- * pairs and returns FGS_ERR_TEMP_TOO_SMALL beyond that. Nothing is allocated or freed, by this library or by any
+ * pairs and returns FGS_ERR_TEMP_TOO_SMALL beyond that (FGS_ERR_BAD_ARG for a negative count). Nothing is allocated or freed, by this library or by any
  * library it calls. The first call on each device looks up the array's device address (with that device
  * current); make that first call outside any stream capture. All calls on a device share the one array and
  * it keeps what the previous call left (the entry point clears the parts that must start at zero), so two
  * calls that overlap on the GPU -- different streams, or different host threads -- race: keep them ordered.
+ * (The address look-up itself is behind a lock; it is the array's CONTENTS that concurrent calls would share.)
  * Inputs, outputs and result are those of fgs_sort_pairs.
  */
 int fgs_sort_static_max_pairs(void);
@@ -153,8 +169,8 @@ int fgs_sort_pairs_static(int num_rendered, int width, int height, int block_x, 
 
 /*
  * fgs_sort_pairs with CUDA events recorded around each of its kernel launches; waits for the stream and
- * fills launch_ms[i] and launch_kind[i] for every launch i (kinds: 0 histogram, 1 digit pass, 2 tile
- * segments, 3 in-block tile sort); *num_launches receives the count (0 when num_rendered is 0). Both arrays
+ * fills launch_ms[i] and launch_kind[i] for every launch i (kinds: 0 histogram, 1 tile-grouping or digit pass,
+ * 2 tile segments, 3 in-block tile sort); *num_launches receives the count (0 when num_rendered is 0). Both arrays
  * must hold `capacity` >= 24 entries. A measurement aid for benchmarks: it creates and destroys events
  * and blocks the host, so it is not for the frame loop. No counterpart in the reference.
  */

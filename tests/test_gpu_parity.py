@@ -277,16 +277,31 @@ def test_pair_overflow_is_reported_not_written(ops, oracle_lib):
         ops.sort_gaussian(R, cam.width, cam.height, 16, 16, z(1 << 20, torch.int8), ku[:cap], vu[:cap], ku[:cap].clone(), vu[:cap].clone())
 
 
-def _sort_case(ops, oracle_lib, keys, vals, width, height):
+def _sort_case(ops, oracle_lib, keys, vals, width, height, junk=False):
+    """Both sort entry points against the oracle's stable sort. ``stable=True``: the same bytes. Default: the same
+    keys and the same multiset of pairs, and every run of identical keys in ascending order of its values (with
+    ``junk`` -- bits above the sorted width in the keys -- only the order on the sorted bits is defined)."""
     n = keys.size
     ki, vi = _t(keys.view(np.int64)), _t(vals.view(np.int32))
-    ko, vo = torch.zeros_like(ki), torch.zeros_like(vi)
     tmp = torch.zeros(ops.get_sort_buffer_size(n), device=DEV, dtype=torch.int8)
-    ops.sort_gaussian(n, width, height, 16, 16, tmp, ki, vi, ko, vo)
-    torch.cuda.synchronize()
     ek, ev = oracle_lib.sort_pairs(keys, vals, width, height)
-    assert (ko.cpu().numpy().view(np.uint64) == ek).all()
-    assert (vo.cpu().numpy().view(np.uint32) == ev).all()      # stable: values follow exactly
+    mask = np.uint64((1 << scenes.sort_end_bit(width, height)) - 1)
+    for stable in (True, False):
+        ko, vo = torch.zeros_like(ki), torch.zeros_like(vi)
+        ops.sort_gaussian(n, width, height, 16, 16, tmp, ki, vi, ko, vo, stable=stable)
+        torch.cuda.synchronize()
+        k, v = ko.cpu().numpy().view(np.uint64), vo.cpu().numpy().view(np.uint32)
+        if stable:
+            assert (k == ek).all()
+            assert (v == ev).all()      # stable: values follow exactly
+            continue
+        assert ((k & mask) == (ek & mask)).all()
+        o1, o2 = np.lexsort((v, k)), np.lexsort((ev, ek))
+        assert (k[o1] == ek[o2]).all() and (v[o1] == ev[o2]).all()      # the same pairs
+        if not junk:
+            assert (k == ek).all()
+            same = k[1:] == k[:-1]
+            assert (v[1:][same] >= v[:-1][same]).all()                  # ties in ascending order of value
     assert (ki.cpu().numpy().view(np.uint64) == keys).all()    # inputs preserved
     assert (vi.cpu().numpy().view(np.uint32) == vals).all()
 
@@ -326,7 +341,11 @@ def test_sort_adversarial(ops, oracle_lib):
     _sort_case(ops, oracle_lib, base & np.uint64(0xFFFFFFFF0000FF00), vals, W, H)             # many duplicates
     # bits at and above the sorted width are carried along but never compared (sort.cu:39)
     junk = base | (rng.integers(0, 1 << 19, n, dtype=np.uint64) << np.uint64(44))
-    _sort_case(ops, oracle_lib, junk, vals, W, H)
+    _sort_case(ops, oracle_lib, junk, vals, W, H, junk=True)
+    # values in no particular order: ties of the default sort still come out by value
+    _sort_case(ops, oracle_lib, base & np.uint64(0xFFFFFFFF0000FF00), rng.permutation(n).astype(np.uint32), W, H)
+    # the same pair twice
+    _sort_case(ops, oracle_lib, np.repeat(base[: n // 2], 2), np.repeat(vals[: n // 2], 2), W, H)
     # tiny image: 1 tile -> 33 live bits, the last digit is a single bit
     _sort_case(ops, oracle_lib, (rng.integers(0, 2, n, dtype=np.uint64) << np.uint64(32)) | (base & np.uint64(0xFFFFFFFF)), vals, 16, 16)
 
@@ -387,7 +406,8 @@ def test_long_tile_lists_among_short_ones(ops, oracle_lib):
     vals = np.arange(n, dtype=np.uint32)
     _sort_case(ops, oracle_lib, keys, vals, W, H)
     junk = keys | (rng.integers(0, 1 << 19, n, dtype=np.uint64) << np.uint64(44))
-    _sort_case(ops, oracle_lib, junk, vals, W, H)
+    _sort_case(ops, oracle_lib, junk, vals, W, H, junk=True)
+    _sort_case(ops, oracle_lib, keys, rng.permutation(n).astype(np.uint32), W, H)
     assert ops.device_status() == 0
 
 
@@ -421,12 +441,12 @@ def test_bounded_lookback_wait_reports_timeout(ops):
     assert ops.device_status() == 0
     L.fgs_debug_sort_skip_publish(3)
     try:
-        ops.sort_gaussian(n, 800, 800, 16, 16, tmp, ki, vi, ko, vo)
+        ops.sort_gaussian(n, 800, 800, 16, 16, tmp, ki, vi, ko, vo, stable=True)   # the look-back lives in the stable path
         torch.cuda.synchronize()
     finally:
         L.fgs_debug_sort_skip_publish(-1)
     assert ops.device_status() & _lib.ERR_LOOKBACK_TIMEOUT
-    ops.sort_gaussian(n, 800, 800, 16, 16, tmp, ki, vi, ko, vo)          # works again
+    ops.sort_gaussian(n, 800, 800, 16, 16, tmp, ki, vi, ko, vo, stable=True)          # works again
     torch.cuda.synchronize()
     assert ops.device_status() == 0
     assert (torch.sort(ki, stable=True)[0] == ko).all()
