@@ -30,6 +30,8 @@ SIGNATURES = {
                                   _p, _p, _p, _p, _p, _i64, _p, _p]),
     "fgs_preprocess_strip_culled": (_i, [_i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _f, _f, _f, _f, _i, _i,
                                          _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p]),
+    "fgs_preprocess_profile": (_i, [_i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _f, _f, _f, _f, _i, _i,
+                                    _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p, _p]),
     "fgs_sort_temp_bytes": (C.c_size_t, [_i64]),
     "fgs_sort_pairs": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p]),
     "fgs_sort_pairs_stable": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p]),
@@ -46,6 +48,8 @@ SIGNATURES = {
     "fgs_ply_vertex_count": (C.c_longlong, [C.c_char_p]),
     "fgs_ply_load": (_i, [C.c_char_p, C.c_longlong, _p, _p, _p, _p]),
 }
+
+TEST_HOOKS = ("fgs_debug_preprocess_no_column_cull", "fgs_debug_sort_plain", "fgs_debug_sort_skip_publish")
 
 _lib = None
 
@@ -71,12 +75,10 @@ def load():
             fn = getattr(lib, name)
             fn.restype = res
             fn.argtypes = args
-        lib.fgs_debug_sort_skip_publish.restype = None
-        lib.fgs_debug_sort_skip_publish.argtypes = [_i]
-        lib.fgs_debug_sort_plain.restype = None
-        lib.fgs_debug_sort_plain.argtypes = [_i]
-        lib.fgs_debug_preprocess_no_column_cull.restype = None
-        lib.fgs_debug_preprocess_no_column_cull.argtypes = [_i]
+        for name in TEST_HOOKS:   # include/flashgs_b200_test.h: switches for the test-suite, not part of the operator ABI
+            fn = getattr(lib, name)
+            fn.restype = None
+            fn.argtypes = [_i]
         _lib = lib
     return _lib
 

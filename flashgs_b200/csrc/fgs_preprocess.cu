@@ -640,18 +640,20 @@ extern "C" int fgs_debug_pre_phase_cycles(unsigned long long* out8, int reset)
 // range. Both settings must produce the same pair set; the tests compare them.
 extern "C" void fgs_debug_preprocess_no_column_cull(int on) { fgs::g_debug_no_column_cull = on; }
 
-extern "C" int fgs_preprocess_strip_culled(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
-                                           int width, int height, int block_x, int block_y,
-                                           const float* cam_position, const float* cam_rotation,
-                                           float focal_x, float focal_y, float zFar, float zNear,
-                                           int tile_row_begin, int tile_row_end,
-                                           float* points_xy, float* rgb_depth, float* conic_opacity,
-                                           uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
-                                           int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream)
+namespace fgs {
+// `events`, when given, holds three events: recorded before the index-list kernel, between the two kernels and after
+// the main kernel (the measurement entry point below).
+static int preprocess_impl(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                           int width, int height, int block_x, int block_y,
+                           const float* cam_position, const float* cam_rotation,
+                           float focal_x, float focal_y, float zFar, float zNear,
+                           int tile_row_begin, int tile_row_end,
+                           float* points_xy, float* rgb_depth, float* conic_opacity,
+                           uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                           int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream, cudaEvent_t* events)
 {
-    using namespace fgs;
-    if (cull_scratch != nullptr && cull_scratch_ints < (int64_t)P + 1) return FGS_ERR_TEMP_TOO_SMALL;
     if (P < 0 || width <= 0 || height <= 0 || block_x <= 0 || block_y <= 0 || pair_capacity < 0) return FGS_ERR_BAD_ARG;
+    if (cull_scratch != nullptr && cull_scratch_ints < (int64_t)P + 1) return FGS_ERR_TEMP_TOO_SMALL;
     if (!cam_position || !cam_rotation || !curr_offset) return FGS_ERR_BAD_ARG;
     if (P == 0) return FGS_OK;
     if (!positions || !shs || !opacities || !cov3ds || !points_xy || !rgb_depth || !conic_opacity ||
@@ -677,14 +679,16 @@ extern "C" int fgs_preprocess_strip_culled(int P, const float* positions, const 
     const int groups = (P + PRE_THREADS - 1) / PRE_THREADS;
     const int blocks = groups;   // one block per 256 Gaussians (with a list: blocks past its end return at once)
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // A strip with scratch for the index list: first the cheap pass that lists the Gaussians reaching the strip.
-    const bool strip = cam.row_begin > 0 || cam.row_end < cam.grid_y;
+    // With scratch for the index list: first the cheap pass that lists the Gaussians reaching the rendered rows and
+    // the image's columns (for a whole frame too: about a third of the scene lies outside the image).
     const int* list = nullptr;
+    if (events) cudaEventRecord(events[0], st);
     if (cull_scratch != nullptr) {
         if (cudaMemsetAsync(cull_scratch, 0, sizeof(int), st) != cudaSuccess) return FGS_ERR_CUDA;
         strip_cull_kernel<<<groups, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, cam, cull_scratch);
         list = cull_scratch;
     }
+    if (events) cudaEventRecord(events[1], st);
     if (vec)
         preprocess_kernel<true><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,
             reinterpret_cast<float2*>(points_xy), reinterpret_cast<float4*>(rgb_depth), reinterpret_cast<float4*>(conic_opacity),
@@ -693,7 +697,51 @@ extern "C" int fgs_preprocess_strip_culled(int P, const float* positions, const 
         preprocess_kernel<false><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,
             reinterpret_cast<float2*>(points_xy), reinterpret_cast<float4*>(rgb_depth), reinterpret_cast<float4*>(conic_opacity),
             keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status, list);
+    if (events) cudaEventRecord(events[2], st);
     return launch_status();
+}
+} // namespace fgs
+
+extern "C" int fgs_preprocess_strip_culled(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                                           int width, int height, int block_x, int block_y,
+                                           const float* cam_position, const float* cam_rotation,
+                                           float focal_x, float focal_y, float zFar, float zNear,
+                                           int tile_row_begin, int tile_row_end,
+                                           float* points_xy, float* rgb_depth, float* conic_opacity,
+                                           uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                                           int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream)
+{
+    return fgs::preprocess_impl(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y, cam_position, cam_rotation,
+                                focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end, points_xy, rgb_depth, conic_opacity,
+                                keys_unsorted, values_unsorted, pair_capacity, curr_offset, cull_scratch, cull_scratch_ints, stream, nullptr);
+}
+
+extern "C" int fgs_preprocess_profile(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                                      int width, int height, int block_x, int block_y,
+                                      const float* cam_position, const float* cam_rotation,
+                                      float focal_x, float focal_y, float zFar, float zNear,
+                                      int tile_row_begin, int tile_row_end,
+                                      float* points_xy, float* rgb_depth, float* conic_opacity,
+                                      uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                                      int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream,
+                                      float* kernel_ms2)
+{
+    if (!kernel_ms2) return FGS_ERR_BAD_ARG;
+    cudaEvent_t ev[3];
+    for (auto& e : ev)
+        if (cudaEventCreate(&e) != cudaSuccess) return FGS_ERR_CUDA;
+    int st = fgs::preprocess_impl(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y, cam_position, cam_rotation,
+                                  focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end, points_xy, rgb_depth, conic_opacity,
+                                  keys_unsorted, values_unsorted, pair_capacity, curr_offset, cull_scratch, cull_scratch_ints, stream, ev);
+    kernel_ms2[0] = kernel_ms2[1] = 0.0f;
+    if (st == FGS_OK && P > 0) {
+        if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) st = FGS_ERR_CUDA;
+        if (st == FGS_OK && (cudaEventElapsedTime(&kernel_ms2[0], ev[0], ev[1]) != cudaSuccess ||
+                             cudaEventElapsedTime(&kernel_ms2[1], ev[1], ev[2]) != cudaSuccess))
+            st = FGS_ERR_CUDA;
+    }
+    for (auto& e : ev) cudaEventDestroy(e);
+    return st;
 }
 
 extern "C" int fgs_preprocess_strip(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,

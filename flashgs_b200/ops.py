@@ -132,6 +132,31 @@ def sort_gaussian(num_rendered, width, height, block_x, block_y, list_sorting_sp
     _lib.check("sort_gaussian", st)
 
 
+def _check_frame_buffers(block_x, block_y, width, height, ranges, out_color, num_rendered=None, records=(), lists=()):
+    """Size checks shared by the render entry points: a short caller buffer must raise here, not become an
+    out-of-bounds store on the device."""
+    tiles = ((int(width) + block_x - 1) // block_x) * ((int(height) + block_y - 1) // block_y)
+    if ranges.numel() < 2 * tiles:
+        raise RuntimeError("ranges holds %d tiles, the image has %d" % (ranges.numel() // 2, tiles))
+    if out_color is not None:
+        if not out_color.is_cuda or not out_color.is_contiguous() or out_color.element_size() != 1:
+            raise RuntimeError("out_color must be a contiguous CUDA int8/uint8 tensor")
+        if out_color.numel() < int(width) * int(height) * 3:
+            raise RuntimeError("out_color is smaller than height*width*3")
+    if num_rendered is not None:
+        for t, nm in lists:
+            if t.numel() < int(num_rendered):
+                raise RuntimeError("%s holds %d pairs, num_rendered is %d" % (nm, t.numel(), int(num_rendered)))
+    rows = None
+    for t, nm, per in records:
+        if t.numel() % per:
+            raise RuntimeError("%s must have %d floats per Gaussian" % (nm, per))
+        rows = t.numel() // per if rows is None else rows
+        if t.numel() // per != rows:
+            raise RuntimeError("points_xy, rgb_depth and conic_opacity must describe the same number of Gaussians")
+    return tiles
+
+
 def _render(fn_name, block_x, block_y, num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
             gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color):
     f32 = torch.float32
@@ -142,13 +167,11 @@ def _render(fn_name, block_x, block_y, num_rendered, width, height, points_xy, r
     vs = _in(gaussian_values_sorted, "gaussian_values_sorted", torch.int32)
     rg = _out(ranges, "ranges", torch.int32)
     bg = _host(bg_color, "bg_color", 3)
-    if not out_color.is_cuda or not out_color.is_contiguous() or out_color.element_size() != 1:
-        raise RuntimeError("out_color must be a contiguous CUDA int8/uint8 tensor")
-    tiles = ((int(width) + block_x - 1) // block_x) * ((int(height) + block_y - 1) // block_y)
-    if rg.numel() < 2 * tiles:
-        raise RuntimeError("ranges holds %d tiles, the image has %d" % (rg.numel() // 2, tiles))
-    if out_color.numel() < int(width) * int(height) * 3:
-        raise RuntimeError("out_color is smaller than height*width*3")
+    if out_color is None:
+        raise RuntimeError("out_color is required")
+    _check_frame_buffers(block_x, block_y, width, height, rg, out_color, num_rendered,
+                         records=((xy, "points_xy", 2), (rd, "rgb_depth", 4), (co, "conic_opacity", 4)),
+                         lists=((ks, "gaussian_keys_sorted"), (vs, "gaussian_values_sorted")))
     st = getattr(_L, fn_name)(int(num_rendered), int(width), int(height),
                               xy.data_ptr(), rd.data_ptr(), co.data_ptr(), ks.data_ptr(), vs.data_ptr(),
                               rg.data_ptr(), bg.data_ptr(), out_color.data_ptr(), _stream())
@@ -184,16 +207,23 @@ def render_ex(block_x, block_y, num_rendered, width, height, points_xy, rgb_dept
     f32 = torch.float32
     bg = _host(bg_color, "bg_color", 3)
     ptr = lambda t: 0 if t is None else t.data_ptr()  # noqa: E731
-    for t, nm, dt in ((out_rgb, "out_rgb", f32), (out_alpha, "out_alpha", f32), (out_depth, "out_depth", f32),
-                      (consumed, "consumed", torch.int32)):
+    xy, rd, co = _in(points_xy, "points_xy", f32), _in(rgb_depth, "rgb_depth", f32), _in(conic_opacity, "conic_opacity", f32)
+    ks = _in(gaussian_keys_sorted, "gaussian_keys_sorted", torch.int64)
+    vs = _in(gaussian_values_sorted, "gaussian_values_sorted", torch.int32)
+    rg = _out(ranges, "ranges", torch.int32)
+    tiles = _check_frame_buffers(int(block_x), int(block_y), width, height, rg, out_color, num_rendered,
+                                 records=((xy, "points_xy", 2), (rd, "rgb_depth", 4), (co, "conic_opacity", 4)),
+                                 lists=((ks, "gaussian_keys_sorted"), (vs, "gaussian_values_sorted")))
+    pixels = int(width) * int(height)
+    for t, nm, dt, need in ((out_rgb, "out_rgb", f32, 3 * pixels), (out_alpha, "out_alpha", f32, pixels),
+                            (out_depth, "out_depth", f32, pixels), (consumed, "consumed", torch.int32, tiles)):
         if t is not None:
             _out(t, nm, dt)
+            if t.numel() < need:
+                raise RuntimeError("%s needs %d elements, has %d" % (nm, need, t.numel()))
     st = _L.fgs_render_ex(int(block_x), int(block_y), int(num_rendered), int(width), int(height),
-                          _in(points_xy, "points_xy", f32).data_ptr(), _in(rgb_depth, "rgb_depth", f32).data_ptr(),
-                          _in(conic_opacity, "conic_opacity", f32).data_ptr(),
-                          _in(gaussian_keys_sorted, "gaussian_keys_sorted", torch.int64).data_ptr(),
-                          _in(gaussian_values_sorted, "gaussian_values_sorted", torch.int32).data_ptr(),
-                          _out(ranges, "ranges", torch.int32).data_ptr(), bg.data_ptr(),
+                          xy.data_ptr(), rd.data_ptr(), co.data_ptr(), ks.data_ptr(), vs.data_ptr(),
+                          rg.data_ptr(), bg.data_ptr(),
                           int(tile_row_begin), int(tile_row_end),
                           ptr(out_color), ptr(out_rgb), ptr(out_alpha), ptr(out_depth), ptr(consumed), _stream())
     _lib.check("render_ex", st)
@@ -220,20 +250,23 @@ def render_frame(orig_points, shs, opacities, cov3Ds, width, height, block_x, bl
     tmp = list_sorting_space
     if not tmp.is_cuda or not tmp.is_contiguous():
         raise RuntimeError("list_sorting_space must be a contiguous CUDA tensor")
-    if not out_color.is_cuda or not out_color.is_contiguous() or out_color.element_size() != 1:
-        raise RuntimeError("out_color must be a contiguous CUDA int8/uint8 tensor")
-    if out_color.numel() < int(width) * int(height) * 3:
-        raise RuntimeError("out_color is smaller than height*width*3")
+    if out_color is None:
+        raise RuntimeError("out_color is required")
     op = _in(opacities, "opacities", f32)
-    st = _L.fgs_render_frame(int(op.size(0)), _in(orig_points, "orig_points", f32).data_ptr(), _in(shs, "shs", f32).data_ptr(),
+    P = int(op.size(0))
+    xy, rd, co = _out(points_xy, "points_xy", f32), _out(rgb_depth, "rgb_depth", f32), _out(conic_opacity, "conic_opacity", f32)
+    rg = _out(ranges, "ranges", torch.int32)
+    _check_frame_buffers(int(block_x), int(block_y), width, height, rg, out_color)
+    if xy.numel() < 2 * P or rd.numel() < 4 * P or co.numel() < 4 * P:
+        raise RuntimeError("points_xy, rgb_depth and conic_opacity need one record per Gaussian (%d)" % P)
+    st = _L.fgs_render_frame(P, _in(orig_points, "orig_points", f32).data_ptr(), _in(shs, "shs", f32).data_ptr(),
                              op.data_ptr(), _in(cov3Ds, "cov3Ds", f32).data_ptr(),
                              int(width), int(height), int(block_x), int(block_y), pos.data_ptr(), rot.data_ptr(),
                              float(focal_x), float(focal_y), float(zFar), float(zNear), bg.data_ptr(),
-                             _out(points_xy, "points_xy", f32).data_ptr(), _out(rgb_depth, "rgb_depth", f32).data_ptr(),
-                             _out(conic_opacity, "conic_opacity", f32).data_ptr(),
+                             xy.data_ptr(), rd.data_ptr(), co.data_ptr(),
                              ku.data_ptr(), vu.data_ptr(), ks.data_ptr(), vs.data_ptr(), cap,
                              tmp.data_ptr(), tmp.numel() * tmp.element_size(),
-                             _out(ranges, "ranges", torch.int32).data_ptr(), _out(curr_offset, "curr_offset", torch.int32).data_ptr(),
+                             rg.data_ptr(), _out(curr_offset, "curr_offset", torch.int32).data_ptr(),
                              int(tile_row_begin), int(tile_row_end), out_color.data_ptr(), _stream())
     _lib.check("render_frame", st)
 

@@ -114,3 +114,91 @@ class PeerFrames:
 
     def barrier(self) -> None:
         self.handle.barrier(channel=0)
+
+
+class HostFrames:
+    """A ring of ``count`` host images ``[H, W, 3]`` in POSIX shared memory, mapped -- and, with ``register=True``,
+    page-locked for CUDA -- in every rank of the group on one node. Each rank copies the pixel rows of its own strip
+    into the current image with one asynchronous copy over its own PCIe link, so a whole frame reaches the host
+    through N links at once instead of being funnelled through the link of the rank that gathered it. There is no
+    collective and no peer traffic at all; the ranks meet in a few counters kept in the same shared memory:
+    ``publish(k)`` says that this rank's strip of frame ``k`` has landed, ``wait_produced(k)`` (the consumer, rank
+    ``dst``) waits for every rank's, ``consume(k)`` releases the image for reuse and ``wait_consumed(k)`` (every
+    rank, before it overwrites an image of the ring) waits for that release. Every wait is bounded: it raises
+    ``TimeoutError`` after ``timeout_s`` seconds, so a rank that died or never joined ends the others with an error
+    instead of leaving them spinning.
+
+    The reference renders on one GPU and copies the image with ``image.cpu()`` (example.py:98); this is the form that
+    copy takes when one frame is rendered as strips on several GPUs.
+    """
+
+    def __init__(self, count: int, height: int, width: int, group=None, dst: int = 0, register: bool = True,
+                 timeout_s: float = 20.0):
+        import time
+        from multiprocessing import shared_memory
+
+        import numpy as np
+        self._time = time
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.dst, self.count, self.timeout_s = dst, count, timeout_s
+        image_bytes = height * width * 3
+        flag_bytes = 8 * (self.world + 1)
+        total = count * image_bytes + 4096 + flag_bytes
+        names = [None]
+        if self.rank == dst:
+            self.shm = shared_memory.SharedMemory(create=True, size=total)
+            names[0] = self.shm.name
+        if self.world > 1:
+            dist.broadcast_object_list(names, src=dst, group=group)
+        if self.rank != dst:
+            self.shm = shared_memory.SharedMemory(name=names[0])
+        buf = np.ndarray((total,), dtype=np.uint8, buffer=self.shm.buf)
+        self._np = buf
+        self.images = [torch.from_numpy(buf[i * image_bytes:(i + 1) * image_bytes].reshape(height, width, 3)).view(torch.int8)
+                       for i in range(count)]
+        off = (count * image_bytes + 4095) // 4096 * 4096
+        self.flags = np.ndarray((self.world + 1,), dtype=np.int64, buffer=self.shm.buf, offset=off)
+        if self.rank == dst:
+            self.flags[:] = -1
+        self.registered = False
+        if register and torch.cuda.is_available():
+            rc = torch.cuda.cudart().cudaHostRegister(buf.ctypes.data, count * image_bytes, 0)
+            self.registered = int(rc) == 0
+        if self.world > 1:
+            dist.barrier(group=group)   # the flags are initialised before anybody polls them
+
+    def _spin(self, ready, what: str) -> None:
+        t0 = self._time.perf_counter()
+        while not ready():
+            if self._time.perf_counter() - t0 > self.timeout_s:
+                raise TimeoutError("HostFrames: %s not reached within %.1f s (flags %s)" % (what, self.timeout_s, self.flags.tolist()))
+
+    def publish(self, frame: int) -> None:
+        """This rank's strip of ``frame`` is complete in host memory (call it after the copy's event has completed)."""
+        self.flags[self.rank] = frame
+
+    def wait_produced(self, frame: int) -> None:
+        self._spin(lambda: bool((self.flags[: self.world] >= frame).all()), "frame %d from every rank" % frame)
+
+    def consume(self, frame: int) -> None:
+        self.flags[self.world] = frame
+
+    def wait_consumed(self, frame: int) -> None:
+        if frame >= 0:
+            self._spin(lambda: int(self.flags[self.world]) >= frame, "release of frame %d" % frame)
+
+    def close(self) -> None:
+        if self.registered:
+            torch.cuda.cudart().cudaHostUnregister(self._np.ctypes.data)
+            self.registered = False
+        self.images, self.flags, self._np = [], None, None
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        try:
+            self.shm.close()
+            if self.rank == self.dst:
+                self.shm.unlink()
+        except Exception:
+            pass

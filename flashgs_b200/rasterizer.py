@@ -15,8 +15,14 @@ from __future__ import annotations
 
 import torch
 
-from . import ops as _ops
-from .scenes import Camera, Scene, tile_grid
+from .scenes import Camera, Scene
+
+
+def _default_ops():
+    """This repository's operator module. Imported on first use only, so that driving ANOTHER implementation of the
+    operator API through the classes below (``ops=`` given) never loads this repository's shared library."""
+    from . import ops
+    return ops
 
 
 class DeviceScene:
@@ -44,8 +50,9 @@ class TorchCamera:
 
 
 class Rasterizer:
-    def __init__(self, scene: DeviceScene, MAX_NUM_RENDERED: int, MAX_NUM_TILES: int, ops=_ops, block=(16, 16)):
+    def __init__(self, scene: DeviceScene, MAX_NUM_RENDERED: int, MAX_NUM_TILES: int, ops=None, block=(16, 16)):
         dev = scene.device
+        ops = ops if ops is not None else _default_ops()
         self.ops = ops
         self.block = block
         z = lambda n, dt: torch.zeros(n, device=dev, dtype=dt)  # noqa: E731

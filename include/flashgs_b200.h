@@ -104,8 +104,9 @@ int fgs_preprocess_strip(int P, const float* positions, const float* shs, const 
  * entry and exit): a first, cheap kernel lists the Gaussians that pass the near and opacity culls and whose
  * vertical reach (bounded from the trace of the 3-D covariance) meets the strip; the preprocess kernel then runs on
  * that list only. A rank that renders one strip of N thus does the expensive work for about 1/N of the scene. Same
- * pair set and feature records as fgs_preprocess_strip (the pair ORDER differs; neither is defined). With a null
- * scratch, or rows covering the whole frame, it is fgs_preprocess_strip. No counterpart in the reference.
+ * pair set and feature records as fgs_preprocess_strip (the pair ORDER differs; neither is defined). The list is
+ * built for a whole frame as well (rows 0 and -1): it then drops the Gaussians left, right, above and below the
+ * image. With a null scratch the call is fgs_preprocess_strip. No counterpart in the reference.
  */
 int fgs_preprocess_strip_culled(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
                                 int width, int height, int block_x, int block_y,
@@ -115,6 +116,21 @@ int fgs_preprocess_strip_culled(int P, const float* positions, const float* shs,
                                 float* points_xy, float* rgb_depth, float* conic_opacity,
                                 uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
                                 int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream);
+
+/*
+ * fgs_preprocess_strip_culled with CUDA events around its two kernels: waits for the stream and fills
+ * kernel_ms2[0] (the index-list kernel; 0 without scratch) and kernel_ms2[1] (the main kernel). A measurement
+ * aid for benchmarks: it creates and destroys events and blocks the host. No counterpart in the reference.
+ */
+int fgs_preprocess_profile(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                           int width, int height, int block_x, int block_y,
+                           const float* cam_position, const float* cam_rotation,
+                           float focal_x, float focal_y, float zFar, float zNear,
+                           int tile_row_begin, int tile_row_end,
+                           float* points_xy, float* rgb_depth, float* conic_opacity,
+                           uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                           int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream,
+                           float* kernel_ms2);
 
 /*
  * Scratch bytes fgs_sort_pairs needs for up to `num_rendered` pairs. Replaces

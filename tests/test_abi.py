@@ -12,8 +12,8 @@ from helpers import identity_camera
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _declared_symbols():
-    text = open(os.path.join(ROOT, "include", "flashgs_b200.h")).read()
+def _declared_symbols(header="flashgs_b200.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(fgs_[a-z0-9_]+)\s*\(", text)))
 
@@ -25,7 +25,11 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), "missing export " + n
         assert n in _lib.SIGNATURES, "no ctypes prototype for " + n
-    assert lib.fgs_abi_version() == 1
+    hooks = _declared_symbols("flashgs_b200_test.h")      # the test-only switches have a header of their own
+    assert sorted(hooks) == sorted(_lib.TEST_HOOKS)
+    for n in hooks:
+        assert hasattr(lib, n), "missing export " + n
+    assert lib.fgs_abi_version() == 2
     assert _lib.status_string(0) == "ok"
     assert "overflow" in _lib.status_string(_lib.ERR_PAIR_OVERFLOW)
 
@@ -64,6 +68,10 @@ def test_argument_checks_need_no_gpu():
                               *([None] * 5), 0, None, None) == _lib.ERR_BAD_ARG
     assert lib.fgs_tile_ranges(0, 0, None, None, None) == _lib.ERR_BAD_ARG
     # scratch for the index list of the Gaussians that reach a strip must hold P + 1 ints (checked before anything runs)
+    assert lib.fgs_preprocess_strip_culled(-1, *([None] * 4), 64, 64, 16, 16, None, None, 1.0, 1.0, 100.0, 0.01, 0, 2,
+                                           *([None] * 5), 0, None, None, 0, None) == _lib.ERR_BAD_ARG   # a negative count first
+    assert lib.fgs_sort_pairs_static(-1, 64, 64, 16, 16, None, None, None, None, None) == _lib.ERR_BAD_ARG
+    assert lib.fgs_sort_pairs_stable(-1, 64, 64, 16, 16, None, 0, None, None, None, None, None) == _lib.ERR_BAD_ARG
     dummy = (C.c_int * 4)()
     assert lib.fgs_preprocess_strip_culled(10, *([None] * 4), 64, 64, 16, 16, None, None, 1.0, 1.0, 100.0, 0.01, 0, 2,
                                            *([None] * 5), 0, None, C.addressof(dummy), 4, None) == _lib.ERR_TEMP_TOO_SMALL
