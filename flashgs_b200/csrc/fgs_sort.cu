@@ -685,93 +685,121 @@ tile_hist_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict
 // (= first), the work lists of the tile sorts' length classes, and the tables of the coarse buckets (a bucket is
 // the run of 2^lo_bits consecutive tile values that share their upper bits): where each bucket starts, its cursor,
 // and the running count of the second pass's units (partitions cut inside a bucket).
+// All global accesses are coalesced (a single SM does this work: strided accesses would cost one memory
+// transaction per lane): the counts are staged in shared memory, scanned there by threads that own consecutive
+// tiles, and the results are written out by threads that own neighbouring tiles. Up to SCAN_ROUND tile values are
+// handled per round (two rounds for 65536).
+constexpr int SCAN_ROUND = 32768;
+constexpr int SCAN_SMEM_BYTES = (SCAN_ROUND + SCAN_ROUND / 32 + 2) * 4;
+__device__ __forceinline__ int scan_pad(int i) { return i + (i >> 5); }   // consecutive chunks of 32 words start in different banks
+
 __global__ void __launch_bounds__(TILE_SCAN_THREADS, 1)
 tile_scan_kernel(const uint32_t* __restrict__ tile_count, int tile_values, int lo_bits,
                  int2* __restrict__ seg, uint32_t* __restrict__ cursor, uint32_t* __restrict__ bucket_tables,
                  int* __restrict__ class_count, uint32_t* __restrict__ class_tiles)
 {
     constexpr int WARPS = TILE_SCAN_THREADS / 32;
-    __shared__ uint32_t s_wsum[5][WARPS];
+    extern __shared__ __align__(16) uint32_t s_pref[];          // counts, then exclusive prefixes (padded), one round
+    __shared__ uint32_t s_wsum[WARPS];
     __shared__ uint32_t s_bucket_first[MAX_BUCKETS + 1];
     __shared__ uint32_t s_units[MAX_BUCKETS];
+    __shared__ uint32_t s_usum[MAX_BUCKETS / 32];
+    __shared__ uint32_t s_class[LOCAL_CLASSES];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int per = (tile_values + TILE_SCAN_THREADS - 1) / TILE_SCAN_THREADS;   // tile values per thread, consecutive
-    const int t0 = tid * per, t1 = min(tile_values, t0 + per);
-    auto length_class = [](uint32_t len) { return len <= 1024u ? 0 : (len <= 2048u ? 1 : (len <= (uint32_t)LOCAL_CAP ? 2 : 3)); };
-    // pass A: this thread's totals -- pairs, and non-empty tiles per length class
-    uint32_t v[5] = { 0, 0, 0, 0, 0 };
-    for (int t = t0; t < t1; t++) {
-        const uint32_t c = tile_count[t];
-        v[0] += c;
-        const int k = c ? length_class(c) : -1;
-#pragma unroll
-        for (int q = 0; q < LOCAL_CLASSES; q++) v[1 + q] += (k == q) ? 1u : 0u;
-    }
-    uint32_t inc[5];
-#pragma unroll
-    for (int q = 0; q < 5; q++) {
-        inc[q] = v[q];
+    const unsigned lt = lanemask_lt();
+    const uint32_t lo_mask = (1u << lo_bits) - 1u;
+    const int buckets = max(1, tile_values >> lo_bits);
+    if (tid < LOCAL_CLASSES) s_class[tid] = 0;
+    uint32_t carry = 0;   // pairs of the tiles of earlier rounds
+    for (int lo = 0; lo < tile_values; lo += SCAN_ROUND) {
+        const int n = min(SCAN_ROUND, tile_values - lo);
+        __syncthreads();   // the previous round's shared memory is no longer read
+        for (int i = tid; i < n; i += TILE_SCAN_THREADS) s_pref[scan_pad(i)] = tile_count[lo + i];
+        __syncthreads();
+        // exclusive scan: a thread owns `per` consecutive tiles
+        const int per = (n + TILE_SCAN_THREADS - 1) / TILE_SCAN_THREADS;
+        const int t0 = min(n, tid * per), t1 = min(n, t0 + per);
+        uint32_t sum = 0;
+        for (int t = t0; t < t1; t++) sum += s_pref[scan_pad(t)];
+        uint32_t inc = sum;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t a = __shfl_up_sync(FULL_MASK, inc[q], o);
-            if (lane >= o) inc[q] += a;
+            const uint32_t a = __shfl_up_sync(FULL_MASK, inc, o);
+            if (lane >= o) inc += a;
         }
-        if (lane == 31) s_wsum[q][warp] = inc[q];
+        if (lane == 31) s_wsum[warp] = inc;
+        __syncthreads();
+        uint32_t run = carry + inc - sum, total = 0;
+        for (int w = 0; w < WARPS; w++) { const uint32_t s = s_wsum[w]; if (w < warp) run += s; total += s; }
+        for (int t = t0; t < t1; t++) {
+            const uint32_t c = s_pref[scan_pad(t)];
+            s_pref[scan_pad(t)] = run;
+            run += c;
+        }
+        if (tid == 0) s_pref[scan_pad(n)] = carry + total;
+        __syncthreads();
+        // outputs, neighbouring threads for neighbouring tiles
+        for (int b = 0; b < n; b += TILE_SCAN_THREADS) {
+            const int i = b + tid;
+            const bool ok = i < n;
+            const uint32_t first = ok ? s_pref[scan_pad(i)] : 0u;
+            const uint32_t c = ok ? s_pref[scan_pad(i + 1)] - first : 0u;
+            const int t = lo + i;
+            if (ok) {
+                seg[t] = make_int2((int)first, (int)(first + c));
+                cursor[t] = first;
+                if (((uint32_t)t & lo_mask) == 0) s_bucket_first[t >> lo_bits] = first;
+            }
+            const int k = c == 0 ? -1 : (c <= 1024u ? 0 : (c <= 2048u ? 1 : (c <= (uint32_t)LOCAL_CAP ? 2 : 3)));
+#pragma unroll
+            for (int q = 0; q < LOCAL_CLASSES; q++) {   // the warp reserves its places in class q's work list with one add
+                const unsigned in_class = __ballot_sync(FULL_MASK, k == q);
+                if (in_class) {
+                    uint32_t at = 0;
+                    if (lane == 0) at = atomicAdd(&s_class[q], (uint32_t)__popc(in_class));
+                    at = __shfl_sync(FULL_MASK, at, 0);
+                    if (k == q) class_tiles[(size_t)q * MAX_TILE_VALUES + at + __popc(in_class & lt)] = (uint32_t)t;
+                }
+            }
+        }
+        carry += total;
     }
     __syncthreads();
-    uint32_t run[5];
-#pragma unroll
-    for (int q = 0; q < 5; q++) {
-        uint32_t off = 0;
-        for (int w = 0; w < warp; w++) off += s_wsum[q][w];
-        run[q] = off + inc[q] - v[q];   // exclusive prefix of this thread's chunk
-    }
-    // pass B: per tile
-    const int buckets = max(1, tile_values >> lo_bits);
-    const uint32_t lo_mask = (1u << lo_bits) - 1u;
-    for (int t = t0; t < t1; t++) {
-        const uint32_t c = tile_count[t];
-        seg[t] = make_int2((int)run[0], (int)(run[0] + c));
-        cursor[t] = run[0];
-        if (((uint32_t)t & lo_mask) == 0) s_bucket_first[t >> lo_bits] = run[0];
-        if (c) {
-            const int k = length_class(c);
-            uint32_t place = 0;
-#pragma unroll
-            for (int q = 0; q < LOCAL_CLASSES; q++)
-                if (k == q) place = run[1 + q]++;
-            class_tiles[(size_t)k * MAX_TILE_VALUES + place] = (uint32_t)t;
-        }
-        run[0] += c;
-    }
-    if (tid == TILE_SCAN_THREADS - 1) {
-        uint32_t total = 0;
-        for (int w = 0; w < WARPS; w++) total += s_wsum[0][w];
-        s_bucket_first[buckets] = total;
-#pragma unroll
-        for (int k = 0; k < LOCAL_CLASSES; k++) {
-            uint32_t cnt = 0;
-            for (int w = 0; w < WARPS; w++) cnt += s_wsum[1 + k][w];
-            class_count[k] = (int)cnt;
-        }
-    }
+    if (tid < LOCAL_CLASSES) class_count[tid] = (int)s_class[tid];
+    if (tid == 0) s_bucket_first[buckets] = carry;
     __syncthreads();
     // bucket tables: [0, B) cursors, [B, 2B+1) firsts, [2B+1, 3B+2) exclusive unit counts (+ their total)
     uint32_t* hi_cursor = bucket_tables;
     uint32_t* bucket_first = bucket_tables + MAX_BUCKETS;
     uint32_t* unit_prefix = bucket_first + MAX_BUCKETS + 1;
-    if (tid < buckets) {
-        const uint32_t first = s_bucket_first[tid], size = s_bucket_first[tid + 1] - first;
-        hi_cursor[tid] = first;
-        bucket_first[tid] = first;
-        s_units[tid] = (size + MS_PART - 1) / MS_PART;
+    if (tid < MAX_BUCKETS) {
+        uint32_t units = 0;
+        if (tid < buckets) {
+            const uint32_t first = s_bucket_first[tid], size = s_bucket_first[tid + 1] - first;
+            hi_cursor[tid] = first;
+            bucket_first[tid] = first;
+            units = (size + MS_PART - 1) / MS_PART;
+        }
+        uint32_t uinc = units;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t a = __shfl_up_sync(FULL_MASK, uinc, o);
+            if (lane >= o) uinc += a;
+        }
+        if (lane == 31) s_usum[warp] = uinc;
+        s_units[tid] = uinc - units;   // exclusive inside the warp
     }
     if (tid == 0) bucket_first[buckets] = s_bucket_first[buckets];
     __syncthreads();
-    if (tid == 0) {
-        uint32_t acc = 0;
-        for (int h = 0; h < buckets; h++) { unit_prefix[h] = acc; acc += s_units[h]; }
-        unit_prefix[buckets] = acc;
+    if (tid < MAX_BUCKETS) {
+        uint32_t off = 0;
+        for (int w = 0; w < warp; w++) off += s_usum[w];
+        if (tid < buckets) unit_prefix[tid] = off + s_units[tid];
+        if (tid == MAX_BUCKETS - 1) {
+            uint32_t all = 0;
+            for (int w = 0; w < MAX_BUCKETS / 32; w++) all += s_usum[w];
+            unit_prefix[buckets] = all;
+        }
     }
 }
 
@@ -1428,6 +1456,7 @@ static int sort_device(int* dev_out, int* sm_count_out)
         opt_in((const void*)multisplit_kernel<false>, MS_SMEM_BYTES);
         opt_in((const void*)multisplit_kernel<true>, MS_SMEM_BYTES);
         opt_in((const void*)tile_hist_kernel, TILE_HIST_SMEM_VALUES * 4);
+        opt_in((const void*)tile_scan_kernel, SCAN_SMEM_BYTES);
         if (e != cudaSuccess) return FGS_ERR_CUDA;
         d.ready = true;
     }
@@ -1542,7 +1571,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         // lower and upper halves of the tile bits: at most 8 bits each
         const int lo_bits = tile_bits <= RADIX_BITS ? tile_bits : tile_bits / 2;
         const int buckets = tile_values >> lo_bits;
-        tile_scan_kernel<<<1, TILE_SCAN_THREADS, 0, st>>>(tile_count, tile_values, lo_bits, seg, tile_cursor, bucket_tables,
+        tile_scan_kernel<<<1, TILE_SCAN_THREADS, SCAN_SMEM_BYTES, st>>>(tile_count, tile_values, lo_bits, seg, tile_cursor, bucket_tables,
                                                           class_count, class_tiles);
         mark(LAUNCH_SEGMENTS);
         const int ms_parts = (int)(((int64_t)n + MS_PART - 1) / MS_PART);
