@@ -226,6 +226,9 @@ def main():
                     help="only the view batch: all views of the workload (C5: 64), dealt out to the ranks")
     ap.add_argument("--view-passes", type=int, default=2)
     ap.add_argument("--view-gaussians", type=int, default=None, help="override the view batch's Gaussian count")
+    ap.add_argument("--no-scene-bounds", action="store_true",
+                    help="the index list of the Gaussians that reach the image is found from the scene arrays (40 bytes per "
+                         "Gaussian) instead of from records prepared once per scene (16 bytes)")
     ap.add_argument("--no-cull-scratch", action="store_true",
                     help="call preprocess with the reference's positional arguments only (no scratch for its index list)")
     args = ap.parse_args()
@@ -304,11 +307,16 @@ def main():
     cap = 1 << 26 if scene.num_vertex > 2_000_000 else 1 << 24
     ras = Rasterizer(ds, cap, 1 << 20, ops=ops)
     if args.no_cull_scratch:
-        ras.cull_scratch = None
+        ras.cull_scratch = ras.scene_bounds = None
+    if args.no_scene_bounds:
+        ras.scene_bounds = None
     use_scratch = ours and ras.cull_scratch is not None
+    use_bounds = use_scratch and ras.scene_bounds is not None
     config["preprocess_call"] = ("the reference's positional arguments plus cull_scratch= (the idle head of the sort's "
-                                 "scratch, for the index list of the Gaussians that reach the image); "
-                                 "stages.preprocess_plain_call_ms is the call without it") if use_scratch else \
+                                 "scratch, for the index list of the Gaussians that reach the image)"
+                                 + (" and scene_bounds= (16-byte records prepared once per scene, outside the timed region, "
+                                    "from which that list is found)" if use_bounds else "")
+                                 + "; stages.preprocess.preprocess_plain_call_ms is the call without them") if use_scratch else \
         "the reference's positional arguments only"
     H, W = cam.height, cam.width
     PAD = 32   # spare rows: the reference writes past ragged images
@@ -320,6 +328,8 @@ def main():
         extra = {} if rows is None else dict(tile_row_begin=rows[0], tile_row_end=rows[1])
         if use_scratch and scratch:
             extra["cull_scratch"] = ras.cull_scratch   # the head of the sort's scratch, idle at this point
+            if use_bounds:
+                extra["scene_bounds"] = ras.scene_bounds
         ops.preprocess(ds.position, ds.shs, ds.opacity, ds.cov3d, W, H, 16, 16, tc.position, tc.rotation,
                        tc.focal_x, tc.focal_y, tc.zFar, tc.zNear, ras.points_xy, ras.rgb_depth, ras.conic_opacity,
                        ras.gaussian_keys_unsorted, ras.gaussian_values_unsorted, ras.curr_offset, **extra)
@@ -535,7 +545,8 @@ def main():
                                           ras.gaussian_keys_unsorted.data_ptr(), ras.gaussian_values_unsorted.data_ptr(), cap,
                                           ras.curr_offset.data_ptr(),
                                           ras.cull_scratch.data_ptr() if use_scratch else None,
-                                          ras.cull_scratch.numel() if use_scratch else 0, stream, ms2)
+                                          ras.cull_scratch.numel() if use_scratch else 0,
+                                          ras.scene_bounds.data_ptr() if use_bounds else None, stream, ms2)
             _lib.check("fgs_preprocess_profile", st)
             pre_k.append([ms2[0], ms2[1]])
         cull_ms, main_ms = [float(x) for x in np.median(np.array(pre_k), axis=0)]
@@ -587,7 +598,7 @@ def main():
             kernels.append(k)
             return k
 
-        bytes_cull = 12 * P + 4 * P1 + 24 * P2 + 4 * listed
+        bytes_cull = (16 * P if use_bounds else 12 * P + 4 * P1 + 24 * P2) + 4 * listed
         bytes_main = (4 + 40) * listed + 192 * V + 40 * V + 12 * R if use_scratch else 12 * P + 4 * P1 + 24 * P2 + 232 * V + 12 * R
         if use_scratch:
             hbm("strip_cull_kernel", cull_ms, 1, bytes_cull)

@@ -30,8 +30,11 @@ SIGNATURES = {
                                   _p, _p, _p, _p, _p, _i64, _p, _p]),
     "fgs_preprocess_strip_culled": (_i, [_i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _f, _f, _f, _f, _i, _i,
                                          _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p]),
+    "fgs_scene_bounds": (_i, [_i, _p, _p, _p, _p, _p]),
+    "fgs_preprocess_prepared": (_i, [_i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _f, _f, _f, _f, _i, _i,
+                                     _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p, _p]),
     "fgs_preprocess_profile": (_i, [_i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _f, _f, _f, _f, _i, _i,
-                                    _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p, _p]),
+                                    _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p, _p, _p]),
     "fgs_sort_temp_bytes": (C.c_size_t, [_i64]),
     "fgs_sort_pairs": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p]),
     "fgs_sort_pairs_stable": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p]),
@@ -50,6 +53,9 @@ SIGNATURES = {
 }
 
 TEST_HOOKS = ("fgs_debug_preprocess_no_column_cull", "fgs_debug_sort_plain", "fgs_debug_sort_skip_publish")
+CHECKED_HOOKS = ("fgs_debug_bounds_report", "fgs_debug_bounds_selftest")   # exported by the checked flavour only
+LIB_CHECKED_PATH = os.path.join(HERE, "libflashgs_b200_checked.so")
+ERR_BOUNDS = 32
 
 _lib = None
 
@@ -79,6 +85,11 @@ def load():
             fn = getattr(lib, name)
             fn.restype = None
             fn.argtypes = [_i]
+        if hasattr(lib, "fgs_debug_bounds_report"):   # the checked flavour (FLASHGS_B200_LIB points at it)
+            lib.fgs_debug_bounds_report.restype = C.c_longlong
+            lib.fgs_debug_bounds_report.argtypes = [_p, _i]
+            lib.fgs_debug_bounds_selftest.restype = _i
+            lib.fgs_debug_bounds_selftest.argtypes = [_i, _i, _p, _p]
         _lib = lib
     return _lib
 

@@ -43,4 +43,39 @@ __device__ __forceinline__ unsigned lanemask_lt()
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---- checked build (-DFGS_DEBUG_BOUNDS) ----
+// Every global store, every index computed from data (a Gaussian index read from a list, a destination derived
+// from counters) and every computed shared-memory index is compared with the extent of what it addresses before the
+// access; an index outside it is counted, the first one is recorded (source line, index, extent) and the access is
+// SKIPPED -- nothing faults, nothing traps. The counters live once per source file; fgs_device_status() gathers
+// them and raises FGS_ERR_BOUNDS. In the normal build the checks compile to nothing.
+#ifdef FGS_DEBUG_BOUNDS
+static __device__ unsigned long long g_bounds_report[4];   // violations, line of the first, its index, its extent
+__device__ __forceinline__ bool index_ok(long long i, long long n, int line)
+{
+    if (i >= 0 && i < n) return true;
+    if (atomicAdd(&g_bounds_report[0], 1ull) == 0ull) {
+        g_bounds_report[1] = (unsigned long long)line;
+        g_bounds_report[2] = (unsigned long long)i;
+        g_bounds_report[3] = (unsigned long long)n;
+    }
+    return false;
+}
+#define FGS_INDEX_OK(i, n) fgs::index_ok((long long)(i), (long long)(n), __LINE__)
+// Defines the function that copies (and optionally clears) this source file's counters.
+#define FGS_BOUNDS_REPORT_FN(NAME)                                                                              \
+    extern "C" int NAME(unsigned long long* out4, int reset)                                                    \
+    {                                                                                                           \
+        if (cudaMemcpyFromSymbol(out4, fgs::g_bounds_report, 4 * sizeof(unsigned long long)) != cudaSuccess) return FGS_ERR_CUDA; \
+        if (reset) {                                                                                            \
+            const unsigned long long zero[4] = { 0, 0, 0, 0 };                                                  \
+            if (cudaMemcpyToSymbol(fgs::g_bounds_report, zero, sizeof zero) != cudaSuccess) return FGS_ERR_CUDA; \
+        }                                                                                                       \
+        return FGS_OK;                                                                                          \
+    }
+#else
+#define FGS_INDEX_OK(i, n) true
+#define FGS_BOUNDS_REPORT_FN(NAME)
+#endif
+
 } // namespace fgs

@@ -80,9 +80,30 @@ extern "C" const char* fgs_status_string(int status)
     case FGS_ERR_PAIR_OVERFLOW: return "pair buffer overflow";
     case FGS_ERR_LOOKBACK_TIMEOUT: return "device-side wait timed out";
     case FGS_ERR_TEMP_TOO_SMALL: return "sort scratch too small";
+    case FGS_ERR_BOUNDS: return "index outside its extent (checked build)";
     default: return "several errors or unknown status";
     }
 }
+
+#ifdef FGS_DEBUG_BOUNDS
+// per source file with kernels: its counters of the checked build
+extern "C" int fgs_debug_bounds_preprocess(unsigned long long* out4, int reset);
+extern "C" int fgs_debug_bounds_sort(unsigned long long* out4, int reset);
+extern "C" int fgs_debug_bounds_render(unsigned long long* out4, int reset);
+
+// Checked build: the counters of all source files as 3 x 4 values (preprocess, sort, render; each: violations, source
+// line of the first, its index, its extent). Returns the total number of violations, or a negative value on error.
+extern "C" long long fgs_debug_bounds_report(unsigned long long* out12, int reset)
+{
+    unsigned long long local[12];
+    unsigned long long* o = out12 ? out12 : local;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -FGS_ERR_CUDA;
+    if (fgs_debug_bounds_preprocess(o, reset) != FGS_OK || fgs_debug_bounds_sort(o + 4, reset) != FGS_OK ||
+        fgs_debug_bounds_render(o + 8, reset) != FGS_OK)
+        return -FGS_ERR_CUDA;
+    return (long long)(o[0] + o[4] + o[8]);
+}
+#endif
 
 extern "C" int fgs_device_status(int reset, void* stream)
 {
@@ -95,6 +116,11 @@ extern "C" int fgs_device_status(int reset, void* stream)
     if (reset && host != 0) {
         if (cudaMemsetAsync(p, 0, sizeof(int), st) != cudaSuccess) return -FGS_ERR_CUDA;
     }
+#ifdef FGS_DEBUG_BOUNDS
+    const long long violations = fgs_debug_bounds_report(nullptr, reset);
+    if (violations < 0) return -FGS_ERR_CUDA;
+    if (violations > 0) host |= FGS_ERR_BOUNDS;
+#endif
     return host;
 }
 

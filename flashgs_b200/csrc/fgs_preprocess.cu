@@ -248,12 +248,40 @@ __device__ __forceinline__ bool misses_columns(const PreCam& cam, float view_z, 
     return px + reach < 0.0f || px - reach > (float)(cam.grid_x * cam.block_x);
 }
 
+// Largest value of ln(256 * opacity) for an opacity in (0, 1]: the 1/256 iso-level of a fully opaque splat.
+constexpr float kPowerMax = 5.5451774f;
+
+// Scene preparation, once per scene: one 16-byte record per Gaussian with all the index-list kernel needs --
+// position and q = trace(Sigma) * ln(256 * opacity), the product that the reach bound of misses_strip is made of
+// (q < 0 marks an opacity below 1/255, which the opacity cull drops whatever the camera; an opacity above 1, which
+// no sigmoid produces, gives q = +inf: never dropped). The index-list kernel then streams 16 bytes per Gaussian
+// instead of 40.
+__global__ void __launch_bounds__(PRE_THREADS)
+scene_bounds_kernel(int P, const float* __restrict__ positions, const float* __restrict__ opacities,
+                    const float* __restrict__ cov3ds, float4* __restrict__ bounds)
+{
+    const int i = blockIdx.x * PRE_THREADS + threadIdx.x;
+    if (i >= P) return;
+    const float opacity = __ldg(opacities + i);
+    const float trace = __ldg(cov3ds + 6 * (size_t)i) + __ldg(cov3ds + 6 * (size_t)i + 3) + __ldg(cov3ds + 6 * (size_t)i + 5);
+    const float pw = fmaxf(kLn2 * 8.0f + kLn2 * approx_lg2(opacity), 0.0f);
+    float q = trace * pw;
+    if (255.0f * opacity < 1.0f) q = -1.0f;
+    else if (pw > kPowerMax) q = __int_as_float(0x7f800000);
+    bounds[i] = make_float4(__ldg(positions + 3 * (size_t)i), __ldg(positions + 3 * (size_t)i + 1), __ldg(positions + 3 * (size_t)i + 2), q);
+}
+
 // Strip rendering, first step: the indices of the Gaussians that pass the near and opacity culls and can reach the
 // strip, appended to list[1...] (list[0] counts them; any order). A rank that renders one strip of N then runs the
 // expensive kernel below on about 1/N of the scene instead of on all of it.
+// BOUNDS: the Gaussians come as the prepared 16-byte records (scene_bounds_kernel) instead of as position, opacity
+// and covariance rows; the reach bound is the same expression with ln(256 * opacity) replaced by its maximum in the
+// low-pass term, so it is never smaller and the list is a superset of the other variant's.
+template <bool BOUNDS>
 __global__ void __launch_bounds__(PRE_THREADS)
 strip_cull_kernel(int P, const float* __restrict__ positions, const float* __restrict__ opacities,
-                  const float* __restrict__ cov3ds, const __grid_constant__ PreCam cam, int* __restrict__ list)
+                  const float* __restrict__ cov3ds, const float4* __restrict__ bounds,
+                  const __grid_constant__ PreCam cam, int* __restrict__ list)
 {
     __shared__ int s_count[PRE_WARPS];
     __shared__ int s_base;
@@ -261,20 +289,42 @@ strip_cull_kernel(int P, const float* __restrict__ positions, const float* __res
     const int i = blockIdx.x * PRE_THREADS + tid;
     bool keep = false;
     if (i < P) {
-        const f3 p = { __ldg(positions + 3 * (size_t)i), __ldg(positions + 3 * (size_t)i + 1), __ldg(positions + 3 * (size_t)i + 2) };
-        const f3 p_view = xform4x3(p, cam.view);
-        const float opacity = __ldg(opacities + i);
-        if (!(p_view.z <= 0.2f) && !(255.0f * opacity < 1.0f)) {
-            const float* pm = cam.proj;
-            const float hy = pm[1] * p.x + pm[5] * p.y + pm[9] * p.z + pm[13];
-            const float hw = pm[3] * p.x + pm[7] * p.y + pm[11] * p.z + pm[15];
-            const float projy = hy * (1.0f / (hw + 0.0000001f));
-            float c3[6];
+        if (BOUNDS) {
+            const float4 b = __ldg(bounds + i);
+            const f3 p = { b.x, b.y, b.z };
+            const f3 p_view = xform4x3(p, cam.view);
+            if (!(p_view.z <= 0.2f) && !(b.w < 0.0f)) {
+                const float* pm = cam.proj;
+                const float hx = pm[0] * p.x + pm[4] * p.y + pm[8] * p.z + pm[12];
+                const float hy = pm[1] * p.x + pm[5] * p.y + pm[9] * p.z + pm[13];
+                const float hw = pm[3] * p.x + pm[7] * p.y + pm[11] * p.z + pm[15];
+                const float p_w = 1.0f / (hw + 0.0000001f);
+                const float fzy = cam.focal_y / p_view.z, ly = 1.3f * cam.tan_fovy;
+                const float fzx = cam.focal_x / p_view.z, lx = 1.3f * cam.tan_fovx;
+                // (|J row|^2 trace 1.02 + 0.3) * power <= |J row|^2 1.02 q + 0.3 kPowerMax
+                const float reach_y = 1.414214f * sqrtf(fzy * fzy * (1.0f + ly * ly) * 1.02f * b.w + 0.3f * kPowerMax) * 1.02f + 2.0f + (float)cam.block_y;
+                const float reach_x = 1.414214f * sqrtf(fzx * fzx * (1.0f + lx * lx) * 1.02f * b.w + 0.3f * kPowerMax) * 1.02f + 2.0f + (float)cam.block_x;
+                const float py = ndc_to_pix(hy * p_w, cam.H), px = ndc_to_pix(hx * p_w, cam.W);
+                const bool off_rows = py + reach_y < (float)(cam.row_begin * cam.block_y) || py - reach_y > (float)(cam.row_end * cam.block_y);
+                const bool off_cols = px + reach_x < 0.0f || px - reach_x > (float)(cam.grid_x * cam.block_x);
+                keep = !off_rows && !off_cols;
+            }
+        } else {
+            const f3 p = { __ldg(positions + 3 * (size_t)i), __ldg(positions + 3 * (size_t)i + 1), __ldg(positions + 3 * (size_t)i + 2) };
+            const f3 p_view = xform4x3(p, cam.view);
+            const float opacity = __ldg(opacities + i);
+            if (!(p_view.z <= 0.2f) && !(255.0f * opacity < 1.0f)) {
+                const float* pm = cam.proj;
+                const float hy = pm[1] * p.x + pm[5] * p.y + pm[9] * p.z + pm[13];
+                const float hw = pm[3] * p.x + pm[7] * p.y + pm[11] * p.z + pm[15];
+                const float projy = hy * (1.0f / (hw + 0.0000001f));
+                float c3[6];
 #pragma unroll
-            for (int q = 0; q < 6; q++) c3[q] = __ldg(cov3ds + 6 * (size_t)i + q);
-            const float hx = pm[0] * p.x + pm[4] * p.y + pm[8] * p.z + pm[12];
-            const float projx = hx * (1.0f / (hw + 0.0000001f));
-            keep = !misses_strip(cam, p_view.z, opacity, c3, projy) && !misses_columns(cam, p_view.z, opacity, c3, projx);
+                for (int q = 0; q < 6; q++) c3[q] = __ldg(cov3ds + 6 * (size_t)i + q);
+                const float hx = pm[0] * p.x + pm[4] * p.y + pm[8] * p.z + pm[12];
+                const float projx = hx * (1.0f / (hw + 0.0000001f));
+                keep = !misses_strip(cam, p_view.z, opacity, c3, projy) && !misses_columns(cam, p_view.z, opacity, c3, projx);
+            }
         }
     }
     const unsigned kept = __ballot_sync(FULL_MASK, keep);
@@ -289,7 +339,7 @@ strip_cull_kernel(int P, const float* __restrict__ positions, const float* __res
     if (keep) {
         int at = s_base + __popc(kept & lanemask_lt());
         for (int w = 0; w < warp; w++) at += s_count[w];
-        list[1 + at] = i;
+        if (FGS_INDEX_OK(at, P)) list[1 + at] = i;
     }
 }
 
@@ -300,6 +350,10 @@ __device__ unsigned long long g_pre_cycles[8];
 #define FGS_PT(i) do { if (threadIdx.x == 0) { const long long now_ = clock64(); atomicAdd(&g_pre_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
 #else
 #define FGS_PT(i) do { } while (0)
+#endif
+
+#ifdef FGS_EXP_TILE_COUNT_IN_PRE
+__device__ unsigned g_exp_tile_count[65536];
 #endif
 
 template <bool VEC>
@@ -341,7 +395,8 @@ preprocess_kernel(int P,
     if (base >= total_here) return;
     const int n_here = min(PRE_THREADS, total_here - base);
     if (list != nullptr) {
-        const int i = tid < n_here ? list[1 + base + tid] : 0;
+        int i = tid < n_here ? list[1 + base + tid] : 0;
+        if (!FGS_INDEX_OK(i, P)) i = 0;   // checked build: a list entry outside the scene is reported and replaced
         s_idx[tid] = i;
         if (tid < n_here) {
 #pragma unroll
@@ -466,11 +521,16 @@ preprocess_kernel(int P,
     const unsigned lt = lanemask_lt(), le = lt | (1u << lane);
     auto write_staged = [&](long long first, int count) {
         for (int i = lane; i < count; i += 32) {
+            if (!FGS_INDEX_OK(i, STG_CAP)) continue;
             const uint2 e = stage[i];
             const long long o = first + i;
+            if (!FGS_INDEX_OK(e.y, PRE_THREADS) || !FGS_INDEX_OK(e.x, cam.grid_x * cam.grid_y)) continue;
             if (o >= 0 && o < capacity) {
                 keys[o] = ((uint64_t)e.x << 32) | (uint32_t)s_rect[e.y].w;
                 values[o] = (uint32_t)s_idx[e.y];
+#ifdef FGS_EXP_TILE_COUNT_IN_PRE
+                atomicAdd(&g_exp_tile_count[e.x & 0xFFFFu], 1u);   // experiment: what per-tile counting costs here
+#endif
             } else {
                 atomicOr(status, FGS_ERR_PAIR_OVERFLOW);
             }
@@ -488,6 +548,7 @@ preprocess_kernel(int P,
                 if (s_prefix[mid] <= item) lo = mid; else hi = mid;
             }
             g = lo;
+            if (!FGS_INDEX_OK(g, PRE_THREADS)) g = 0;
             const int4 rc = s_rect[g];
             const int t = item - s_prefix[g];
             const int ns = (rc.z + 31) >> 5;
@@ -537,7 +598,7 @@ preprocess_kernel(int P,
         if (candidates == 0) continue;
         const unsigned has = __ballot_sync(FULL_MASK, cnt > 0);
         __syncwarp();   // the previous round's reads of s_rec / s_src are over
-        if (cnt > 0) s_src[warp][__popc(has & lt)] = (uint8_t)lane;
+        if (cnt > 0 && FGS_INDEX_OK(__popc(has & lt), 32)) s_src[warp][__popc(has & lt)] = (uint8_t)lane;
         s_rec[warp][lane] = make_int4(excl, g, ty, x_begin);
         __syncwarp();
         // 3. 32 candidates at a time, one exact test per lane; hits go to the warp's staging buffer
@@ -550,7 +611,11 @@ preprocess_kernel(int P,
             int tile = 0, gs = 0;
             if (j < candidates) {
                 // the item this candidate belongs to: the last one that begins at or before it
-                const int4 rc = s_rec[warp][s_src[warp][before + __popc(starts & le) - 1]];
+                int src_at = before + __popc(starts & le) - 1;
+                if (!FGS_INDEX_OK(src_at, 32)) src_at = 0;
+                int src_lane = s_src[warp][src_at];
+                if (!FGS_INDEX_OK(src_lane, 32)) src_lane = 0;
+                const int4 rc = s_rec[warp][src_lane];
                 const int tx = rc.w + (j - rc.x);
                 gs = rc.y;
                 const float2 c = s_xy[gs];
@@ -559,7 +624,7 @@ preprocess_kernel(int P,
                 tile = rc.z * cam.grid_x + tx;
             }
             const unsigned hits = __ballot_sync(FULL_MASK, hit);
-            if (hit) {
+            if (hit && FGS_INDEX_OK(staged + __popc(hits & lt), STG_CAP) && FGS_INDEX_OK(gs, PRE_THREADS)) {
                 stage[staged + __popc(hits & lt)] = make_uint2((unsigned)tile, (unsigned)gs);
                 s_vis[gs] = 1;
             }
@@ -587,7 +652,7 @@ preprocess_kernel(int P,
     }
 
     // ---- features of visible Gaussians (preprocess.cu:411-417) ----
-    if (tid < n_here && s_vis[tid]) {
+    if (tid < n_here && s_vis[tid] && FGS_INDEX_OK(s_idx[tid], P)) {
         const int idx = s_idx[tid];
         float sh[48];
         if (VEC) {
@@ -626,6 +691,8 @@ void host_view_proj(int width, int height, const float* pos, const float* rot, f
 
 } // namespace fgs
 
+FGS_BOUNDS_REPORT_FN(fgs_debug_bounds_preprocess)
+
 #ifdef FGS_PRE_TIMING
 extern "C" int fgs_debug_pre_phase_cycles(unsigned long long* out8, int reset)
 {
@@ -650,7 +717,8 @@ static int preprocess_impl(int P, const float* positions, const float* shs, cons
                            int tile_row_begin, int tile_row_end,
                            float* points_xy, float* rgb_depth, float* conic_opacity,
                            uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
-                           int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream, cudaEvent_t* events)
+                           int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream, cudaEvent_t* events,
+                           const float* scene_bounds = nullptr)
 {
     if (P < 0 || width <= 0 || height <= 0 || block_x <= 0 || block_y <= 0 || pair_capacity < 0) return FGS_ERR_BAD_ARG;
     if (cull_scratch != nullptr && cull_scratch_ints < (int64_t)P + 1) return FGS_ERR_TEMP_TOO_SMALL;
@@ -685,7 +753,10 @@ static int preprocess_impl(int P, const float* positions, const float* shs, cons
     if (events) cudaEventRecord(events[0], st);
     if (cull_scratch != nullptr) {
         if (cudaMemsetAsync(cull_scratch, 0, sizeof(int), st) != cudaSuccess) return FGS_ERR_CUDA;
-        strip_cull_kernel<<<groups, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, cam, cull_scratch);
+        if (scene_bounds != nullptr && aligned16(scene_bounds))
+            strip_cull_kernel<true><<<groups, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, reinterpret_cast<const float4*>(scene_bounds), cam, cull_scratch);
+        else
+            strip_cull_kernel<false><<<groups, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, nullptr, cam, cull_scratch);
         list = cull_scratch;
     }
     if (events) cudaEventRecord(events[1], st);
@@ -716,6 +787,33 @@ extern "C" int fgs_preprocess_strip_culled(int P, const float* positions, const 
                                 keys_unsorted, values_unsorted, pair_capacity, curr_offset, cull_scratch, cull_scratch_ints, stream, nullptr);
 }
 
+extern "C" int fgs_scene_bounds(int P, const float* positions, const float* opacities, const float* cov3ds, float* bounds, void* stream)
+{
+    if (P < 0) return FGS_ERR_BAD_ARG;
+    if (P == 0) return FGS_OK;
+    if (!positions || !opacities || !cov3ds || !bounds || !fgs::aligned16(bounds)) return FGS_ERR_BAD_ARG;
+    fgs::scene_bounds_kernel<<<(P + fgs::PRE_THREADS - 1) / fgs::PRE_THREADS, fgs::PRE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+        P, positions, opacities, cov3ds, reinterpret_cast<float4*>(bounds));
+    return fgs::launch_status();
+}
+
+extern "C" int fgs_preprocess_prepared(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                                       int width, int height, int block_x, int block_y,
+                                       const float* cam_position, const float* cam_rotation,
+                                       float focal_x, float focal_y, float zFar, float zNear,
+                                       int tile_row_begin, int tile_row_end,
+                                       float* points_xy, float* rgb_depth, float* conic_opacity,
+                                       uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                                       int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints,
+                                       const float* scene_bounds, void* stream)
+{
+    if (scene_bounds != nullptr && (cull_scratch == nullptr || !fgs::aligned16(scene_bounds))) return FGS_ERR_BAD_ARG;
+    return fgs::preprocess_impl(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y, cam_position, cam_rotation,
+                                focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end, points_xy, rgb_depth, conic_opacity,
+                                keys_unsorted, values_unsorted, pair_capacity, curr_offset, cull_scratch, cull_scratch_ints, stream, nullptr,
+                                scene_bounds);
+}
+
 extern "C" int fgs_preprocess_profile(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
                                       int width, int height, int block_x, int block_y,
                                       const float* cam_position, const float* cam_rotation,
@@ -723,8 +821,8 @@ extern "C" int fgs_preprocess_profile(int P, const float* positions, const float
                                       int tile_row_begin, int tile_row_end,
                                       float* points_xy, float* rgb_depth, float* conic_opacity,
                                       uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
-                                      int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream,
-                                      float* kernel_ms2)
+                                      int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints,
+                                      const float* scene_bounds, void* stream, float* kernel_ms2)
 {
     if (!kernel_ms2) return FGS_ERR_BAD_ARG;
     cudaEvent_t ev[3];
@@ -732,7 +830,8 @@ extern "C" int fgs_preprocess_profile(int P, const float* positions, const float
         if (cudaEventCreate(&e) != cudaSuccess) return FGS_ERR_CUDA;
     int st = fgs::preprocess_impl(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y, cam_position, cam_rotation,
                                   focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end, points_xy, rgb_depth, conic_opacity,
-                                  keys_unsorted, values_unsorted, pair_capacity, curr_offset, cull_scratch, cull_scratch_ints, stream, ev);
+                                  keys_unsorted, values_unsorted, pair_capacity, curr_offset, cull_scratch, cull_scratch_ints, stream, ev,
+                                  scene_bounds);
     kernel_ms2[0] = kernel_ms2[1] = 0.0f;
     if (st == FGS_OK && P > 0) {
         if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) st = FGS_ERR_CUDA;

@@ -63,7 +63,7 @@ __global__ void tile_ranges_kernel(const uint64_t* __restrict__ keys, int n, con
     __syncthreads();
     if (threadIdx.x >= RANGE_TILES || tile >= num_tiles) return;
     const int first = s_first[threadIdx.x], last = s_first[threadIdx.x + 1];
-    ranges[tile] = (last > first) ? make_int2(first, last) : make_int2(0, 0);
+    if (FGS_INDEX_OK(tile, num_tiles)) ranges[tile] = (last > first) ? make_int2(first, last) : make_int2(0, 0);
 }
 
 __device__ __forceinline__ float ex2_approx_ftz(float x)
@@ -109,7 +109,7 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
              int width, int height, int grid_x, int row_begin, int num_strip_tiles,
              const float2* __restrict__ points_xy, const float4* __restrict__ rgb_depth,
              const float4* __restrict__ conic_opacity,
-             float bg_r, float bg_g, float bg_b, int vector_store,
+             float bg_r, float bg_g, float bg_b, int vector_store, int list_len, const int* __restrict__ list_len_dev,
              uint8_t* __restrict__ out_color, float* __restrict__ out_rgb, float* __restrict__ out_alpha,
              float* __restrict__ out_depth, int* __restrict__ consumed)
 {
@@ -123,7 +123,14 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
     const int tile_y = row_begin + strip_tile / grid_x;
     const int tile_x = strip_tile - (strip_tile / grid_x) * grid_x;
     const int tile = tile_y * grid_x + tile_x;
-    const int2 range = ranges[tile];
+    int2 range = ranges[tile];
+#ifdef FGS_DEBUG_BOUNDS
+    {   // checked build: a tile's range must lie inside the sorted list
+        int len = list_len;
+        if (list_len_dev != nullptr) { const int v = *list_len_dev; len = v < 0 ? 0 : (v < len ? v : len); }
+        if (range.y != range.x && !(FGS_INDEX_OK(range.x, len) && FGS_INDEX_OK(range.y - 1, len) && range.y > range.x)) range = make_int2(0, 0);
+    }
+#endif
     const int n = range.y - range.x;
     BlendStage* stage = s_stage[warp];
 
@@ -263,7 +270,7 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
             so[cy][cx * 3 + 2] = encode_u8(bl);
             if (EXTRA) {
                 const int X = px0 + j, Y = py0 + i;
-                if (X < width && Y < height) {
+                if (X < width && Y < height && FGS_INDEX_OK((size_t)Y * width + X, (size_t)height * width)) {
                     const size_t pix = (size_t)Y * width + X;
                     if (out_rgb) { out_rgb[3 * pix] = r; out_rgb[3 * pix + 1] = g; out_rgb[3 * pix + 2] = bl; }
                     if (out_alpha) out_alpha[pix] = 1.0f - Traw;
@@ -278,7 +285,7 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
         constexpr int CHUNKS_PER_ROW = BX * 3 / 16;
         for (int c = lane; c < BY * CHUNKS_PER_ROW; c += 32) {
             const int row = c / CHUNKS_PER_ROW, part = c - row * CHUNKS_PER_ROW;
-            if (Y0 + row < height) {
+            if (Y0 + row < height && FGS_INDEX_OK(((size_t)(Y0 + row) * width + X0) * 3 + part * 16 + 15, (size_t)height * width * 3)) {
                 const uint4 v = *reinterpret_cast<const uint4*>(&so[row][part * 16]);
                 *reinterpret_cast<uint4*>(out_color + ((size_t)(Y0 + row) * width + X0) * 3 + part * 16) = v;
             }
@@ -287,7 +294,7 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
         for (int c = lane; c < BY * BX * 3; c += 32) {
             const int row = c / (BX * 3), col = c - row * (BX * 3);
             const int X = X0 + col / 3;
-            if (Y0 + row < height && X < width)
+            if (Y0 + row < height && X < width && FGS_INDEX_OK(((size_t)(Y0 + row) * width + X) * 3 + (col - (col / 3) * 3), (size_t)height * width * 3))
                 out_color[((size_t)(Y0 + row) * width + X) * 3 + (col - (col / 3) * 3)] = so[row][col];
         }
     }
@@ -316,13 +323,13 @@ int launch_render(int num_rendered, int width, int height,
         blend_kernel<BX, BY, true><<<blocks, BLEND_WARPS * 32, 0, st>>>(
             reinterpret_cast<const int2*>(ranges), values_sorted, width, height, grid_x, row_begin, strip_tiles,
             reinterpret_cast<const float2*>(points_xy), reinterpret_cast<const float4*>(rgb_depth),
-            reinterpret_cast<const float4*>(conic_opacity), bg[0], bg[1], bg[2], vec,
+            reinterpret_cast<const float4*>(conic_opacity), bg[0], bg[1], bg[2], vec, num_rendered, n_dev,
             out_color, out_rgb, out_alpha, out_depth, consumed);
     else
         blend_kernel<BX, BY, false><<<blocks, BLEND_WARPS * 32, 0, st>>>(
             reinterpret_cast<const int2*>(ranges), values_sorted, width, height, grid_x, row_begin, strip_tiles,
             reinterpret_cast<const float2*>(points_xy), reinterpret_cast<const float4*>(rgb_depth),
-            reinterpret_cast<const float4*>(conic_opacity), bg[0], bg[1], bg[2], vec,
+            reinterpret_cast<const float4*>(conic_opacity), bg[0], bg[1], bg[2], vec, num_rendered, n_dev,
             out_color, nullptr, nullptr, nullptr, nullptr);
     return launch_status();
 }
@@ -333,6 +340,25 @@ int sort_pairs_device_count(int capacity, const int* n_dev, int width, int heigh
                             void* temp, size_t temp_bytes, const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
                             uint64_t* keys_sorted, uint32_t* values_sorted, void* stream);
 } // namespace fgs
+
+FGS_BOUNDS_REPORT_FN(fgs_debug_bounds_render)
+
+#ifdef FGS_DEBUG_BOUNDS
+namespace fgs {
+__global__ void bounds_selftest_kernel(int index, int extent, int* touched)
+{
+    if (FGS_INDEX_OK(index, extent)) *touched = 1;   // the "access" the check guards
+}
+} // namespace fgs
+// Checked build: runs the check itself on (index, extent) with one thread, touching a caller-owned int only when the
+// index is inside the extent; lets a test see that a violation is counted, recorded and skipped.
+extern "C" int fgs_debug_bounds_selftest(int index, int extent, int* touched, void* stream)
+{
+    if (!touched) return FGS_ERR_BAD_ARG;
+    fgs::bounds_selftest_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(index, extent, touched);
+    return fgs::launch_status();
+}
+#endif
 
 // One whole frame without any host round trip: preprocess -> sort -> tile ranges -> blend, the pair count staying on
 // the device. See include/flashgs_b200.h.

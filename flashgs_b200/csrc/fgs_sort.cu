@@ -424,8 +424,10 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
             if (j < valid) {
                 const uint64_t k = out_keys[j];
                 const uint32_t dst = s_delta[digit_of<SHIFT>(k, digit_mask)] + (uint32_t)j;
-                keys_out[dst] = k;
-                vals_out[dst] = out_vals[j];
+                if (FGS_INDEX_OK(dst, n)) {
+                    keys_out[dst] = k;
+                    vals_out[dst] = out_vals[j];
+                }
             }
         }
     };
@@ -551,8 +553,10 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict
         for (int i = 0; i < SORT_ITEMS; i++) {
             const uint32_t d = digit_of<SHIFT>(key[i], digit_mask);
             const uint32_t pos = s_local_start[b][d] + s_whist[warp][d] + rank[i];
-            out_keys[pos] = key[i];
-            out_vals[pos] = val[i];
+            if (FGS_INDEX_OK(pos, SORT_PART)) {
+                out_keys[pos] = key[i];
+                out_vals[pos] = val[i];
+            }
         }
         prev_valid = valid;
         // after a failed wait no further partitions are started: both loops end within two iterations
@@ -598,7 +602,7 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
     int c = -1, slot = 0;
     if (threadIdx.x < SEG_TILES && t < tile_values) {
         const int first = s_first[threadIdx.x], last = s_first[threadIdx.x + 1];
-        seg[t] = make_int2(first, last);
+        if (FGS_INDEX_OK(t, MAX_TILE_VALUES)) seg[t] = make_int2(first, last);
         const int len = last - first;
         if (len > 0) {   // queue the tile for the sort of its length class
             c = len <= 1024 ? 0 : (len <= 2048 ? 1 : (len <= LOCAL_CAP ? 2 : 3));
@@ -611,7 +615,7 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
     if (threadIdx.x < LOCAL_CLASSES && s_class_count[threadIdx.x] > 0)
         s_class_base[threadIdx.x] = atomicAdd(class_count + threadIdx.x, s_class_count[threadIdx.x]);
     __syncthreads();
-    if (c >= 0) class_tiles[(size_t)c * MAX_TILE_VALUES + s_class_base[c] + slot] = (uint32_t)t;
+    if (c >= 0 && FGS_INDEX_OK(s_class_base[c] + slot, MAX_TILE_VALUES)) class_tiles[(size_t)c * MAX_TILE_VALUES + s_class_base[c] + slot] = (uint32_t)t;
 }
 
 // ---- tile grouping without any wait between blocks ----
@@ -659,6 +663,7 @@ tile_hist_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict
     }
     auto count = [&](uint64_t key) {
         const uint32_t t = (uint32_t)(key >> 32) & tile_mask;
+        if (!FGS_INDEX_OK(t, tile_values)) return;
         if (in_smem) atomicAdd(&s_tiles[t], 1u); else atomicAdd(tile_count + t, 1u);
     };
     const int64_t stride = (int64_t)gridDim.x * TILE_HIST_THREADS, me = (int64_t)blockIdx.x * TILE_HIST_THREADS + threadIdx.x;
@@ -745,10 +750,10 @@ tile_scan_kernel(const uint32_t* __restrict__ tile_count, int tile_values, int l
             const uint32_t first = ok ? s_pref[scan_pad(i)] : 0u;
             const uint32_t c = ok ? s_pref[scan_pad(i + 1)] - first : 0u;
             const int t = lo + i;
-            if (ok) {
+            if (ok && FGS_INDEX_OK(t, MAX_TILE_VALUES)) {
                 seg[t] = make_int2((int)first, (int)(first + c));
                 cursor[t] = first;
-                if (((uint32_t)t & lo_mask) == 0) s_bucket_first[t >> lo_bits] = first;
+                if (((uint32_t)t & lo_mask) == 0 && FGS_INDEX_OK(t >> lo_bits, MAX_BUCKETS)) s_bucket_first[t >> lo_bits] = first;
             }
             const int k = c == 0 ? -1 : (c <= 1024u ? 0 : (c <= 2048u ? 1 : (c <= (uint32_t)LOCAL_CAP ? 2 : 3)));
 #pragma unroll
@@ -758,7 +763,8 @@ tile_scan_kernel(const uint32_t* __restrict__ tile_count, int tile_values, int l
                     uint32_t at = 0;
                     if (lane == 0) at = atomicAdd(&s_class[q], (uint32_t)__popc(in_class));
                     at = __shfl_sync(FULL_MASK, at, 0);
-                    if (k == q) class_tiles[(size_t)q * MAX_TILE_VALUES + at + __popc(in_class & lt)] = (uint32_t)t;
+                    if (k == q && FGS_INDEX_OK(at + __popc(in_class & lt), MAX_TILE_VALUES))
+                        class_tiles[(size_t)q * MAX_TILE_VALUES + at + __popc(in_class & lt)] = (uint32_t)t;
                 }
             }
         }
@@ -898,7 +904,8 @@ multisplit_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restri
     const uint32_t lstart = off + inc - c;
     s_lstart[tid] = lstart;
     uint32_t gstart = 0;
-    if (c) gstart = atomicAdd(cursors + cursor_base + tid, c);   // its round trip overlaps the reordering below
+    if (c && FGS_INDEX_OK(cursor_base + tid, SECOND ? MAX_TILE_VALUES : MAX_BUCKETS))
+        gstart = atomicAdd(cursors + cursor_base + tid, c);   // its round trip overlaps the reordering below
 #if FGS_MS_LATE_VALUES
     // the values are not needed before this point: fetched now, they do not hold registers during the ranking
     uint32_t val[MS_ITEMS];
@@ -914,8 +921,10 @@ multisplit_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restri
         const int j = i * MS_THREADS + tid;
         if (j < count) {
             const uint32_t pos = s_lstart[digit_of_key(key[i])] + slot[i];
-            st_keys[pos] = key[i];
-            st_vals[pos] = val[i];
+            if (FGS_INDEX_OK(pos, MS_PART)) {
+                st_keys[pos] = key[i];
+                st_vals[pos] = val[i];
+            }
         }
     }
     s_delta[tid] = gstart - lstart;
@@ -923,7 +932,7 @@ multisplit_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restri
     for (int j = tid; j < count; j += MS_THREADS) {
         const uint64_t k = st_keys[j];
         const uint32_t dst = s_delta[digit_of_key(k)] + (uint32_t)j;
-        if (dst < (uint32_t)n) {   // always true for consistent tables
+        if (FGS_INDEX_OK(dst, n) && dst < (uint32_t)n) {   // always true for consistent tables
             keys_out[dst] = k;
             vals_out[dst] = st_vals[j];
         }
@@ -1085,8 +1094,10 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
                 if (wb + q * 32 + lane < n) {
                     const uint32_t d = digit_of_pair(key[q], val[q], pass);
                     const uint32_t pos = lstart[d] + whist[warp * RADIX + d] + rank[q];
-                    stage_k[pos] = key[q];
-                    stage_v[pos] = val[q];
+                    if (FGS_INDEX_OK(pos, CHUNK)) {
+                        stage_k[pos] = key[q];
+                        stage_v[pos] = val[q];
+                    }
                 }
             }
             __syncthreads();
@@ -1096,8 +1107,10 @@ __device__ void long_list_sort(uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_
                 const uint32_t v = stage_v[j];
                 const uint32_t d = digit_of_pair(k, v, pass);
                 const uint32_t pos = run[d] + ((uint32_t)j - lstart[d]);
-                dst_k[pos] = k;
-                dst_v[pos] = v;
+                if (FGS_INDEX_OK(pos, n)) {
+                    dst_k[pos] = k;
+                    dst_v[pos] = v;
+                }
             }
             __syncthreads();
             if (tid < RADIX) run[tid] += chunk_count;
@@ -1271,7 +1284,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
             const int i = tid + q * THREADS;
             if (i < n) {
                 const int b = bucket_of(d[q]);
-                where[q] = (uint32_t)b | (atomicAdd(&cursor[b], 1u) << 16);
+                if (FGS_INDEX_OK(b, NB)) where[q] = (uint32_t)b | (atomicAdd(&cursor[b], 1u) << 16);
             }
         }
         int2 next_seg = make_int2(0, -1);
@@ -1304,7 +1317,8 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
 #pragma unroll
             for (int q = 0; q < ITEMS; q++) {
                 const int i = tid + q * THREADS;
-                if (i < n) bk[start[where[q] & 0xFFFFu] + (where[q] >> 16)] = ((uint64_t)d[q] << 32) | low[q];
+                if (i < n && FGS_INDEX_OK(start[where[q] & 0xFFFFu] + (where[q] >> 16), n))
+                    bk[start[where[q] & 0xFFFFu] + (where[q] >> 16)] = ((uint64_t)d[q] << 32) | low[q];
             }
             fetch(s_seg);   // the registers are free again: request the next list's keys
             fetched = true;
@@ -1322,7 +1336,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
                     const uint64_t other = bk[y];
                     rank += (other < kc) || (other == kc && y < x);
                 }
-                a[s0 + rank] = kc;
+                if (FGS_INDEX_OK(s0 + rank, n)) a[s0 + rank] = kc;
             }
             FGS_LT(5);
             gathered = true;
@@ -1371,7 +1385,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
         if (by_value) {
             keys_out[r.x + i] = ((uint64_t)tile_word << 32) | (k >> 32);
             vals_out[r.x + i] = low_word;
-        } else {
+        } else if (FGS_INDEX_OK(low_word, n)) {
             const uint32_t high = mixed ? (uint32_t)(__ldg(keys_grouped + r.x + low_word) >> 32) : tile_word;
             keys_out[r.x + i] = ((uint64_t)high << 32) | (k >> 32);
             vals_out[r.x + i] = __ldg(vals_grouped + r.x + low_word);
@@ -1389,6 +1403,8 @@ int g_debug_skip_publish_part = -1;
 
 } // namespace
 } // namespace fgs
+
+FGS_BOUNDS_REPORT_FN(fgs_debug_bounds_sort)
 
 #ifdef FGS_SORT_TIMING
 extern "C" int fgs_debug_local_phase_cycles(unsigned long long* out8, int reset)

@@ -73,10 +73,11 @@ def preprocess(orig_points, shs, opacities, cov3Ds, width, height, block_x, bloc
                position, rotation, focal_x, focal_y, zFar, zNear,
                points_xy, rgb_depth, conic_opacity,
                gaussian_keys_unsorted, gaussian_values_unsorted, curr_offset,
-               tile_row_begin: int = 0, tile_row_end: int = -1, cull_scratch=None) -> None:
+               tile_row_begin: int = 0, tile_row_end: int = -1, cull_scratch=None, scene_bounds=None) -> None:
     """csrc/pybind.cpp:122-150. The trailing keyword arguments restrict the pairs to a strip of tile rows;
     ``cull_scratch`` (int32 CUDA tensor, at least P + 1 elements) lets a strip list the Gaussians that can reach it
-    first and run the expensive kernel on those only."""
+    first and run the expensive kernel on those only; ``scene_bounds`` (what ``prepare_scene`` returned for these
+    arrays) makes that first kernel read 16 bytes per Gaussian instead of 40."""
     f32 = torch.float32
     pts = _in(orig_points, "orig_points", f32)
     sh = _in(shs, "shs", f32)
@@ -93,16 +94,38 @@ def preprocess(orig_points, shs, opacities, cov3Ds, width, height, block_x, bloc
     P = int(op.size(0))
     cap = min(int(keys.numel()), int(vals.numel()))
     scratch = None if cull_scratch is None else _out(cull_scratch, "cull_scratch", torch.int32)
-    st = _L.fgs_preprocess_strip_culled(P, pts.data_ptr(), sh.data_ptr(), op.data_ptr(), cov.data_ptr(),
-                                        int(width), int(height), int(block_x), int(block_y),
-                                        pos.data_ptr(), rot.data_ptr(),
-                                        float(focal_x), float(focal_y), float(zFar), float(zNear),
-                                        int(tile_row_begin), int(tile_row_end),
-                                        xy.data_ptr(), rd.data_ptr(), co.data_ptr(),
-                                        keys.data_ptr(), vals.data_ptr(), cap, off.data_ptr(),
-                                        None if scratch is None else scratch.data_ptr(),
-                                        0 if scratch is None else int(scratch.numel()), _stream())
+    bounds = None
+    if scene_bounds is not None:
+        bounds = _in(scene_bounds, "scene_bounds", f32)
+        if scratch is None or bounds.numel() != 4 * P or not scene_bounds.is_contiguous():
+            raise RuntimeError("scene_bounds needs cull_scratch and one contiguous [4] record per Gaussian")
+    st = _L.fgs_preprocess_prepared(P, pts.data_ptr(), sh.data_ptr(), op.data_ptr(), cov.data_ptr(),
+                                    int(width), int(height), int(block_x), int(block_y),
+                                    pos.data_ptr(), rot.data_ptr(),
+                                    float(focal_x), float(focal_y), float(zFar), float(zNear),
+                                    int(tile_row_begin), int(tile_row_end),
+                                    xy.data_ptr(), rd.data_ptr(), co.data_ptr(),
+                                    keys.data_ptr(), vals.data_ptr(), cap, off.data_ptr(),
+                                    None if scratch is None else scratch.data_ptr(),
+                                    0 if scratch is None else int(scratch.numel()),
+                                    None if bounds is None else bounds.data_ptr(), _stream())
     _lib.check("preprocess", st)
+
+
+def prepare_scene(orig_points, opacities, cov3Ds, out=None):
+    """Once per scene (no reference counterpart): the ``[P, 4]`` float32 records -- position and
+    trace(covariance) * ln(256 * opacity) -- that ``preprocess(..., cull_scratch=, scene_bounds=)`` streams to list the
+    Gaussians that can reach a strip. They depend on the scene only, not on the camera."""
+    f32 = torch.float32
+    pts, op, cov = _in(orig_points, "orig_points", f32), _in(opacities, "opacities", f32), _in(cov3Ds, "cov3Ds", f32)
+    P = int(op.size(0))
+    if out is None:
+        out = torch.empty((P, 4), device=op.device, dtype=f32)
+    out = _out(out, "out", f32)
+    if out.numel() < 4 * P:
+        raise RuntimeError("out needs 4 floats per Gaussian")
+    _lib.check("prepare_scene", _L.fgs_scene_bounds(P, pts.data_ptr(), op.data_ptr(), cov.data_ptr(), out.data_ptr(), _stream()))
+    return out
 
 
 def get_sort_buffer_size(num_rendered: int) -> int:

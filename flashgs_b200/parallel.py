@@ -4,8 +4,11 @@ The reference is single-GPU; this is the multi-GPU form of the same path. Every 
 holds the whole scene, runs the pipeline restricted to its strip of tile rows
 (``preprocess`` drops every Gaussian whose tile rectangle misses the strip, keys keep
 their whole-frame tile ids) and ends up with the pixel rows of its strip. There is no
-collective inside the frame. Only when a single image is wanted are the strips gathered
-on one rank (one ``gather`` of equally padded strips, over NVLink when the backend is NCCL).
+collective inside the frame. When a single image is wanted on one DEVICE, the strips are
+gathered on one rank (``gather_strips``: one ``gather`` of equally padded strips, over NVLink
+when the backend is NCCL); when it is wanted on the HOST, every rank copies its own strip into
+one host image that all ranks of the node share (``HostFrames``), so that the frame leaves
+through all PCIe links at once and nothing crosses between GPUs.
 
 The helpers here are backend-agnostic (they work on CPU tensors over gloo as well), so the
 partition and gather logic is testable without a GPU.
@@ -89,31 +92,6 @@ def gather_strips(local_image: torch.Tensor, all_rows: List[Tuple[int, int]], bl
         if b > a:
             out[a:b] = recv[r][: b - a]
     return out
-
-
-class PeerFrames:
-    """``count`` frame buffers that live on rank ``dst`` and are mapped into every rank of the group (torch symmetric
-    memory: peer mappings over NVLink). A rank passes ``frames[i]`` as the output image of its strip, so its blend
-    kernel stores the strip's pixels straight into the destination's buffer with ordinary stores; ``barrier()``
-    (device side, on the current stream) then tells the destination that every strip has landed. No gather follows.
-    Raises whatever the symmetric-memory set-up raises when peer mappings are not available; callers fall back to
-    ``gather_strips``."""
-
-    def __init__(self, count: int, height: int, width: int, device, dst: int = 0, group=None):
-        import os
-        # only plain peer stores are used: ask the allocator not to bind the buffers to an NVLink multicast object
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        import torch.distributed._symmetric_memory as symm_mem
-        group = group if group is not None else dist.group.WORLD
-        shape = (count, height, width, 3)
-        self.local = symm_mem.empty(shape, dtype=torch.int8, device=device)
-        self.handle = symm_mem.rendezvous(self.local, group)
-        target = self.handle.get_buffer(dst, shape, torch.int8)
-        self.frames = [target[i] for i in range(count)]
-        self.dst = dst
-
-    def barrier(self) -> None:
-        self.handle.barrier(channel=0)
 
 
 class HostFrames:

@@ -75,6 +75,9 @@ class Rasterizer:
         need = 4 * (scene.num_vertex + 1)
         ours = hasattr(ops, "render_frame")   # another operator module (the reference's) has no such argument
         self.cull_scratch = (self.list_sorting_space[:need].view(torch.int32) if ours and self.SORT_BUFFER_SIZE >= need else None)
+        # ... and that list is found from 16-byte records prepared once per scene (position and a bound on the reach)
+        self.scene_bounds = (ops.prepare_scene(scene.position, scene.opacity, scene.cov3d)
+                             if self.cull_scratch is not None and hasattr(ops, "prepare_scene") else None)
         self._render = {(16, 16): "render_16x16", (32, 16): "render_32x16", (32, 32): "render_32x32"}[tuple(block)]
 
     def forward(self, scene: DeviceScene, camera, bg_color, out_color=None, rows=None):
@@ -84,6 +87,8 @@ class Rasterizer:
         extra = {} if rows is None else dict(tile_row_begin=rows[0], tile_row_end=rows[1])
         if self.cull_scratch is not None:
             extra["cull_scratch"] = self.cull_scratch
+            if self.scene_bounds is not None:
+                extra["scene_bounds"] = self.scene_bounds
         ops.preprocess(scene.position, scene.shs, scene.opacity, scene.cov3d,
                        camera.width, camera.height, bx, by,
                        camera.position, camera.rotation,

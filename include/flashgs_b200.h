@@ -31,6 +31,8 @@ extern "C" {
 #define FGS_ERR_PAIR_OVERFLOW 4    /* more (tile, Gaussian) pairs than the pair buffers hold */
 #define FGS_ERR_LOOKBACK_TIMEOUT 8 /* a bounded device-side wait gave up */
 #define FGS_ERR_TEMP_TOO_SMALL 16  /* sort scratch smaller than fgs_sort_temp_bytes() */
+#define FGS_ERR_BOUNDS 32          /* checked build only (-DFGS_DEBUG_BOUNDS): a kernel met an index outside its extent
+                                      and skipped the access; see fgs_debug_bounds_report in flashgs_b200_test.h */
 
 /* Version of this ABI; bumped when a signature changes. */
 int fgs_abi_version(void);
@@ -118,7 +120,33 @@ int fgs_preprocess_strip_culled(int P, const float* positions, const float* shs,
                                 int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream);
 
 /*
- * fgs_preprocess_strip_culled with CUDA events around its two kernels: waits for the stream and fills
+ * Scene preparation for fgs_preprocess_prepared, once per scene (not per frame): fills `bounds` [P,4] (16-byte
+ * aligned) with one record per Gaussian -- position and trace(covariance) * ln(256 * opacity), negative for an
+ * opacity below 1/255 -- which is all the index-list kernel needs to decide whether a Gaussian can reach a strip.
+ * No counterpart in the reference.
+ */
+int fgs_scene_bounds(int P, const float* positions, const float* opacities, const float* cov3ds, float* bounds, void* stream);
+
+/*
+ * fgs_preprocess_strip_culled whose index-list kernel streams the prepared records of fgs_scene_bounds (16 bytes per
+ * Gaussian) instead of position, opacity and covariance (40 bytes): that kernel runs over the WHOLE scene on every
+ * GPU that renders a strip, so it is the part of a frame that does not shrink with the number of GPUs. The list
+ * is a superset of fgs_preprocess_strip_culled's; pairs and feature records are the same. `scene_bounds` may be
+ * NULL (then this is fgs_preprocess_strip_culled); with it, `cull_scratch` is required. The records must describe
+ * the arrays passed here. No counterpart in the reference.
+ */
+int fgs_preprocess_prepared(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                            int width, int height, int block_x, int block_y,
+                            const float* cam_position, const float* cam_rotation,
+                            float focal_x, float focal_y, float zFar, float zNear,
+                            int tile_row_begin, int tile_row_end,
+                            float* points_xy, float* rgb_depth, float* conic_opacity,
+                            uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                            int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints,
+                            const float* scene_bounds, void* stream);
+
+/*
+ * fgs_preprocess_prepared with CUDA events around its two kernels: waits for the stream and fills
  * kernel_ms2[0] (the index-list kernel; 0 without scratch) and kernel_ms2[1] (the main kernel). A measurement
  * aid for benchmarks: it creates and destroys events and blocks the host. No counterpart in the reference.
  */
@@ -129,8 +157,8 @@ int fgs_preprocess_profile(int P, const float* positions, const float* shs, cons
                            int tile_row_begin, int tile_row_end,
                            float* points_xy, float* rgb_depth, float* conic_opacity,
                            uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
-                           int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream,
-                           float* kernel_ms2);
+                           int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints,
+                           const float* scene_bounds, void* stream, float* kernel_ms2);
 
 /*
  * Scratch bytes fgs_sort_pairs needs for up to `num_rendered` pairs. Replaces

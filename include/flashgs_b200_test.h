@@ -36,6 +36,22 @@ void fgs_debug_sort_plain(int on);
  */
 void fgs_debug_sort_skip_publish(int part);
 
+/*
+ * The two functions below exist only in the CHECKED flavour of the library (libflashgs_b200_checked.so, built with
+ * -DFGS_DEBUG_BOUNDS by `python -m flashgs_b200.build --checked`). In that flavour every kernel compares each global
+ * store, each index it computed from data and each computed shared-memory index with the extent of what it
+ * addresses, and SKIPS an access that falls outside (nothing faults or traps); fgs_device_status() then carries
+ * FGS_ERR_BOUNDS. It stands in for a memory checker on machines where none can be run, at a cost in speed.
+ *
+ * fgs_debug_bounds_report: waits for the device, then fills out12 (may be NULL) with 3 x 4 values -- for the
+ * preprocess, sort and render kernels: number of violations, source line of the first one, its index, its extent
+ * -- clears the counters if `reset` is non-zero, and returns the total number of violations (negative on error).
+ * fgs_debug_bounds_selftest: applies the check to (index, extent) in a one-thread kernel that writes 1 to the
+ * caller-owned device int `touched` only if the index passes: shows that a violation is counted and skipped.
+ */
+long long fgs_debug_bounds_report(unsigned long long* out12, int reset);
+int fgs_debug_bounds_selftest(int index, int extent, int* touched, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

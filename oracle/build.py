@@ -18,7 +18,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "libfgs_oracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "flash_gaussian_splatting.so")
-CXX = "/usr/bin/g++"  # the system compiler; a wrapped compiler produced a reference module that crashed in loadPly
+# Tool and source locations; each can be overridden from the environment.
+CXX = os.environ.get("FLASHGS_CXX", "/usr/bin/g++")   # the system compiler; a wrapped compiler produced a reference module that crashed in loadPly
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+REFERENCE_ROOT = os.environ.get("FLASHGS_REFERENCE_ROOT", "/root/reference")
+REF_EXAMPLE = os.path.join(REF_DIR, "example.py")   # the reference's example script, beside its build (untracked like it)
 
 
 def _newer(target: str, sources) -> bool:
@@ -38,8 +42,16 @@ def build_oracle(force: bool = False) -> str:
     return ORACLE_SO
 
 
-def build_reference(ref_root: str = "/root/reference", force: bool = False):
-    """Compile the reference extension from its own sources into ``oracle/_ref``. Returns the path or None."""
+def build_reference(ref_root: str = REFERENCE_ROOT, force: bool = False):
+    """Compile the reference extension from its own sources into ``oracle/_ref``. Returns the path or None.
+    The reference's example script is placed beside the build (a test runs it, unmodified, against this
+    repository's drop-in module); like the build it stays out of the history."""
+    example = os.path.join(ref_root, "example.py")
+    if os.path.exists(example):
+        import shutil
+        os.makedirs(REF_DIR, exist_ok=True)
+        if not os.path.exists(REF_EXAMPLE) or os.path.getmtime(REF_EXAMPLE) < os.path.getmtime(example):
+            shutil.copyfile(example, REF_EXAMPLE)
     srcs = [os.path.join(ref_root, "csrc", "cuda_rasterizer", f) for f in ("preprocess.cu", "sort.cu", "render.cu")]
     binding = os.path.join(ref_root, "csrc", "pybind.cpp")
     if not all(os.path.exists(s) for s in srcs + [binding]):
@@ -51,7 +63,7 @@ def build_reference(ref_root: str = "/root/reference", force: bool = False):
 
     os.makedirs(REF_DIR, exist_ok=True)
     inc = []
-    for d in ce.include_paths() + [sysconfig.get_paths()["include"], "/usr/local/cuda/include"]:
+    for d in ce.include_paths() + [sysconfig.get_paths()["include"], os.path.join(CUDA_HOME, "include")]:
         inc += ["-isystem", d]
     defs = ["-DTORCH_EXTENSION_NAME=flash_gaussian_splatting", "-DTORCH_API_INCLUDE_EXTENSION_H",
             "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
@@ -68,7 +80,7 @@ def build_reference(ref_root: str = "/root/reference", force: bool = False):
     o = os.path.join(REF_DIR, "pybind.o")
     subprocess.check_call([CXX, "-c", binding, "-o", o, "-g", "-O1", "-std=c++17", "-fPIC"] + defs + inc)
     objs.append(o)
-    libdirs = ce.library_paths() + ["/usr/local/cuda/lib64"]
+    libdirs = ce.library_paths() + [os.path.join(CUDA_HOME, "lib64")]
     link = [CXX, "-shared", "-o", REF_SO] + objs
     for d in libdirs:
         link += ["-L" + d, "-Wl,-rpath," + d]

@@ -26,9 +26,15 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, n), "missing export " + n
         assert n in _lib.SIGNATURES, "no ctypes prototype for " + n
     hooks = _declared_symbols("flashgs_b200_test.h")      # the test-only switches have a header of their own
-    assert sorted(hooks) == sorted(_lib.TEST_HOOKS)
-    for n in hooks:
+    assert sorted(hooks) == sorted(_lib.TEST_HOOKS + _lib.CHECKED_HOOKS)
+    for n in _lib.TEST_HOOKS:
         assert hasattr(lib, n), "missing export " + n
+    for n in _lib.CHECKED_HOOKS:       # the checked flavour's own exports are not in the product library
+        assert not hasattr(lib, n), n
+    if os.path.exists(_lib.LIB_CHECKED_PATH):
+        checked = C.CDLL(_lib.LIB_CHECKED_PATH)
+        for n in names + list(_lib.TEST_HOOKS + _lib.CHECKED_HOOKS):
+            assert hasattr(checked, n), "checked flavour: missing export " + n
     assert lib.fgs_abi_version() == 2
     assert _lib.status_string(0) == "ok"
     assert "overflow" in _lib.status_string(_lib.ERR_PAIR_OVERFLOW)
@@ -92,3 +98,23 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(ImportError, match="no CPU fallback"):
         _lib.load()
+
+
+def test_integration_shim_compiles_against_the_reference_header(tmp_path):
+    """The C++ binding shown in INTEGRATION.md (the reference's operators implemented on top of this library's C ABI)
+    is real code: it compiles against the reference's csrc/ops.h where a checkout of the reference is present."""
+    import shutil
+    import subprocess
+    from oracle import build as oracle_build
+    ops_h = os.path.join(oracle_build.REFERENCE_ROOT, "csrc", "ops.h")
+    cuda_inc = os.path.join(oracle_build.CUDA_HOME, "include")
+    if not (os.path.exists(ops_h) and os.path.exists(os.path.join(cuda_inc, "cuda_runtime.h")) and shutil.which(oracle_build.CXX)):
+        pytest.skip("needs the reference checkout, the CUDA headers and a C++ compiler")
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    code = re.search(r"```cpp\n(.*?)```", text, flags=re.S).group(1)
+    assert "namespace flashgs" in code and "fgs_preprocess(" in code and "fgs_sort_pairs(" in code and "fgs_render_16x16(" in code
+    src = tmp_path / "ops_b200.cpp"
+    src.write_text(code)
+    r = subprocess.run([oracle_build.CXX, "-std=c++17", "-fsyntax-only", "-Wall", "-I", os.path.dirname(ops_h),
+                        "-I", os.path.join(ROOT, "include"), "-I", cuda_inc, str(src)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]

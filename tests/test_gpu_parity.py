@@ -52,6 +52,8 @@ class Frame:
         extra = {} if rows is None else dict(tile_row_begin=rows[0], tile_row_end=rows[1])
         if cull:   # scratch for the index list of the Gaussians that reach the strip; its contents do not matter
             extra["cull_scratch"] = torch.full((P + 1,), 0x7F7F7F7F, device=DEV, dtype=torch.int32)
+            if cull == "bounds":   # ... found from the 16-byte records prepared once per scene
+                extra["scene_bounds"] = ops.prepare_scene(self.pos, self.opa, self.cov)
         ops.preprocess(self.pos, self.shs, self.opa, self.cov, cam.width, cam.height, bx, by, self.cpos, self.crot,
                        cam.focal_x, cam.focal_y, cam.zFar, cam.zNear, self.xy, self.rd, self.co,
                        self.ku, self.vu, self.off, **extra)
@@ -452,7 +454,8 @@ def test_bounded_lookback_wait_reports_timeout(ops):
     assert (torch.sort(ki, stable=True)[0] == ko).all()
 
 
-@pytest.mark.parametrize("name,n,strips,cull", [("C1", 60000, 3, False), ("C1", 60000, 3, True), ("C4", 200000, 8, True)])
+@pytest.mark.parametrize("name,n,strips,cull", [("C1", 60000, 3, False), ("C1", 60000, 3, True), ("C4", 200000, 8, True),
+                                                ("C1", 60000, 3, "bounds"), ("C4", 200000, 8, "bounds"), ("C3", 150000, 5, "bounds")])
 def test_strips_union_equals_frame(ops, name, n, strips, cull):
     """One frame split into strips of tile rows: the strips' pairs together are the frame's pairs, and the strips'
     pixels are the frame's pixels -- with and without the index list of the Gaussians that reach a strip."""
@@ -632,4 +635,74 @@ def test_fused_frame_equals_stage_calls(ops, oracle_lib):
     torch.cuda.synchronize()
     assert int(small.curr_offset.cpu()[0]) > 4096
     assert ops.device_status() & _lib.ERR_PAIR_OVERFLOW
+    assert ops.device_status() == 0
+
+
+def test_reference_example_script_runs_unchanged(tmp_path):
+    """The reference's own example.py (placed beside the reference build by oracle/build.py, byte for byte the
+    reference's file), run as a script in a fresh interpreter with this repository first on the module path: its
+    ``import flash_gaussian_splatting`` resolves to the drop-in package, and the PPM files it writes are the ones this
+    repository's own driver writes."""
+    import hashlib
+    import json
+    import os
+    import subprocess
+    import sys
+    from flashgs_b200 import ply, render_scene
+    from oracle import build as oracle_build
+    script = oracle_build.REF_EXAMPLE
+    if not os.path.exists(script):
+        pytest.skip("the reference's example.py is not present beside the reference build")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    rng = np.random.default_rng(34)
+    n = 30000
+    d = tmp_path / "model"
+    (d / "point_cloud" / "iteration_30000").mkdir(parents=True)
+    ply.save_ply(str(d / "point_cloud" / "iteration_30000" / "point_cloud.ply"), rng.normal(size=(n, 3)) * 2.0,
+                 rng.normal(size=(n, 3)) * 0.5, rng.normal(size=(n, 45)) * 0.05, rng.normal(size=n) * 2.0,
+                 rng.normal(size=(n, 3)) * 0.8 - 4.0, rng.normal(size=(n, 4)))
+    cams = [scenes.look_at_camera(400, 304, 9.0, 60.0, az, 10.0, cam_id=i) for i, az in enumerate((0.0, 120.0, 240.0))]
+    (d / "cameras.json").write_text(json.dumps([render_scene.camera_to_json(c) for c in cams]))
+    code = ("import sys, runpy\n"
+            "sys.path.insert(0, %r)\n"
+            "sys.argv = [%r, %r]\n"
+            "runpy.run_path(%r, run_name='__main__')\n"
+            "import flash_gaussian_splatting, flashgs_b200.ops\n"
+            "assert flash_gaussian_splatting.ops is flashgs_b200.ops\n" % (root, script, str(d), script))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-3000:]
+    assert "num_vertex = %d" % n in r.stdout and "fps = " in r.stdout
+    theirs = {c.img_name: (d / "test_out" / (c.img_name + ".ppm")).read_bytes() for c in cams}
+    for c in cams:
+        os.remove(str(d / "test_out" / (c.img_name + ".ppm")))
+    render_scene.render_scene(str(d), max_num_rendered=1 << 22, max_num_tiles=1 << 12)
+    for c in cams:
+        mine = (d / "test_out" / (c.img_name + ".ppm")).read_bytes()
+        assert mine.startswith(b"P6\n400 304\n255\n")
+        assert hashlib.sha256(mine).digest() == hashlib.sha256(theirs[c.img_name]).digest(), c.img_name
+
+
+def test_view_batch_views_match_oracle(ops, oracle_lib):
+    """Views of the 64-view workload (a circle of cameras at 15 degrees elevation around one scene) at reduced size:
+    the views a rank renders one after the other with one set of buffers are each the oracle's image of that view."""
+    from flashgs_b200 import parallel
+    from flashgs_b200.rasterizer import DeviceScene, Rasterizer, TorchCamera
+    w = scenes.WORKLOADS["C5"]
+    sc = scenes.make_scene(60000, w.clusters, w.log_scale, seed=w.seed)
+    all_cams = scenes.make_cameras(w)
+    assert len(all_cams) == 64
+    mine = parallel.views_of_rank(len(all_cams), 8, 3)       # the views of rank 3 of 8
+    assert mine == list(range(3, 64, 8))
+    ds = DeviceScene(sc, DEV)
+    ras = Rasterizer(ds, 1 << 22, 1 << 14)
+    img = torch.zeros((270, 480, 3), device=DEV, dtype=torch.int8)
+    for v in mine[:3]:
+        full = all_cams[v]
+        cam = scenes.look_at_camera(480, 270, w.radius, w.hfov_deg, w.azimuth_deg + 360.0 * v / w.views, w.elevation_deg, cam_id=v)
+        assert np.allclose(cam.position, full.position) and np.allclose(cam.rotation, full.rotation)
+        ras.forward(ds, TorchCamera(cam), torch.zeros(3), out_color=img)
+        want = oracle_lib.render_frame(sc, cam, floats=False)
+        assert ras.num_rendered == int(want["counters"][3])
+        d = np.abs(img.cpu().numpy().view(np.uint8).astype(int) - want["u8"].astype(int))
+        assert d.max() <= 1 and (d > 0).mean() <= 1e-3
     assert ops.device_status() == 0

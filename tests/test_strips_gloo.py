@@ -83,3 +83,48 @@ def test_balanced_strips_follow_cost():
     assert max(sums) <= 1.5 * (sum(cost) / 4)
     assert all(b > a for a, b in parallel.balanced_strip_rows([0.0] * 8, 8))
     assert parallel.strip_pixel_rows((60, 68), 16, 1080) == (960, 1080)
+
+
+def _host_frames_worker(rank, world, port, out_path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        H, W = 96, 40
+        rows = [parallel.strip_rows(H // 16, world, r) for r in range(world)]
+        y0, y1 = parallel.strip_pixel_rows(rows[rank], 16, H)
+        ring = parallel.HostFrames(2, H, W, register=False, timeout_s=20.0)
+        ok = True
+        for k in range(6):
+            ring.wait_consumed(k - 2)                       # image k % 2 is free again
+            ring.images[k % 2][y0:y1] = (10 * k + rank) % 100   # this rank's strip of frame k
+            ring.publish(k)
+            if rank == 0:
+                ring.wait_produced(k)
+                img = ring.images[k % 2].numpy()
+                for r, rr in enumerate(rows):
+                    a, b = parallel.strip_pixel_rows(rr, 16, H)
+                    ok = ok and bool((img[a:b] == (10 * k + r) % 100).all())
+                ring.consume(k)
+        # a frame that one rank never delivers: the consumer's wait runs out instead of spinning for ever
+        timed_out = False
+        if rank == 0:
+            ring.timeout_s = 0.3
+            try:
+                ring.wait_produced(99)
+            except TimeoutError:
+                timed_out = True
+        ring.close()
+        if rank == 0:
+            with open(out_path, "w") as f:
+                f.write("ok" if ok and timed_out else "bad ok=%s timeout=%s" % (ok, timed_out))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_host_frame_ring_two_ranks(tmp_path):
+    """Every rank writes the rows of its own strip into a host image shared by all ranks; the consumer sees whole
+    frames, the ring's images are reused only after their release, and a missing strip ends the wait with an error."""
+    out = tmp_path / "ring.txt"
+    mp.spawn(_host_frames_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
+    assert out.read_text() == "ok"
