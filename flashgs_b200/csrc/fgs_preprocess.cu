@@ -401,8 +401,17 @@ preprocess_kernel(int P,
         if (tid < n_here) {
 #pragma unroll
             for (int q = 0; q < 3; q++) s_pos[3 * tid + q] = __ldg(positions + 3 * (size_t)i + q);
+            if (VEC) {   // a covariance row is 24 bytes: 8-byte aligned whenever the array is
+                const float2* c2 = reinterpret_cast<const float2*>(cov3ds + 6 * (size_t)i);
 #pragma unroll
-            for (int q = 0; q < 6; q++) s_cov[6 * tid + q] = __ldg(cov3ds + 6 * (size_t)i + q);
+                for (int q = 0; q < 3; q++) {
+                    const float2 v = __ldg(c2 + q);
+                    s_cov[6 * tid + 2 * q] = v.x; s_cov[6 * tid + 2 * q + 1] = v.y;
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 6; q++) s_cov[6 * tid + q] = __ldg(cov3ds + 6 * (size_t)i + q);
+            }
             s_opa[tid] = __ldg(opacities + i);
         }
     } else if (VEC) {
