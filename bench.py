@@ -226,6 +226,8 @@ def main():
                     help="only the view batch: all views of the workload (C5: 64), dealt out to the ranks")
     ap.add_argument("--view-passes", type=int, default=2)
     ap.add_argument("--view-gaussians", type=int, default=None, help="override the view batch's Gaussian count")
+    ap.add_argument("--no-tile-counts", action="store_true",
+                    help="the sort counts the pairs per tile itself (one more pass over the keys) instead of taking preprocess's table")
     ap.add_argument("--no-scene-bounds", action="store_true",
                     help="the index list of the Gaussians that reach the image is found from the scene arrays (40 bytes per "
                          "Gaussian) instead of from records prepared once per scene (16 bytes)")
@@ -310,12 +312,17 @@ def main():
         ras.cull_scratch = ras.scene_bounds = None
     if args.no_scene_bounds:
         ras.scene_bounds = None
+    if args.no_tile_counts or not ours:
+        ras.tile_counts = None
     use_scratch = ours and ras.cull_scratch is not None
     use_bounds = use_scratch and ras.scene_bounds is not None
+    use_counts = ours and ras.tile_counts is not None
     config["preprocess_call"] = ("the reference's positional arguments plus cull_scratch= (the idle head of the sort's "
                                  "scratch, for the index list of the Gaussians that reach the image)"
                                  + (" and scene_bounds= (16-byte records prepared once per scene, outside the timed region, "
                                     "from which that list is found)" if use_bounds else "")
+                                 + (" and tile_counts= (preprocess counts the pairs per tile as it emits them; sort_gaussian is "
+                                    "given the table and does not count them again)" if use_counts else "")
                                  + "; stages.preprocess.preprocess_plain_call_ms is the call without them") if use_scratch else \
         "the reference's positional arguments only"
     H, W = cam.height, cam.width
@@ -326,17 +333,24 @@ def main():
     def stage_pre(rows=None, scratch=True):
         ras.curr_offset.fill_(0)
         extra = {} if rows is None else dict(tile_row_begin=rows[0], tile_row_end=rows[1])
+        if not scratch:   # the reference's positional call (plus the strip's rows)
+            return ops.preprocess(ds.position, ds.shs, ds.opacity, ds.cov3d, W, H, 16, 16, tc.position, tc.rotation,
+                                  tc.focal_x, tc.focal_y, tc.zFar, tc.zNear, ras.points_xy, ras.rgb_depth, ras.conic_opacity,
+                                  ras.gaussian_keys_unsorted, ras.gaussian_values_unsorted, ras.curr_offset, **extra)
         if use_scratch and scratch:
             extra["cull_scratch"] = ras.cull_scratch   # the head of the sort's scratch, idle at this point
             if use_bounds:
                 extra["scene_bounds"] = ras.scene_bounds
+        if use_counts:
+            extra["tile_counts"] = ras.tile_counts
         ops.preprocess(ds.position, ds.shs, ds.opacity, ds.cov3d, W, H, 16, 16, tc.position, tc.rotation,
                        tc.focal_x, tc.focal_y, tc.zFar, tc.zNear, ras.points_xy, ras.rgb_depth, ras.conic_opacity,
                        ras.gaussian_keys_unsorted, ras.gaussian_values_unsorted, ras.curr_offset, **extra)
 
     def stage_sort(n):
+        extra = {"tile_counts": ras.tile_counts} if use_counts else {}
         ops.sort_gaussian(n, W, H, 16, 16, ras.list_sorting_space, ras.gaussian_keys_unsorted, ras.gaussian_values_unsorted,
-                          ras.gaussian_keys_sorted, ras.gaussian_values_sorted)
+                          ras.gaussian_keys_sorted, ras.gaussian_values_sorted, **extra)
 
     def stage_render(n, rows=None, img=None):
         img = out_img if img is None else img
@@ -546,7 +560,8 @@ def main():
                                           ras.curr_offset.data_ptr(),
                                           ras.cull_scratch.data_ptr() if use_scratch else None,
                                           ras.cull_scratch.numel() if use_scratch else 0,
-                                          ras.scene_bounds.data_ptr() if use_bounds else None, stream, ms2)
+                                          ras.scene_bounds.data_ptr() if use_bounds else None,
+                                          ras.tile_counts.data_ptr() if use_counts else None, stream, ms2)
             _lib.check("fgs_preprocess_profile", st)
             pre_k.append([ms2[0], ms2[1]])
         cull_ms, main_ms = [float(x) for x in np.median(np.array(pre_k), axis=0)]
@@ -571,7 +586,7 @@ def main():
             st = L.fgs_sort_pairs_profile(n, W, H, 16, 16, ras.list_sorting_space.data_ptr(), ras.list_sorting_space.numel(),
                                           ras.gaussian_keys_unsorted.data_ptr(), ras.gaussian_values_unsorted.data_ptr(),
                                           ras.gaussian_keys_sorted.data_ptr(), ras.gaussian_values_sorted.data_ptr(),
-                                          stream, ms, kinds, CAPN, C.byref(nl))
+                                          ras.tile_counts.data_ptr() if use_counts else None, stream, ms, kinds, CAPN, C.byref(nl))
             _lib.check("fgs_sort_pairs_profile", st)
             per.append([ms[i] for i in range(nl.value)])
         per = np.median(np.array(per), axis=0) if nl.value else np.zeros(0)
@@ -605,7 +620,8 @@ def main():
         hbm("preprocess_kernel", main_ms, 1, bytes_main)
         names = {0: "tile_hist_kernel", 1: "multisplit_kernel", 2: "tile_scan_kernel", 3: "local_sort_kernel + long_list_kernel"}
         hist_ms, pass_ms, seg_ms, local_ms = sum(by_kind(0)), by_kind(1), sum(by_kind(2)), sum(by_kind(3))
-        hbm(names[0], hist_ms, len(by_kind(0)), 8 * R)
+        if by_kind(0):
+            hbm(names[0], hist_ms, len(by_kind(0)), 8 * R)
         mean_pass = float(np.mean(pass_ms)) if pass_ms else 0.0
         hbm(names[1], mean_pass, len(pass_ms), 24 * R, "mean of the passes: " + ", ".join("%.3f" % x for x in pass_ms))
         hbm(names[2], seg_ms, len(by_kind(2)), 16 * 32768, "one block; bound by its own latency, not by HBM")

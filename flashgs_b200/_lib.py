@@ -11,6 +11,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("FLASHGS_B200_LIB") or os.path.join(HERE, "libflashgs_b200.so")
 
+TILE_COUNT_WORDS = 65536   # FGS_TILE_COUNT_WORDS
 OK, ERR_BAD_ARG, ERR_CUDA, ERR_PAIR_OVERFLOW, ERR_LOOKBACK_TIMEOUT, ERR_TEMP_TOO_SMALL = 0, 1, 2, 4, 8, 16
 
 _p = C.c_void_p
@@ -32,15 +33,16 @@ SIGNATURES = {
                                          _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p]),
     "fgs_scene_bounds": (_i, [_i, _p, _p, _p, _p, _p]),
     "fgs_preprocess_prepared": (_i, [_i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _f, _f, _f, _f, _i, _i,
-                                     _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p, _p]),
+                                     _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p, _p, _p]),
     "fgs_preprocess_profile": (_i, [_i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _f, _f, _f, _f, _i, _i,
-                                    _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p, _p, _p]),
+                                    _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _p, _p, _p, _p]),
     "fgs_sort_temp_bytes": (C.c_size_t, [_i64]),
     "fgs_sort_pairs": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p]),
     "fgs_sort_pairs_stable": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p]),
+    "fgs_sort_pairs_counted": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p, _p]),
     "fgs_sort_static_max_pairs": (_i, []),
     "fgs_sort_pairs_static": (_i, [_i, _i, _i, _i, _i, _p, _p, _p, _p, _p]),
-    "fgs_sort_pairs_profile": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p, _p, _p, _i, _p]),
+    "fgs_sort_pairs_profile": (_i, [_i, _i, _i, _i, _i, _p, C.c_size_t, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p]),
     "fgs_render_16x16": (_i, [_i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]),
     "fgs_render_32x16": (_i, [_i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]),
     "fgs_render_32x32": (_i, [_i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]),

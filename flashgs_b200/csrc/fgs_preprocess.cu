@@ -352,10 +352,6 @@ __device__ unsigned long long g_pre_cycles[8];
 #define FGS_PT(i) do { } while (0)
 #endif
 
-#ifdef FGS_EXP_TILE_COUNT_IN_PRE
-__device__ unsigned g_exp_tile_count[65536];
-#endif
-
 template <bool VEC>
 __global__ void __launch_bounds__(PRE_THREADS, PRE_BLOCKS_PER_SM)
 preprocess_kernel(int P,
@@ -364,7 +360,8 @@ preprocess_kernel(int P,
                   const __grid_constant__ PreCam cam,
                   float2* __restrict__ points_xy, float4* __restrict__ rgb_depth, float4* __restrict__ conic_opacity,
                   uint64_t* __restrict__ keys, uint32_t* __restrict__ values, long long capacity,
-                  int* __restrict__ curr_offset, int* __restrict__ status, const int* __restrict__ list)
+                  int* __restrict__ curr_offset, int* __restrict__ status, const int* __restrict__ list,
+                  unsigned* __restrict__ tile_count)
 {
     __shared__ __align__(16) float s_pos[PRE_THREADS * 3];
     __shared__ __align__(16) float s_cov[PRE_THREADS * 6];
@@ -537,9 +534,7 @@ preprocess_kernel(int P,
             if (o >= 0 && o < capacity) {
                 keys[o] = ((uint64_t)e.x << 32) | (uint32_t)s_rect[e.y].w;
                 values[o] = (uint32_t)s_idx[e.y];
-#ifdef FGS_EXP_TILE_COUNT_IN_PRE
-                atomicAdd(&g_exp_tile_count[e.x & 0xFFFFu], 1u);   // experiment: what per-tile counting costs here
-#endif
+                if (tile_count != nullptr) atomicAdd(tile_count + e.x, 1u);   // pairs per tile, for the sort that follows
             } else {
                 atomicOr(status, FGS_ERR_PAIR_OVERFLOW);
             }
@@ -727,7 +722,7 @@ static int preprocess_impl(int P, const float* positions, const float* shs, cons
                            float* points_xy, float* rgb_depth, float* conic_opacity,
                            uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
                            int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints, void* stream, cudaEvent_t* events,
-                           const float* scene_bounds = nullptr)
+                           const float* scene_bounds = nullptr, uint32_t* tile_counts = nullptr)
 {
     if (P < 0 || width <= 0 || height <= 0 || block_x <= 0 || block_y <= 0 || pair_capacity < 0) return FGS_ERR_BAD_ARG;
     if (cull_scratch != nullptr && cull_scratch_ints < (int64_t)P + 1) return FGS_ERR_TEMP_TOO_SMALL;
@@ -759,6 +754,10 @@ static int preprocess_impl(int P, const float* positions, const float* shs, cons
     // With scratch for the index list: first the cheap pass that lists the Gaussians reaching the rendered rows and
     // the image's columns (for a whole frame too: about a third of the scene lies outside the image).
     const int* list = nullptr;
+    // pairs per tile for the sort: only images whose tile ids the tile-bucketed sort takes (see fgs_sort_pairs_counted)
+    if (tile_counts != nullptr && (int64_t)cam.grid_x * cam.grid_y >= FGS_TILE_COUNT_WORDS) tile_counts = nullptr;
+    if (tile_counts != nullptr && cudaMemsetAsync(tile_counts, 0, sizeof(uint32_t) * FGS_TILE_COUNT_WORDS, st) != cudaSuccess)
+        return FGS_ERR_CUDA;
     if (events) cudaEventRecord(events[0], st);
     if (cull_scratch != nullptr) {
         if (cudaMemsetAsync(cull_scratch, 0, sizeof(int), st) != cudaSuccess) return FGS_ERR_CUDA;
@@ -772,11 +771,11 @@ static int preprocess_impl(int P, const float* positions, const float* shs, cons
     if (vec)
         preprocess_kernel<true><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,
             reinterpret_cast<float2*>(points_xy), reinterpret_cast<float4*>(rgb_depth), reinterpret_cast<float4*>(conic_opacity),
-            keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status, list);
+            keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status, list, tile_counts);
     else
         preprocess_kernel<false><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,
             reinterpret_cast<float2*>(points_xy), reinterpret_cast<float4*>(rgb_depth), reinterpret_cast<float4*>(conic_opacity),
-            keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status, list);
+            keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status, list, tile_counts);
     if (events) cudaEventRecord(events[2], st);
     return launch_status();
 }
@@ -814,13 +813,13 @@ extern "C" int fgs_preprocess_prepared(int P, const float* positions, const floa
                                        float* points_xy, float* rgb_depth, float* conic_opacity,
                                        uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
                                        int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints,
-                                       const float* scene_bounds, void* stream)
+                                       const float* scene_bounds, uint32_t* tile_counts, void* stream)
 {
     if (scene_bounds != nullptr && (cull_scratch == nullptr || !fgs::aligned16(scene_bounds))) return FGS_ERR_BAD_ARG;
     return fgs::preprocess_impl(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y, cam_position, cam_rotation,
                                 focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end, points_xy, rgb_depth, conic_opacity,
                                 keys_unsorted, values_unsorted, pair_capacity, curr_offset, cull_scratch, cull_scratch_ints, stream, nullptr,
-                                scene_bounds);
+                                scene_bounds, tile_counts);
 }
 
 extern "C" int fgs_preprocess_profile(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
@@ -831,7 +830,7 @@ extern "C" int fgs_preprocess_profile(int P, const float* positions, const float
                                       float* points_xy, float* rgb_depth, float* conic_opacity,
                                       uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
                                       int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints,
-                                      const float* scene_bounds, void* stream, float* kernel_ms2)
+                                      const float* scene_bounds, uint32_t* tile_counts, void* stream, float* kernel_ms2)
 {
     if (!kernel_ms2) return FGS_ERR_BAD_ARG;
     cudaEvent_t ev[3];
@@ -840,7 +839,7 @@ extern "C" int fgs_preprocess_profile(int P, const float* positions, const float
     int st = fgs::preprocess_impl(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y, cam_position, cam_rotation,
                                   focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end, points_xy, rgb_depth, conic_opacity,
                                   keys_unsorted, values_unsorted, pair_capacity, curr_offset, cull_scratch, cull_scratch_ints, stream, ev,
-                                  scene_bounds);
+                                  scene_bounds, tile_counts);
     kernel_ms2[0] = kernel_ms2[1] = 0.0f;
     if (st == FGS_OK && P > 0) {
         if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) st = FGS_ERR_CUDA;

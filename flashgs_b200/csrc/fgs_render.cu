@@ -338,8 +338,19 @@ int launch_render(int num_rendered, int width, int height,
 
 int sort_pairs_device_count(int capacity, const int* n_dev, int width, int height, int block_x, int block_y,
                             void* temp, size_t temp_bytes, const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
-                            uint64_t* keys_sorted, uint32_t* values_sorted, void* stream);
+                            uint64_t* keys_sorted, uint32_t* values_sorted, void* stream, bool counts_in_scratch);
+void sort_scratch_regions(int64_t capacity, size_t* tile_count_off, size_t* list_off, size_t* list_bytes);
 } // namespace fgs
+
+extern "C" int fgs_preprocess_prepared(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
+                                       int width, int height, int block_x, int block_y,
+                                       const float* cam_position, const float* cam_rotation,
+                                       float focal_x, float focal_y, float zFar, float zNear,
+                                       int tile_row_begin, int tile_row_end,
+                                       float* points_xy, float* rgb_depth, float* conic_opacity,
+                                       uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
+                                       int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints,
+                                       const float* scene_bounds, uint32_t* tile_counts, void* stream);
 
 FGS_BOUNDS_REPORT_FN(fgs_debug_bounds_render)
 
@@ -376,17 +387,27 @@ extern "C" int fgs_render_frame(int P, const float* positions, const float* shs,
     if (pair_capacity <= 0 || pair_capacity >= (1 << 30) || !curr_offset || !out_color || !bg_color || !ranges) return FGS_ERR_BAD_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (cudaMemsetAsync(curr_offset, 0, sizeof(int), st) != cudaSuccess) return FGS_ERR_CUDA;
-    // The sort's scratch is idle while preprocess runs: its first P + 1 ints hold the list of the Gaussians that can
-    // reach the image (or the strip); the sort clears its bookkeeping itself before it starts.
-    int* cull_list = (sort_temp != nullptr && aligned16(sort_temp) && sort_temp_bytes >= ((size_t)P + 1) * sizeof(int))
-                         ? static_cast<int*>(sort_temp) : nullptr;
-    int rc = fgs_preprocess_strip_culled(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y, cam_position,
-                                         cam_rotation, focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end, points_xy,
-                                         rgb_depth, conic_opacity, keys_unsorted, values_unsorted, pair_capacity, curr_offset,
-                                         cull_list, cull_list ? (int64_t)P + 1 : 0, stream);
+    // The sort's scratch is idle while preprocess runs. Preprocess leaves two things in it: the list of the Gaussians
+    // that can reach the image (or the strip), in the alternate value buffer at the scratch's end, and the pairs per
+    // tile, in the sort's own table -- the sort then starts from that table instead of counting the pairs again.
+    int* cull_list = nullptr;
+    uint32_t* tile_counts = nullptr;
+    if (sort_temp != nullptr && aligned16(sort_temp) && sort_temp_bytes >= fgs_sort_temp_bytes(pair_capacity)) {
+        size_t count_off = 0, list_off = 0, list_bytes = 0;
+        sort_scratch_regions(pair_capacity, &count_off, &list_off, &list_bytes);
+        if (list_bytes >= ((size_t)P + 1) * sizeof(int)) cull_list = reinterpret_cast<int*>(static_cast<char*>(sort_temp) + list_off);
+        const int64_t tiles = (block_x > 0 && block_y > 0 && width > 0 && height > 0)
+                                  ? (int64_t)((width + block_x - 1) / block_x) * ((height + block_y - 1) / block_y) : FGS_TILE_COUNT_WORDS;
+        if (tiles < FGS_TILE_COUNT_WORDS)
+            tile_counts = reinterpret_cast<uint32_t*>(static_cast<char*>(sort_temp) + count_off);
+    }
+    int rc = fgs_preprocess_prepared(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y, cam_position,
+                                     cam_rotation, focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end, points_xy,
+                                     rgb_depth, conic_opacity, keys_unsorted, values_unsorted, pair_capacity, curr_offset,
+                                     cull_list, cull_list ? (int64_t)P + 1 : 0, nullptr, tile_counts, stream);
     if (rc != FGS_OK) return rc;
     rc = sort_pairs_device_count((int)pair_capacity, curr_offset, width, height, block_x, block_y, sort_temp, sort_temp_bytes,
-                                 keys_unsorted, values_unsorted, keys_sorted, values_sorted, stream);
+                                 keys_unsorted, values_unsorted, keys_sorted, values_sorted, stream, tile_counts != nullptr);
     if (rc != FGS_OK) return rc;
 #define FGS_FRAME_CASE(BX, BY)                                                                                          \
     if (block_x == BX && block_y == BY)                                                                                 \

@@ -139,14 +139,15 @@ __device__ __forceinline__ int device_count(int n, const int* n_dev)
 // Clears the ticket counters, flags, digit counts and the look-back words of the partitions a sort of the
 // device-side count uses (the host-count path uses a memset of exactly that region instead).
 __global__ void clear_bookkeeping_kernel(uint32_t* __restrict__ base_words, size_t head_words, uint32_t* __restrict__ status_words,
-                                         int slots, int parts_stride, int n, const int* __restrict__ n_dev)
+                                         int slots, int parts_stride, int n, const int* __restrict__ n_dev,
+                                         size_t keep_begin, size_t keep_end)
 {
     n = device_count(n, n_dev);
     const int parts = (n + SORT_PART - 1) / SORT_PART;
     const size_t per_slot = (size_t)parts * RADIX;
     const size_t total = head_words + (size_t)slots * per_slot;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        if (i < head_words) base_words[i] = 0;
+        if (i < head_words) { if (i < keep_begin || i >= keep_end) base_words[i] = 0; }   // [keep_begin, keep_end): counts an earlier kernel left
         else {
             const size_t j = i - head_words;
             const size_t slot = j / per_slot;
@@ -636,7 +637,10 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
 #define FGS_MS_ITEMS 16
 #endif
 #ifndef FGS_MS_LATE_VALUES
-#define FGS_MS_LATE_VALUES 0   // 1: read a partition's values after the ranking instead of with its keys
+#define FGS_MS_LATE_VALUES 1   // 1: read a partition's values after the ranking instead of with its keys
+#endif
+#ifndef FGS_MS_AGGREGATE
+#define FGS_MS_AGGREGATE 0     // 1: lanes with equal digits add to the block's counter as one group
 #endif
 constexpr int MS_THREADS = 256;                       // thread d owns digit value d (at most 8 bits per pass)
 constexpr int MS_ITEMS = FGS_MS_ITEMS;
@@ -647,6 +651,7 @@ constexpr int TILE_HIST_THREADS = 1024;
 constexpr int TILE_HIST_SMEM_VALUES = 49152;          // tile values whose counters fit one block's shared memory
 constexpr int TILE_SCAN_THREADS = 1024;
 static_assert(MS_THREADS == MAX_BUCKETS, "a pass has at most as many digit values as the block has threads");
+static_assert((MS_THREADS / 32) * 2 * MS_THREADS * 4 <= MS_SMEM_BYTES, "the warps' mask words fit the reorder buffer");
 
 // Pairs per tile value, added to tile_count[] (zero on entry). With `in_smem` a block counts into shared memory
 // (tile_values * 4 bytes of dynamic shared memory) and adds its non-zero counters to the global ones at the end;
@@ -701,7 +706,8 @@ __device__ __forceinline__ int scan_pad(int i) { return i + (i >> 5); }   // con
 __global__ void __launch_bounds__(TILE_SCAN_THREADS, 1)
 tile_scan_kernel(const uint32_t* __restrict__ tile_count, int tile_values, int lo_bits,
                  int2* __restrict__ seg, uint32_t* __restrict__ cursor, uint32_t* __restrict__ bucket_tables,
-                 int* __restrict__ class_count, uint32_t* __restrict__ class_tiles)
+                 int* __restrict__ class_count, uint32_t* __restrict__ class_tiles,
+                 int n_pairs, const int* __restrict__ n_dev, int* __restrict__ dev_status)
 {
     constexpr int WARPS = TILE_SCAN_THREADS / 32;
     extern __shared__ __align__(16) uint32_t s_pref[];          // counts, then exclusive prefixes (padded), one round
@@ -719,7 +725,19 @@ tile_scan_kernel(const uint32_t* __restrict__ tile_count, int tile_values, int l
     for (int lo = 0; lo < tile_values; lo += SCAN_ROUND) {
         const int n = min(SCAN_ROUND, tile_values - lo);
         __syncthreads();   // the previous round's shared memory is no longer read
-        for (int i = tid; i < n; i += TILE_SCAN_THREADS) s_pref[scan_pad(i)] = tile_count[lo + i];
+        for (int b = 0; b < n; b += 8 * TILE_SCAN_THREADS) {   // eight independent loads in flight per thread
+            uint32_t v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int i = b + u * TILE_SCAN_THREADS + tid;
+                v[u] = i < n ? tile_count[lo + i] : 0u;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int i = b + u * TILE_SCAN_THREADS + tid;
+                if (i < n) s_pref[scan_pad(i)] = v[u];
+            }
+        }
         __syncthreads();
         // exclusive scan: a thread owns `per` consecutive tiles
         const int per = (n + TILE_SCAN_THREADS - 1) / TILE_SCAN_THREADS;
@@ -771,7 +789,11 @@ tile_scan_kernel(const uint32_t* __restrict__ tile_count, int tile_values, int l
         carry += total;
     }
     __syncthreads();
-    if (tid < LOCAL_CLASSES) class_count[tid] = (int)s_class[tid];
+    // The counts must add up to the number of pairs (they do when this sort counted them itself; a table handed in by
+    // the caller is checked here): otherwise nothing is moved -- no work for the passes, no lists for the tile sorts.
+    const bool consistent = carry == (uint32_t)device_count(n_pairs, n_dev);
+    if (!consistent && tid == 0) atomicOr(dev_status, FGS_ERR_BAD_ARG);
+    if (tid < LOCAL_CLASSES) class_count[tid] = consistent ? (int)s_class[tid] : 0;
     if (tid == 0) s_bucket_first[buckets] = carry;
     __syncthreads();
     // bucket tables: [0, B) cursors, [B, 2B+1) firsts, [2B+1, 3B+2) exclusive unit counts (+ their total)
@@ -782,9 +804,9 @@ tile_scan_kernel(const uint32_t* __restrict__ tile_count, int tile_values, int l
         uint32_t units = 0;
         if (tid < buckets) {
             const uint32_t first = s_bucket_first[tid], size = s_bucket_first[tid + 1] - first;
-            hi_cursor[tid] = first;
+            hi_cursor[tid] = consistent ? first : 0x80000000u;   // inconsistent counts: every destination falls outside the list
             bucket_first[tid] = first;
-            units = (size + MS_PART - 1) / MS_PART;
+            units = consistent ? (size + MS_PART - 1) / MS_PART : 0u;
         }
         uint32_t uinc = units;
 #pragma unroll
@@ -879,13 +901,45 @@ multisplit_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restri
     }
 #endif
     __syncthreads();
-    // place inside the digit's run: the arrival number of a shared-memory add (any order will do)
+    // place inside the digit's run (any order will do)
     uint32_t slot[MS_ITEMS];
+#if FGS_MS_AGGREGATE
+    // Neighbouring pairs often share their digit (a splat's tiles of one row lie in one coarse bucket), and 32 adds to
+    // one shared-memory word take 32 turns. The lanes that hold the same digit therefore meet first -- every lane ORs
+    // its bit into the warp's word of its digit and reads the word back -- and the lowest of them adds the whole
+    // group to the block's counter with ONE add. The words live in the reorder buffer, which is idle until the scan
+    // below is done; two sets are used in turn and the group's lowest lane clears its word after use.
+    {
+        const unsigned lt = lanemask_lt();
+        uint32_t* my_masks = reinterpret_cast<uint32_t*>(s_ms) + warp * (2 * MS_THREADS);
+#pragma unroll
+        for (int i = 0; i < 2 * MS_THREADS / 32; i++) my_masks[i * 32 + lane] = 0;
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < MS_ITEMS; i++) {
+            const bool ok = i * MS_THREADS + tid < count;
+            const uint32_t d = digit_of_key(key[i]);
+            volatile uint32_t* word = my_masks + (i & 1) * MS_THREADS + d;
+            if (ok) atomicOr(const_cast<uint32_t*>(word), 1u << lane);
+            __syncwarp();
+            const unsigned peers = ok ? *word : (1u << lane);
+            __syncwarp();
+            uint32_t pre = 0;
+            if (ok && (peers & lt) == 0) {
+                *word = 0;
+                pre = atomicAdd(&s_cnt[d], (uint32_t)__popc(peers));
+            }
+            pre = __shfl_sync(FULL_MASK, pre, __ffs(peers) - 1);
+            slot[i] = pre + __popc(peers & lt);
+        }
+    }
+#else
 #pragma unroll
     for (int i = 0; i < MS_ITEMS; i++) {
         const int j = i * MS_THREADS + tid;
         slot[i] = j < count ? atomicAdd(&s_cnt[digit_of_key(key[i])], 1u) : 0u;
     }
+#endif
     __syncthreads();
     // thread d: exclusive scan of the counts (start of digit d's run in the reordered partition), and the
     // reservation of the run's place at its destination
@@ -1488,8 +1542,10 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
                            const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
                            uint64_t* keys_sorted, uint32_t* values_sorted, void* stream,
                            cudaEvent_t* events, int* kinds, int* num_launches, const int* n_dev = nullptr,
-                           int order = ORDER_BY_VALUE)
+                           int order = ORDER_BY_VALUE, const uint32_t* given_counts = nullptr, bool counts_in_scratch = false)
 {
+    // given_counts: pairs per tile left by preprocess in a caller-owned table; counts_in_scratch: left in this
+    // scratch's own table (the frame entry point). Either way the pass that would count them is skipped.
     // With n_dev the count lives on the device (clamped to num_rendered, which is then the buffers' capacity).
     if (num_launches) *num_launches = 0;
     if (num_rendered < 0 || num_rendered >= (1 << 30) || width <= 0 || height <= 0 || block_x <= 0 || block_y <= 0)
@@ -1534,12 +1590,16 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
 
     // ticket counters and look-back regions in use: one per look-back digit pass (none on the wait-free path)
     const int slots = by_value ? 0 : (bucketed ? tile_passes : passes);
+    const bool have_counts = by_value && (given_counts != nullptr || counts_in_scratch);
     if (n_dev == nullptr) {
-        const size_t clear_bytes = L.status_off + (size_t)slots * L.parts * RADIX * 4;
+        // with counts from outside, the scratch's own table is not used: only what lies in front of it is cleared
+        const size_t clear_bytes = have_counts ? L.tilecnt_off : L.status_off + (size_t)slots * L.parts * RADIX * 4;
         if (cudaMemsetAsync(base, 0, clear_bytes, st) != cudaSuccess) return FGS_ERR_CUDA;
     } else {
+        const bool keep = have_counts && counts_in_scratch;
         clear_bookkeeping_kernel<<<sms * 8, 256, 0, st>>>(reinterpret_cast<uint32_t*>(base), L.status_off / 4, status_words,
-                                                          slots, L.parts, n, n_dev);
+                                                          slots, L.parts, n, n_dev,
+                                                          keep ? L.tilecnt_off / 4 : 0, keep ? L.status_off / 4 : 0);
     }
 
     int launches = 0;
@@ -1578,17 +1638,22 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
 
     if (by_value) {
         // ---- wait-free tile grouping, then tile sorts by (depth bits, value) ----
-        const int in_smem = tile_values <= TILE_HIST_SMEM_VALUES && n >= 4 * tile_values;
-        int hist_blocks = (int)(((int64_t)n + 65535) / 65536);
-        hist_blocks = hist_blocks < 1 ? 1 : (hist_blocks > sms ? sms : hist_blocks);
-        tile_hist_kernel<<<hist_blocks, TILE_HIST_THREADS, in_smem ? (size_t)tile_values * 4 : 0, st>>>(
-            keys_unsorted, n, n_dev, (uint32_t)tile_values - 1u, tile_values, in_smem, tile_count);
-        mark(LAUNCH_HISTOGRAM);
+        const uint32_t* counts = tile_count;
+        if (have_counts) {
+            if (given_counts != nullptr) counts = given_counts;
+        } else {
+            const int in_smem = tile_values <= TILE_HIST_SMEM_VALUES && n >= 4 * tile_values;
+            int hist_blocks = (int)(((int64_t)n + 65535) / 65536);
+            hist_blocks = hist_blocks < 1 ? 1 : (hist_blocks > sms ? sms : hist_blocks);
+            tile_hist_kernel<<<hist_blocks, TILE_HIST_THREADS, in_smem ? (size_t)tile_values * 4 : 0, st>>>(
+                keys_unsorted, n, n_dev, (uint32_t)tile_values - 1u, tile_values, in_smem, tile_count);
+            mark(LAUNCH_HISTOGRAM);
+        }
         // lower and upper halves of the tile bits: at most 8 bits each
         const int lo_bits = tile_bits <= RADIX_BITS ? tile_bits : tile_bits / 2;
         const int buckets = tile_values >> lo_bits;
-        tile_scan_kernel<<<1, TILE_SCAN_THREADS, SCAN_SMEM_BYTES, st>>>(tile_count, tile_values, lo_bits, seg, tile_cursor, bucket_tables,
-                                                          class_count, class_tiles);
+        tile_scan_kernel<<<1, TILE_SCAN_THREADS, SCAN_SMEM_BYTES, st>>>(counts, tile_values, lo_bits, seg, tile_cursor, bucket_tables,
+                                                          class_count, class_tiles, n, n_dev, dev_status);
         mark(LAUNCH_SEGMENTS);
         const int ms_parts = (int)(((int64_t)n + MS_PART - 1) / MS_PART);
         const uint64_t* src_k = keys_unsorted;
@@ -1678,11 +1743,22 @@ namespace fgs {
 // Sort whose pair count is the device counter *n_dev (at most `capacity`); used by the frame entry point.
 int sort_pairs_device_count(int capacity, const int* n_dev, int width, int height, int block_x, int block_y,
                             void* temp, size_t temp_bytes, const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
-                            uint64_t* keys_sorted, uint32_t* values_sorted, void* stream)
+                            uint64_t* keys_sorted, uint32_t* values_sorted, void* stream, bool counts_in_scratch)
 {
     if (!n_dev || capacity <= 0) return FGS_ERR_BAD_ARG;
     return sort_pairs_impl(capacity, width, height, block_x, block_y, temp, temp_bytes, keys_unsorted, values_unsorted,
-                           keys_sorted, values_sorted, stream, nullptr, nullptr, nullptr, n_dev);
+                           keys_sorted, values_sorted, stream, nullptr, nullptr, nullptr, n_dev, ORDER_BY_VALUE, nullptr,
+                           counts_in_scratch);
+}
+
+// Where the frame entry point may let preprocess leave its per-tile counts (inside the sort's scratch) and its index
+// list (the alternate value buffer at the scratch's end, which the sort does not touch before its second pass).
+void sort_scratch_regions(int64_t capacity, size_t* tile_count_off, size_t* list_off, size_t* list_bytes)
+{
+    const SortLayout L = make_layout(capacity);
+    *tile_count_off = L.tilecnt_off;
+    *list_off = L.alt_vals_off;
+    *list_bytes = L.total - L.alt_vals_off;
 }
 } // namespace fgs
 
@@ -1698,6 +1774,16 @@ extern "C" int fgs_sort_pairs(int num_rendered, int width, int height, int block
                                 values_unsorted, keys_sorted, values_sorted, stream, nullptr, nullptr, nullptr);
 }
 
+extern "C" int fgs_sort_pairs_counted(int num_rendered, int width, int height, int block_x, int block_y,
+                                      void* temp, size_t temp_bytes,
+                                      const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                                      uint64_t* keys_sorted, uint32_t* values_sorted, const uint32_t* tile_counts, void* stream)
+{
+    return fgs::sort_pairs_impl(num_rendered, width, height, block_x, block_y, temp, temp_bytes, keys_unsorted,
+                                values_unsorted, keys_sorted, values_sorted, stream, nullptr, nullptr, nullptr, nullptr,
+                                fgs::ORDER_BY_VALUE, tile_counts);
+}
+
 extern "C" int fgs_sort_pairs_stable(int num_rendered, int width, int height, int block_x, int block_y,
                                      void* temp, size_t temp_bytes,
                                      const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
@@ -1711,7 +1797,7 @@ extern "C" int fgs_sort_pairs_stable(int num_rendered, int width, int height, in
 extern "C" int fgs_sort_pairs_profile(int num_rendered, int width, int height, int block_x, int block_y,
                                       void* temp, size_t temp_bytes,
                                       const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
-                                      uint64_t* keys_sorted, uint32_t* values_sorted, void* stream,
+                                      uint64_t* keys_sorted, uint32_t* values_sorted, const uint32_t* tile_counts, void* stream,
                                       float* launch_ms, int* launch_kind, int capacity, int* num_launches)
 {
     using namespace fgs;
@@ -1721,7 +1807,8 @@ extern "C" int fgs_sort_pairs_profile(int num_rendered, int width, int height, i
         if (cudaEventCreate(&e) != cudaSuccess) return FGS_ERR_CUDA;
     int launches = 0;
     int st = sort_pairs_impl(num_rendered, width, height, block_x, block_y, temp, temp_bytes, keys_unsorted,
-                             values_unsorted, keys_sorted, values_sorted, stream, ev, launch_kind, &launches);
+                             values_unsorted, keys_sorted, values_sorted, stream, ev, launch_kind, &launches, nullptr,
+                             ORDER_BY_VALUE, tile_counts);
     *num_launches = 0;
     if (st == FGS_OK && launches > 0) {
         if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) st = FGS_ERR_CUDA;

@@ -73,11 +73,13 @@ def preprocess(orig_points, shs, opacities, cov3Ds, width, height, block_x, bloc
                position, rotation, focal_x, focal_y, zFar, zNear,
                points_xy, rgb_depth, conic_opacity,
                gaussian_keys_unsorted, gaussian_values_unsorted, curr_offset,
-               tile_row_begin: int = 0, tile_row_end: int = -1, cull_scratch=None, scene_bounds=None) -> None:
+               tile_row_begin: int = 0, tile_row_end: int = -1, cull_scratch=None, scene_bounds=None,
+               tile_counts=None) -> None:
     """csrc/pybind.cpp:122-150. The trailing keyword arguments restrict the pairs to a strip of tile rows;
     ``cull_scratch`` (int32 CUDA tensor, at least P + 1 elements) lets a strip list the Gaussians that can reach it
     first and run the expensive kernel on those only; ``scene_bounds`` (what ``prepare_scene`` returned for these
-    arrays) makes that first kernel read 16 bytes per Gaussian instead of 40."""
+    arrays) makes that first kernel read 16 bytes per Gaussian instead of 40; ``tile_counts`` (int32 CUDA tensor of
+    65536 elements) receives the pairs per tile, which ``sort_gaussian(..., tile_counts=)`` then need not count again."""
     f32 = torch.float32
     pts = _in(orig_points, "orig_points", f32)
     sh = _in(shs, "shs", f32)
@@ -99,6 +101,11 @@ def preprocess(orig_points, shs, opacities, cov3Ds, width, height, block_x, bloc
         bounds = _in(scene_bounds, "scene_bounds", f32)
         if scratch is None or bounds.numel() != 4 * P or not scene_bounds.is_contiguous():
             raise RuntimeError("scene_bounds needs cull_scratch and one contiguous [4] record per Gaussian")
+    counts = None
+    if tile_counts is not None:
+        counts = _out(tile_counts, "tile_counts", torch.int32)
+        if counts.numel() < _lib.TILE_COUNT_WORDS:
+            raise RuntimeError("tile_counts needs %d elements" % _lib.TILE_COUNT_WORDS)
     st = _L.fgs_preprocess_prepared(P, pts.data_ptr(), sh.data_ptr(), op.data_ptr(), cov.data_ptr(),
                                     int(width), int(height), int(block_x), int(block_y),
                                     pos.data_ptr(), rot.data_ptr(),
@@ -108,7 +115,8 @@ def preprocess(orig_points, shs, opacities, cov3Ds, width, height, block_x, bloc
                                     keys.data_ptr(), vals.data_ptr(), cap, off.data_ptr(),
                                     None if scratch is None else scratch.data_ptr(),
                                     0 if scratch is None else int(scratch.numel()),
-                                    None if bounds is None else bounds.data_ptr(), _stream())
+                                    None if bounds is None else bounds.data_ptr(),
+                                    None if counts is None else counts.data_ptr(), _stream())
     _lib.check("preprocess", st)
 
 
@@ -135,10 +143,11 @@ def get_sort_buffer_size(num_rendered: int) -> int:
 
 def sort_gaussian(num_rendered, width, height, block_x, block_y, list_sorting_space,
                   gaussian_keys_unsorted, gaussian_values_unsorted,
-                  gaussian_keys_sorted, gaussian_values_sorted, stable: bool = False) -> None:
+                  gaussian_keys_sorted, gaussian_values_sorted, stable: bool = False, tile_counts=None) -> None:
     """csrc/pybind.cpp:152-163. Pairs with identical sorted key bits come out in ascending order of their values
     (the frame is then the same bytes every run); ``stable=True`` keeps them in input order, which is the reference's
-    library-sort contract, through the slower look-back passes (see ``fgs_sort_pairs`` in include/flashgs_b200.h)."""
+    library-sort contract, through the slower look-back passes (see ``fgs_sort_pairs`` in include/flashgs_b200.h).
+    ``tile_counts``: the table ``preprocess(..., tile_counts=)`` filled for this pair list; the sort starts from it."""
     n = int(num_rendered)
     ki = _in(gaussian_keys_unsorted, "gaussian_keys_unsorted", torch.int64)
     vi = _in(gaussian_values_unsorted, "gaussian_values_unsorted", torch.int32)
@@ -149,9 +158,17 @@ def sort_gaussian(num_rendered, width, height, block_x, block_y, list_sorting_sp
     tmp = list_sorting_space
     if not tmp.is_cuda or not tmp.is_contiguous():
         raise RuntimeError("list_sorting_space must be a contiguous CUDA tensor")
-    st = (_L.fgs_sort_pairs_stable if stable else _L.fgs_sort_pairs)(n, int(width), int(height), int(block_x), int(block_y),
-        tmp.data_ptr(), tmp.numel() * tmp.element_size(),
-        ki.data_ptr(), vi.data_ptr(), ko.data_ptr(), vo.data_ptr(), _stream())
+    args = (n, int(width), int(height), int(block_x), int(block_y), tmp.data_ptr(), tmp.numel() * tmp.element_size(),
+            ki.data_ptr(), vi.data_ptr(), ko.data_ptr(), vo.data_ptr())
+    if stable:
+        st = _L.fgs_sort_pairs_stable(*args, _stream())
+    elif tile_counts is not None:
+        counts = _in(tile_counts, "tile_counts", torch.int32)
+        if counts.numel() < _lib.TILE_COUNT_WORDS or not tile_counts.is_contiguous():
+            raise RuntimeError("tile_counts needs %d contiguous elements" % _lib.TILE_COUNT_WORDS)
+        st = _L.fgs_sort_pairs_counted(*args, counts.data_ptr(), _stream())
+    else:
+        st = _L.fgs_sort_pairs(*args, _stream())
     _lib.check("sort_gaussian", st)
 
 

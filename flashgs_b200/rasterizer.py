@@ -78,6 +78,8 @@ class Rasterizer:
         # ... and that list is found from 16-byte records prepared once per scene (position and a bound on the reach)
         self.scene_bounds = (ops.prepare_scene(scene.position, scene.opacity, scene.cov3d)
                              if self.cull_scratch is not None and hasattr(ops, "prepare_scene") else None)
+        # preprocess knows every pair's tile when it emits it: it counts the pairs per tile for the sort that follows
+        self.tile_counts = z(65536, torch.int32) if ours else None
         self._render = {(16, 16): "render_16x16", (32, 16): "render_32x16", (32, 32): "render_32x32"}[tuple(block)]
 
     def forward(self, scene: DeviceScene, camera, bg_color, out_color=None, rows=None):
@@ -89,6 +91,10 @@ class Rasterizer:
             extra["cull_scratch"] = self.cull_scratch
             if self.scene_bounds is not None:
                 extra["scene_bounds"] = self.scene_bounds
+        sort_extra = {}
+        if self.tile_counts is not None:
+            extra["tile_counts"] = self.tile_counts
+            sort_extra["tile_counts"] = self.tile_counts
         ops.preprocess(scene.position, scene.shs, scene.opacity, scene.cov3d,
                        camera.width, camera.height, bx, by,
                        camera.position, camera.rotation,
@@ -103,7 +109,7 @@ class Rasterizer:
         ops.sort_gaussian(num_rendered, camera.width, camera.height, bx, by,
                           self.list_sorting_space,
                           self.gaussian_keys_unsorted, self.gaussian_values_unsorted,
-                          self.gaussian_keys_sorted, self.gaussian_values_sorted)
+                          self.gaussian_keys_sorted, self.gaussian_values_sorted, **sort_extra)
         if out_color is None:
             out_color = torch.zeros((camera.height, camera.width, 3), device=scene.device, dtype=torch.int8)
         if rows is None:

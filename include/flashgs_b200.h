@@ -34,6 +34,9 @@ extern "C" {
 #define FGS_ERR_BOUNDS 32          /* checked build only (-DFGS_DEBUG_BOUNDS): a kernel met an index outside its extent
                                       and skipped the access; see fgs_debug_bounds_report in flashgs_b200_test.h */
 
+/* Length, in 32-bit words, of a per-tile pair-count table (fgs_preprocess_prepared -> fgs_sort_pairs_counted). */
+#define FGS_TILE_COUNT_WORDS 65536
+
 /* Version of this ABI; bumped when a signature changes. */
 int fgs_abi_version(void);
 
@@ -133,7 +136,11 @@ int fgs_scene_bounds(int P, const float* positions, const float* opacities, cons
  * GPU that renders a strip, so it is the part of a frame that does not shrink with the number of GPUs. The list
  * is a superset of fgs_preprocess_strip_culled's; pairs and feature records are the same. `scene_bounds` may be
  * NULL (then this is fgs_preprocess_strip_culled); with it, `cull_scratch` is required. The records must describe
- * the arrays passed here. No counterpart in the reference.
+ * the arrays passed here.
+ * `tile_counts` (NULL, or FGS_TILE_COUNT_WORDS words): preprocess knows each pair's tile at the moment it emits the
+ * pair, so it can count the pairs per tile as it goes (the table is zeroed first; entry t = pairs of tile t that
+ * were stored, i.e. that fitted the pair buffers); fgs_sort_pairs_counted then skips the pass over all keys that
+ * would recount them. Ignored for images with more than FGS_TILE_COUNT_WORDS tiles. No counterpart in the reference.
  */
 int fgs_preprocess_prepared(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
                             int width, int height, int block_x, int block_y,
@@ -143,7 +150,7 @@ int fgs_preprocess_prepared(int P, const float* positions, const float* shs, con
                             float* points_xy, float* rgb_depth, float* conic_opacity,
                             uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
                             int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints,
-                            const float* scene_bounds, void* stream);
+                            const float* scene_bounds, uint32_t* tile_counts, void* stream);
 
 /*
  * fgs_preprocess_prepared with CUDA events around its two kernels: waits for the stream and fills
@@ -158,7 +165,7 @@ int fgs_preprocess_profile(int P, const float* positions, const float* shs, cons
                            float* points_xy, float* rgb_depth, float* conic_opacity,
                            uint64_t* keys_unsorted, uint32_t* values_unsorted, int64_t pair_capacity,
                            int* curr_offset, int* cull_scratch, int64_t cull_scratch_ints,
-                           const float* scene_bounds, void* stream, float* kernel_ms2);
+                           const float* scene_bounds, uint32_t* tile_counts, void* stream, float* kernel_ms2);
 
 /*
  * Scratch bytes fgs_sort_pairs needs for up to `num_rendered` pairs. Replaces
@@ -193,6 +200,19 @@ int fgs_sort_pairs_stable(int num_rendered, int width, int height, int block_x, 
                           uint64_t* keys_sorted, uint32_t* values_sorted, void* stream);
 
 /*
+ * fgs_sort_pairs given the pairs per tile (`tile_counts`, FGS_TILE_COUNT_WORDS words, as fgs_preprocess_prepared
+ * leaves them for the same image, tile shape and pair list): the sort starts from that table instead of reading
+ * all keys once to build it. The table is checked against num_rendered on the device: if its total differs the
+ * sort moves nothing, raises FGS_ERR_BAD_ARG in the device status word and leaves the outputs undefined (it never
+ * writes outside them). With a NULL table, or an image with more than FGS_TILE_COUNT_WORDS tiles, it is
+ * fgs_sort_pairs. No counterpart in the reference.
+ */
+int fgs_sort_pairs_counted(int num_rendered, int width, int height, int block_x, int block_y,
+                           void* temp, size_t temp_bytes,
+                           const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
+                           uint64_t* keys_sorted, uint32_t* values_sorted, const uint32_t* tile_counts, void* stream);
+
+/*
  * fgs_sort_pairs for callers that have no scratch buffer to give and must not allocate one: code that runs
  * where device allocation is off limits (inside another framework's memory plan, in a callback, in a process
  * whose allocator is owned by someone else). It has no counterpart in the reference, whose sort always takes
@@ -212,7 +232,7 @@ int fgs_sort_pairs_static(int num_rendered, int width, int height, int block_x, 
                           uint64_t* keys_sorted, uint32_t* values_sorted, void* stream);
 
 /*
- * fgs_sort_pairs with CUDA events recorded around each of its kernel launches; waits for the stream and
+ * fgs_sort_pairs_counted with CUDA events recorded around each of its kernel launches; waits for the stream and
  * fills launch_ms[i] and launch_kind[i] for every launch i (kinds: 0 histogram, 1 tile-grouping or digit pass,
  * 2 tile segments, 3 in-block tile sort); *num_launches receives the count (0 when num_rendered is 0). Both arrays
  * must hold `capacity` >= 24 entries. A measurement aid for benchmarks: it creates and destroys events
@@ -221,7 +241,7 @@ int fgs_sort_pairs_static(int num_rendered, int width, int height, int block_x, 
 int fgs_sort_pairs_profile(int num_rendered, int width, int height, int block_x, int block_y,
                            void* temp, size_t temp_bytes,
                            const uint64_t* keys_unsorted, const uint32_t* values_unsorted,
-                           uint64_t* keys_sorted, uint32_t* values_sorted, void* stream,
+                           uint64_t* keys_sorted, uint32_t* values_sorted, const uint32_t* tile_counts, void* stream,
                            float* launch_ms, int* launch_kind, int capacity, int* num_launches);
 
 /*

@@ -54,6 +54,10 @@ class Frame:
             extra["cull_scratch"] = torch.full((P + 1,), 0x7F7F7F7F, device=DEV, dtype=torch.int32)
             if cull == "bounds":   # ... found from the 16-byte records prepared once per scene
                 extra["scene_bounds"] = ops.prepare_scene(self.pos, self.opa, self.cov)
+        sort_extra = {}
+        if cull == "bounds":       # the whole set of extensions: preprocess also counts the pairs per tile for the sort
+            self.counts = torch.full((65536,), 0x7F7F7F7F, device=DEV, dtype=torch.int32)
+            extra["tile_counts"] = sort_extra["tile_counts"] = self.counts
         ops.preprocess(self.pos, self.shs, self.opa, self.cov, cam.width, cam.height, bx, by, self.cpos, self.crot,
                        cam.focal_x, cam.focal_y, cam.zFar, cam.zNear, self.xy, self.rd, self.co,
                        self.ku, self.vu, self.off, **extra)
@@ -63,7 +67,7 @@ class Frame:
             return
         R = self.R
         self.temp = z(ops.get_sort_buffer_size(max(R, 1)), torch.int8)
-        ops.sort_gaussian(R, cam.width, cam.height, bx, by, self.temp, self.ku, self.vu, self.ks, self.vs)
+        ops.sort_gaussian(R, cam.width, cam.height, bx, by, self.temp, self.ku, self.vu, self.ks, self.vs, **sort_extra)
         self.ranges = z((gx * gy, 2), torch.int32)
         self.img = z((cam.height, cam.width, 3), torch.uint8)
         bgt = torch.tensor(bg, dtype=torch.float32)
@@ -705,4 +709,37 @@ def test_view_batch_views_match_oracle(ops, oracle_lib):
         assert ras.num_rendered == int(want["counters"][3])
         d = np.abs(img.cpu().numpy().view(np.uint8).astype(int) - want["u8"].astype(int))
         assert d.max() <= 1 and (d > 0).mean() <= 1e-3
+    assert ops.device_status() == 0
+
+
+def test_sort_from_preprocess_tile_counts(ops, oracle_lib):
+    """preprocess counts the pairs per tile while it emits them; the sort given that table skips its own counting pass
+    and gives the same bytes. A table that does not belong to the pair list is detected on the device: nothing is
+    moved, the status word says so, nothing outside the buffers is touched."""
+    from flashgs_b200 import _lib
+    w, sc, cams = scenes.make_workload("C1", 50000)
+    cam = cams[0]
+    a = Frame(ops, sc, cam, floats=False)
+    b = Frame(ops, sc, cam, floats=False, cull="bounds")
+    assert a.R == b.R
+    assert (a.np("ks", a.R) == b.np("ks", b.R)).all() and (a.np("vs", a.R) == b.np("vs", b.R)).all()
+    assert (a.np("img") == b.np("img")).all()            # the same pair set -> byte for byte the same image
+    gx, gy = scenes.tile_grid(cam.width, cam.height)
+    counts = b.counts.cpu().numpy()
+    want = np.bincount((b.np("ku", b.R) >> np.uint64(32)).astype(np.int64), minlength=65536)
+    assert (counts == want).all() and counts[gx * gy:].sum() == 0
+    # strips count their own pairs only
+    c = Frame(ops, sc, cam, rows=(10, 20), cull="bounds")
+    want = np.bincount((c.np("ku", c.R) >> np.uint64(32)).astype(np.int64), minlength=65536)
+    assert (c.counts.cpu().numpy() == want).all()
+    d = np.abs(a.np("img")[160:320].astype(int) - c.np("img")[160:320].astype(int))
+    assert d.max() <= 1 and (d > 0).mean() <= 1e-5
+    # a table of another frame: refused on the device
+    assert ops.device_status() == 0
+    guard_k = torch.full((a.R + 64,), -7, device=DEV, dtype=torch.int64)
+    guard_v = torch.full((a.R + 64,), -7, device=DEV, dtype=torch.int32)
+    ops.sort_gaussian(a.R, cam.width, cam.height, 16, 16, a.temp, a.ku, a.vu, guard_k[: a.R], guard_v[: a.R], tile_counts=c.counts)
+    torch.cuda.synchronize()
+    assert ops.device_status() & _lib.ERR_BAD_ARG
+    assert (guard_k[a.R:] == -7).all() and (guard_v[a.R:] == -7).all()
     assert ops.device_status() == 0

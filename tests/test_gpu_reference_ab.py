@@ -39,11 +39,12 @@ class Run:
         self.ku, self.vu, self.ks, self.vs = z(cap, torch.int64), z(cap, torch.int32), z(cap, torch.int64), z(cap, torch.int32)
         off = z(1, torch.int32)
         tmp = z(ops.get_sort_buffer_size(cap), torch.int8)
-        extra = {}
+        extra, sort_extra = {}, {}
         if cull:   # the bench's path: the head of the sort's scratch holds the index list of the Gaussians that reach the image
             extra["cull_scratch"] = tmp[: 4 * (P + 1)].view(torch.int32)
-            if cull == "bounds":   # ... and the list is found from 16-byte records prepared once per scene
-                extra["scene_bounds"] = ops.prepare_scene(pos, opa, cov)
+            if cull == "bounds":   # ... the list is found from 16-byte records prepared once per scene, and preprocess
+                extra["scene_bounds"] = ops.prepare_scene(pos, opa, cov)   # counts the pairs per tile for the sort
+                sort_extra["tile_counts"] = extra["tile_counts"] = z(65536, torch.int32)
         ops.preprocess(pos, shs, opa, cov, W, H, 16, 16, torch.from_numpy(cam.position.copy()),
                        torch.from_numpy(cam.rotation.copy()), cam.focal_x, cam.focal_y, cam.zFar, cam.zNear,
                        self.xy, self.rd, self.co, self.ku, self.vu, off, **extra)
@@ -51,7 +52,7 @@ class Run:
         self.cap = cap
         if R >= cap:
             return
-        ops.sort_gaussian(R, W, H, 16, 16, tmp, self.ku, self.vu, self.ks, self.vs)
+        ops.sort_gaussian(R, W, H, 16, 16, tmp, self.ku, self.vu, self.ks, self.vs, **sort_extra)
         torch.cuda.synchronize()
         del tmp
         cnt = torch.bincount(self.ks[:R] >> 32, minlength=gx * gy)
