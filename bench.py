@@ -619,13 +619,13 @@ def main():
             hbm("strip_cull_kernel", cull_ms, 1, bytes_cull)
         hbm("preprocess_kernel", main_ms, 1, bytes_main)
         names = {0: "tile_hist_kernel", 1: "multisplit_kernel", 2: "tile_scan_kernel", 3: "local_sort_kernel + long_list_kernel"}
-        hist_ms, pass_ms, seg_ms, local_ms = sum(by_kind(0)), by_kind(1), sum(by_kind(2)), sum(by_kind(3))
+        hist_ms, pass_ms, seg_ms, tile_sort_ms = sum(by_kind(0)), by_kind(1), sum(by_kind(2)), sum(by_kind(3))
         if by_kind(0):
             hbm(names[0], hist_ms, len(by_kind(0)), 8 * R)
         mean_pass = float(np.mean(pass_ms)) if pass_ms else 0.0
         hbm(names[1], mean_pass, len(pass_ms), 24 * R, "mean of the passes: " + ", ".join("%.3f" % x for x in pass_ms))
         hbm(names[2], seg_ms, len(by_kind(2)), 16 * 32768, "one block; bound by its own latency, not by HBM")
-        k_local = hbm(names[3], local_ms, len(by_kind(3)), 24 * R, "all four launches (three list-length classes and the long lists) as one: "
+        k_local = hbm(names[3], tile_sort_ms, len(by_kind(3)), 24 * R, "all four launches (three list-length classes and the long lists) as one: "
                       + ", ".join("%.3f" % x for x in by_kind(3)))
         k_local["lumped"] = True
         hbm("tile_ranges_kernel", ranges_ms, 1, 8 * Tn, "binary searches: 2 log2(R) cached reads per tile")

@@ -691,122 +691,109 @@ tile_hist_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict
     }
 }
 
-// One block. From the pairs per tile value: every tile's [first, last) in the tile-grouped list and its cursor
-// (= first), the work lists of the tile sorts' length classes, and the tables of the coarse buckets (a bucket is
-// the run of 2^lo_bits consecutive tile values that share their upper bits): where each bucket starts, its cursor,
-// and the running count of the second pass's units (partitions cut inside a bucket).
-// All global accesses are coalesced (a single SM does this work: strided accesses would cost one memory
-// transaction per lane): the counts are staged in shared memory, scanned there by threads that own consecutive
-// tiles, and the results are written out by threads that own neighbouring tiles. Up to SCAN_ROUND tile values are
-// handled per round (two rounds for 65536).
-constexpr int SCAN_ROUND = 32768;
-constexpr int SCAN_SMEM_BYTES = (SCAN_ROUND + SCAN_ROUND / 32 + 2) * 4;
-__device__ __forceinline__ int scan_pad(int i) { return i + (i >> 5); }   // consecutive chunks of 32 words start in different banks
+// From the pairs per tile value: every tile's [first, last) in the tile-grouped list and its cursor (= first), the
+// work lists of the tile sorts' length classes, and the tables of the coarse buckets (a bucket is the run of
+// 2^lo_bits consecutive tile values that share their upper bits): where each bucket starts, its cursor, and the
+// running count of the second pass's units (partitions cut inside a bucket).
+// A block owns SCAN_CHUNK consecutive tile values. It finds the pairs in front of its chunk by summing the counts
+// of all earlier tiles itself (at most 64 K coalesced loads spread over its threads: cheaper than any hand-over
+// between blocks, and nobody waits for anybody), scans its own counts, and writes its tiles' outputs. The block
+// that finishes last (a ticket drawn after a fence; no block waits for it) builds the unit table from the
+// buckets' starts and checks the total against the pair count.
+constexpr int SCAN_CHUNK = TILE_SCAN_THREADS;   // one tile value per thread
 
 __global__ void __launch_bounds__(TILE_SCAN_THREADS, 1)
 tile_scan_kernel(const uint32_t* __restrict__ tile_count, int tile_values, int lo_bits,
-                 int2* __restrict__ seg, uint32_t* __restrict__ cursor, uint32_t* __restrict__ bucket_tables,
-                 int* __restrict__ class_count, uint32_t* __restrict__ class_tiles,
-                 int n_pairs, const int* __restrict__ n_dev, int* __restrict__ dev_status)
+                 int2* __restrict__ seg, uint32_t* __restrict__ cursor, uint32_t* bucket_tables,
+                 int* class_count, uint32_t* __restrict__ class_tiles,
+                 int n_pairs, const int* __restrict__ n_dev, int* __restrict__ dev_status, uint32_t* done_ticket)
 {
     constexpr int WARPS = TILE_SCAN_THREADS / 32;
-    extern __shared__ __align__(16) uint32_t s_pref[];          // counts, then exclusive prefixes (padded), one round
-    __shared__ uint32_t s_wsum[WARPS];
-    __shared__ uint32_t s_bucket_first[MAX_BUCKETS + 1];
+    __shared__ uint32_t s_wsum[2][WARPS];
     __shared__ uint32_t s_units[MAX_BUCKETS];
     __shared__ uint32_t s_usum[MAX_BUCKETS / 32];
-    __shared__ uint32_t s_class[LOCAL_CLASSES];
+    __shared__ int s_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const unsigned lt = lanemask_lt();
     const uint32_t lo_mask = (1u << lo_bits) - 1u;
     const int buckets = max(1, tile_values >> lo_bits);
-    if (tid < LOCAL_CLASSES) s_class[tid] = 0;
-    uint32_t carry = 0;   // pairs of the tiles of earlier rounds
-    for (int lo = 0; lo < tile_values; lo += SCAN_ROUND) {
-        const int n = min(SCAN_ROUND, tile_values - lo);
-        __syncthreads();   // the previous round's shared memory is no longer read
-        for (int b = 0; b < n; b += 8 * TILE_SCAN_THREADS) {   // eight independent loads in flight per thread
-            uint32_t v[8];
+    uint32_t* hi_cursor = bucket_tables;                      // [0, B) cursors of the coarse buckets
+    uint32_t* bucket_first = bucket_tables + MAX_BUCKETS;     // [B + 1] where each bucket starts, then the total
+    uint32_t* unit_prefix = bucket_first + MAX_BUCKETS + 1;   // [B + 1] exclusive unit counts, then their total
+
+    const int chunk0 = blockIdx.x * SCAN_CHUNK;
+    const int t = chunk0 + tid;
+    // pairs of all earlier tiles: eight independent loads in flight per thread
+    uint32_t before = 0;
+    for (int b = 0; b < chunk0; b += 8 * TILE_SCAN_THREADS) {
+        uint32_t v[8];
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                const int i = b + u * TILE_SCAN_THREADS + tid;
-                v[u] = i < n ? tile_count[lo + i] : 0u;
-            }
+        for (int u = 0; u < 8; u++) {
+            const int i = b + u * TILE_SCAN_THREADS + tid;
+            v[u] = i < chunk0 ? tile_count[i] : 0u;
+        }
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                const int i = b + u * TILE_SCAN_THREADS + tid;
-                if (i < n) s_pref[scan_pad(i)] = v[u];
-            }
-        }
-        __syncthreads();
-        // exclusive scan: a thread owns `per` consecutive tiles
-        const int per = (n + TILE_SCAN_THREADS - 1) / TILE_SCAN_THREADS;
-        const int t0 = min(n, tid * per), t1 = min(n, t0 + per);
-        uint32_t sum = 0;
-        for (int t = t0; t < t1; t++) sum += s_pref[scan_pad(t)];
-        uint32_t inc = sum;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t a = __shfl_up_sync(FULL_MASK, inc, o);
-            if (lane >= o) inc += a;
-        }
-        if (lane == 31) s_wsum[warp] = inc;
-        __syncthreads();
-        uint32_t run = carry + inc - sum, total = 0;
-        for (int w = 0; w < WARPS; w++) { const uint32_t s = s_wsum[w]; if (w < warp) run += s; total += s; }
-        for (int t = t0; t < t1; t++) {
-            const uint32_t c = s_pref[scan_pad(t)];
-            s_pref[scan_pad(t)] = run;
-            run += c;
-        }
-        if (tid == 0) s_pref[scan_pad(n)] = carry + total;
-        __syncthreads();
-        // outputs, neighbouring threads for neighbouring tiles
-        for (int b = 0; b < n; b += TILE_SCAN_THREADS) {
-            const int i = b + tid;
-            const bool ok = i < n;
-            const uint32_t first = ok ? s_pref[scan_pad(i)] : 0u;
-            const uint32_t c = ok ? s_pref[scan_pad(i + 1)] - first : 0u;
-            const int t = lo + i;
-            if (ok && FGS_INDEX_OK(t, MAX_TILE_VALUES)) {
-                seg[t] = make_int2((int)first, (int)(first + c));
-                cursor[t] = first;
-                if (((uint32_t)t & lo_mask) == 0 && FGS_INDEX_OK(t >> lo_bits, MAX_BUCKETS)) s_bucket_first[t >> lo_bits] = first;
-            }
-            const int k = c == 0 ? -1 : (c <= 1024u ? 0 : (c <= 2048u ? 1 : (c <= (uint32_t)LOCAL_CAP ? 2 : 3)));
-#pragma unroll
-            for (int q = 0; q < LOCAL_CLASSES; q++) {   // the warp reserves its places in class q's work list with one add
-                const unsigned in_class = __ballot_sync(FULL_MASK, k == q);
-                if (in_class) {
-                    uint32_t at = 0;
-                    if (lane == 0) at = atomicAdd(&s_class[q], (uint32_t)__popc(in_class));
-                    at = __shfl_sync(FULL_MASK, at, 0);
-                    if (k == q && FGS_INDEX_OK(at + __popc(in_class & lt), MAX_TILE_VALUES))
-                        class_tiles[(size_t)q * MAX_TILE_VALUES + at + __popc(in_class & lt)] = (uint32_t)t;
-                }
-            }
-        }
-        carry += total;
+        for (int u = 0; u < 8; u++) before += v[u];
     }
+    const uint32_t c = t < tile_values ? tile_count[t] : 0u;
+    uint32_t inc = c, red = before;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t a = __shfl_up_sync(FULL_MASK, inc, o);
+        if (lane >= o) inc += a;
+        red += __shfl_xor_sync(FULL_MASK, red, o);
+    }
+    if (lane == 31) s_wsum[0][warp] = inc;
+    if (lane == 0) s_wsum[1][warp] = red;
     __syncthreads();
+    uint32_t first = inc - c, base = 0, chunk_total = 0;
+    for (int w = 0; w < WARPS; w++) {
+        const uint32_t s = s_wsum[0][w];
+        if (w < warp) first += s;
+        chunk_total += s;
+        base += s_wsum[1][w];
+    }
+    first += base;
+    if (t < tile_values && FGS_INDEX_OK(t, MAX_TILE_VALUES)) {
+        seg[t] = make_int2((int)first, (int)(first + c));
+        cursor[t] = first;
+        if (((uint32_t)t & lo_mask) == 0 && FGS_INDEX_OK(t >> lo_bits, MAX_BUCKETS)) {
+            bucket_first[t >> lo_bits] = first;
+            hi_cursor[t >> lo_bits] = first;
+        }
+    }
+    const int k = c == 0 ? -1 : (c <= 1024u ? 0 : (c <= 2048u ? 1 : (c <= (uint32_t)LOCAL_CAP ? 2 : 3)));
+#pragma unroll
+    for (int q = 0; q < LOCAL_CLASSES; q++) {   // the warp reserves its places in class q's work list with one add
+        const unsigned in_class = __ballot_sync(FULL_MASK, k == q);
+        if (in_class) {
+            uint32_t at = 0;
+            if (lane == 0) at = (uint32_t)atomicAdd(class_count + q, __popc(in_class));
+            at = __shfl_sync(FULL_MASK, at, 0);
+            if (k == q && FGS_INDEX_OK(at + __popc(in_class & lt), MAX_TILE_VALUES))
+                class_tiles[(size_t)q * MAX_TILE_VALUES + at + __popc(in_class & lt)] = (uint32_t)t;
+        }
+    }
+    // the block that finishes last completes the tables
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(done_ticket, 1u) == gridDim.x - 1 ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const uint32_t total = (uint32_t)((volatile int2*)seg)[tile_values - 1].y;
     // The counts must add up to the number of pairs (they do when this sort counted them itself; a table handed in by
     // the caller is checked here): otherwise nothing is moved -- no work for the passes, no lists for the tile sorts.
-    const bool consistent = carry == (uint32_t)device_count(n_pairs, n_dev);
+    const bool consistent = total == (uint32_t)device_count(n_pairs, n_dev);
     if (!consistent && tid == 0) atomicOr(dev_status, FGS_ERR_BAD_ARG);
-    if (tid < LOCAL_CLASSES) class_count[tid] = consistent ? (int)s_class[tid] : 0;
-    if (tid == 0) s_bucket_first[buckets] = carry;
-    __syncthreads();
-    // bucket tables: [0, B) cursors, [B, 2B+1) firsts, [2B+1, 3B+2) exclusive unit counts (+ their total)
-    uint32_t* hi_cursor = bucket_tables;
-    uint32_t* bucket_first = bucket_tables + MAX_BUCKETS;
-    uint32_t* unit_prefix = bucket_first + MAX_BUCKETS + 1;
+    if (!consistent && tid < LOCAL_CLASSES) class_count[tid] = 0;
     if (tid < MAX_BUCKETS) {
         uint32_t units = 0;
         if (tid < buckets) {
-            const uint32_t first = s_bucket_first[tid], size = s_bucket_first[tid + 1] - first;
-            hi_cursor[tid] = consistent ? first : 0x80000000u;   // inconsistent counts: every destination falls outside the list
-            bucket_first[tid] = first;
-            units = consistent ? (size + MS_PART - 1) / MS_PART : 0u;
+            const uint32_t bf = ((volatile uint32_t*)bucket_first)[tid];
+            const uint32_t next = tid + 1 < buckets ? ((volatile uint32_t*)bucket_first)[tid + 1] : total;
+            units = consistent ? (next - bf + MS_PART - 1) / MS_PART : 0u;
+            if (!consistent) hi_cursor[tid] = 0x80000000u;   // every destination of the first pass falls outside the list
         }
         uint32_t uinc = units;
 #pragma unroll
@@ -817,7 +804,7 @@ tile_scan_kernel(const uint32_t* __restrict__ tile_count, int tile_values, int l
         if (lane == 31) s_usum[warp] = uinc;
         s_units[tid] = uinc - units;   // exclusive inside the warp
     }
-    if (tid == 0) bucket_first[buckets] = s_bucket_first[buckets];
+    if (tid == 0) bucket_first[buckets] = total;
     __syncthreads();
     if (tid < MAX_BUCKETS) {
         uint32_t off = 0;
@@ -1526,7 +1513,6 @@ static int sort_device(int* dev_out, int* sm_count_out)
         opt_in((const void*)multisplit_kernel<false>, MS_SMEM_BYTES);
         opt_in((const void*)multisplit_kernel<true>, MS_SMEM_BYTES);
         opt_in((const void*)tile_hist_kernel, TILE_HIST_SMEM_VALUES * 4);
-        opt_in((const void*)tile_scan_kernel, SCAN_SMEM_BYTES);
         if (e != cudaSuccess) return FGS_ERR_CUDA;
         d.ready = true;
     }
@@ -1652,8 +1638,9 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         // lower and upper halves of the tile bits: at most 8 bits each
         const int lo_bits = tile_bits <= RADIX_BITS ? tile_bits : tile_bits / 2;
         const int buckets = tile_values >> lo_bits;
-        tile_scan_kernel<<<1, TILE_SCAN_THREADS, SCAN_SMEM_BYTES, st>>>(counts, tile_values, lo_bits, seg, tile_cursor, bucket_tables,
-                                                          class_count, class_tiles, n, n_dev, dev_status);
+        tile_scan_kernel<<<(tile_values + SCAN_CHUNK - 1) / SCAN_CHUNK, TILE_SCAN_THREADS, 0, st>>>(
+            counts, tile_values, lo_bits, seg, tile_cursor, bucket_tables, class_count, class_tiles, n, n_dev, dev_status,
+            tickets /* the first ticket word: cleared above, not used by any pass of this path */);
         mark(LAUNCH_SEGMENTS);
         const int ms_parts = (int)(((int64_t)n + MS_PART - 1) / MS_PART);
         const uint64_t* src_k = keys_unsorted;
