@@ -639,9 +639,7 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
 #ifndef FGS_MS_LATE_VALUES
 #define FGS_MS_LATE_VALUES 1   // 1: read a partition's values after the ranking instead of with its keys
 #endif
-#ifndef FGS_MS_AGGREGATE
-#define FGS_MS_AGGREGATE 0     // 1: lanes with equal digits add to the block's counter as one group
-#endif
+
 constexpr int MS_THREADS = 256;                       // thread d owns digit value d (at most 8 bits per pass)
 constexpr int MS_ITEMS = FGS_MS_ITEMS;
 constexpr int MS_PART = MS_THREADS * MS_ITEMS;        // pairs per partition
@@ -651,7 +649,6 @@ constexpr int TILE_HIST_THREADS = 1024;
 constexpr int TILE_HIST_SMEM_VALUES = 49152;          // tile values whose counters fit one block's shared memory
 constexpr int TILE_SCAN_THREADS = 1024;
 static_assert(MS_THREADS == MAX_BUCKETS, "a pass has at most as many digit values as the block has threads");
-static_assert((MS_THREADS / 32) * 2 * MS_THREADS * 4 <= MS_SMEM_BYTES, "the warps' mask words fit the reorder buffer");
 
 // Pairs per tile value, added to tile_count[] (zero on entry). With `in_smem` a block counts into shared memory
 // (tile_values * 4 bytes of dynamic shared memory) and adds its non-zero counters to the global ones at the end;
@@ -888,45 +885,15 @@ multisplit_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restri
     }
 #endif
     __syncthreads();
-    // place inside the digit's run (any order will do)
+    // Place inside the digit's run: the arrival number of a shared-memory add (any order will do). Letting the lanes
+    // that hold the same digit meet first and add as one group (bit masks in shared memory, as the stable digit pass
+    // ranks) was measured slower here: 0.27 ms per pass against 0.17.
     uint32_t slot[MS_ITEMS];
-#if FGS_MS_AGGREGATE
-    // Neighbouring pairs often share their digit (a splat's tiles of one row lie in one coarse bucket), and 32 adds to
-    // one shared-memory word take 32 turns. The lanes that hold the same digit therefore meet first -- every lane ORs
-    // its bit into the warp's word of its digit and reads the word back -- and the lowest of them adds the whole
-    // group to the block's counter with ONE add. The words live in the reorder buffer, which is idle until the scan
-    // below is done; two sets are used in turn and the group's lowest lane clears its word after use.
-    {
-        const unsigned lt = lanemask_lt();
-        uint32_t* my_masks = reinterpret_cast<uint32_t*>(s_ms) + warp * (2 * MS_THREADS);
-#pragma unroll
-        for (int i = 0; i < 2 * MS_THREADS / 32; i++) my_masks[i * 32 + lane] = 0;
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < MS_ITEMS; i++) {
-            const bool ok = i * MS_THREADS + tid < count;
-            const uint32_t d = digit_of_key(key[i]);
-            volatile uint32_t* word = my_masks + (i & 1) * MS_THREADS + d;
-            if (ok) atomicOr(const_cast<uint32_t*>(word), 1u << lane);
-            __syncwarp();
-            const unsigned peers = ok ? *word : (1u << lane);
-            __syncwarp();
-            uint32_t pre = 0;
-            if (ok && (peers & lt) == 0) {
-                *word = 0;
-                pre = atomicAdd(&s_cnt[d], (uint32_t)__popc(peers));
-            }
-            pre = __shfl_sync(FULL_MASK, pre, __ffs(peers) - 1);
-            slot[i] = pre + __popc(peers & lt);
-        }
-    }
-#else
 #pragma unroll
     for (int i = 0; i < MS_ITEMS; i++) {
         const int j = i * MS_THREADS + tid;
         slot[i] = j < count ? atomicAdd(&s_cnt[digit_of_key(key[i])], 1u) : 0u;
     }
-#endif
     __syncthreads();
     // thread d: exclusive scan of the counts (start of digit d's run in the reordered partition), and the
     // reservation of the run's place at its destination

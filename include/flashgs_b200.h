@@ -216,7 +216,7 @@ int fgs_sort_pairs_counted(int num_rendered, int width, int height, int block_x,
  * fgs_sort_pairs for callers that have no scratch buffer to give and must not allocate one: code that runs
  * where device allocation is off limits (inside another framework's memory plan, in a callback, in a process
  * whose allocator is owned by someone else). It has no counterpart in the reference, whose sort always takes
- * caller scratch. The scratch lives in a fixed array inside the library (about 5.9 MB that every GPU loading
+ * caller scratch. The scratch lives in a fixed array inside the library (about 5.8 MB that every GPU loading
  * the library holds until the process ends), so the call is limited to fgs_sort_static_max_pairs() = 262144
  * pairs and returns FGS_ERR_TEMP_TOO_SMALL beyond that (FGS_ERR_BAD_ARG for a negative count). Nothing is allocated or freed, by this library or by any
  * library it calls. The first call on each device looks up the array's device address (with that device
