@@ -631,14 +631,15 @@ def main():
         hbm("tile_ranges_kernel", ranges_ms, 1, 8 * Tn, "binary searches: 2 log2(R) cached reads per tile")
         fp32_peak = SM_COUNT * FP32_LANES_PER_SM * f_sm
         t_min_13 = 13 * pairs_px / fp32_peak * 1e3
-        t_min_own = max(7 * pairs_px / fp32_peak, pairs_px / (SM_COUNT * MUFU_LANES_PER_SM * f_sm)) * 1e3
+        t_min_own = max(10 * pairs_px / fp32_peak, pairs_px / (SM_COUNT * MUFU_LANES_PER_SM * f_sm)) * 1e3
         blend = {"kernel": "blend_kernel", "ms": blend_ms, "launches": 1, "bound": "fp32",
                  "achieved": 13 * pairs_px / (blend_ms * 1e-3) / 1e9, "peak": fp32_peak / 1e9, "unit": "G FP32 lane-instructions/s",
                  "frac": t_min_13 / blend_ms,
                  "formula": "13 FP32 instructions per (pixel, splat) pair x S x 256 pixels / time, against 148 SMs x 128 lanes x the sampled SM clock",
                  "sm_mhz": f_sm / 1e6, "pixel_splat_pairs": pairs_px,
                  "own_floor": {"ms": t_min_own, "frac": t_min_own / blend_ms,
-                               "formula": "this kernel issues 7 FP32 lane-instructions and 1 ex2 per pair: max(7 pairs / FP32 lanes, pairs / 16 SFU lanes per SM)"},
+                               "formula": "this kernel's own count: per lane and splat 4 per-column, 2 per-row and 7 per-pixel-pair packed operations, "
+                                          "40 for 8 pixels = 10 FP32 lane-instructions per pair, and 1 ex2: max(10 pairs / FP32 lanes, pairs / 16 SFU lanes per SM)"},
                  "algorithmic_bytes_per_launch": 8 * Tn + 44 * (S or 0) + 3 * pix}
         kernels.append(blend)
         longest = max(kernels, key=lambda k: max(by_kind(3) or [0.0]) if k.get("lumped") else k["ms"])   # by single launch

@@ -277,58 +277,82 @@ scene_bounds_kernel(int P, const float* __restrict__ positions, const float* __r
 // BOUNDS: the Gaussians come as the prepared 16-byte records (scene_bounds_kernel) instead of as position, opacity
 // and covariance rows; the reach bound is the same expression with ln(256 * opacity) replaced by its maximum in the
 // low-pass term, so it is never smaller and the list is a superset of the other variant's.
+constexpr int CULL_PER_BLOCK = 4096;                      // Gaussians a block of the index-list kernel looks at
+constexpr int CULL_PER_WARP = CULL_PER_BLOCK / PRE_WARPS;    // ... of which a warp can keep at most this many
+
 template <bool BOUNDS>
 __global__ void __launch_bounds__(PRE_THREADS)
 strip_cull_kernel(int P, const float* __restrict__ positions, const float* __restrict__ opacities,
                   const float* __restrict__ cov3ds, const float4* __restrict__ bounds,
                   const __grid_constant__ PreCam cam, int* __restrict__ list)
 {
+    // A block looks at CULL_PER_BLOCK consecutive Gaussians, 256 at a time; every warp collects the indices it keeps
+    // in its own shared-memory region, and the block appends all of them to the list with ONE atomicAdd at the end
+    // (every block adds to the same counter: one add per 256 Gaussians made the kernel wait on that word).
+    __shared__ int s_keep[PRE_WARPS][CULL_PER_WARP];
     __shared__ int s_count[PRE_WARPS];
     __shared__ int s_base;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int i = blockIdx.x * PRE_THREADS + tid;
-    bool keep = false;
-    if (i < P) {
+    const unsigned lt = lanemask_lt();
+    const int block_first = blockIdx.x * CULL_PER_BLOCK;
+    int kept_here = 0;   // indices this warp holds (the same in every lane)
+
+    auto reaches = [&](const f3& p, float q_or_opacity, const float* c3) -> bool {
+        const f3 p_view = xform4x3(p, cam.view);
+        if (p_view.z <= 0.2f) return false;
+        const float* pm = cam.proj;
+        const float hx = pm[0] * p.x + pm[4] * p.y + pm[8] * p.z + pm[12];
+        const float hy = pm[1] * p.x + pm[5] * p.y + pm[9] * p.z + pm[13];
+        const float hw = pm[3] * p.x + pm[7] * p.y + pm[11] * p.z + pm[15];
+        const float p_w = 1.0f / (hw + 0.0000001f);
         if (BOUNDS) {
-            const float4 b = __ldg(bounds + i);
-            const f3 p = { b.x, b.y, b.z };
-            const f3 p_view = xform4x3(p, cam.view);
-            if (!(p_view.z <= 0.2f) && !(b.w < 0.0f)) {
-                const float* pm = cam.proj;
-                const float hx = pm[0] * p.x + pm[4] * p.y + pm[8] * p.z + pm[12];
-                const float hy = pm[1] * p.x + pm[5] * p.y + pm[9] * p.z + pm[13];
-                const float hw = pm[3] * p.x + pm[7] * p.y + pm[11] * p.z + pm[15];
-                const float p_w = 1.0f / (hw + 0.0000001f);
-                const float fzy = cam.focal_y / p_view.z, ly = 1.3f * cam.tan_fovy;
-                const float fzx = cam.focal_x / p_view.z, lx = 1.3f * cam.tan_fovx;
-                // (|J row|^2 trace 1.02 + 0.3) * power <= |J row|^2 1.02 q + 0.3 kPowerMax
-                const float reach_y = 1.414214f * sqrtf(fzy * fzy * (1.0f + ly * ly) * 1.02f * b.w + 0.3f * kPowerMax) * 1.02f + 2.0f + (float)cam.block_y;
-                const float reach_x = 1.414214f * sqrtf(fzx * fzx * (1.0f + lx * lx) * 1.02f * b.w + 0.3f * kPowerMax) * 1.02f + 2.0f + (float)cam.block_x;
-                const float py = ndc_to_pix(hy * p_w, cam.H), px = ndc_to_pix(hx * p_w, cam.W);
-                const bool off_rows = py + reach_y < (float)(cam.row_begin * cam.block_y) || py - reach_y > (float)(cam.row_end * cam.block_y);
-                const bool off_cols = px + reach_x < 0.0f || px - reach_x > (float)(cam.grid_x * cam.block_x);
-                keep = !off_rows && !off_cols;
-            }
-        } else {
-            const f3 p = { __ldg(positions + 3 * (size_t)i), __ldg(positions + 3 * (size_t)i + 1), __ldg(positions + 3 * (size_t)i + 2) };
-            const f3 p_view = xform4x3(p, cam.view);
-            const float opacity = __ldg(opacities + i);
-            if (!(p_view.z <= 0.2f) && !(255.0f * opacity < 1.0f)) {
-                const float* pm = cam.proj;
-                const float hy = pm[1] * p.x + pm[5] * p.y + pm[9] * p.z + pm[13];
-                const float hw = pm[3] * p.x + pm[7] * p.y + pm[11] * p.z + pm[15];
-                const float projy = hy * (1.0f / (hw + 0.0000001f));
-                float c3[6];
+            if (q_or_opacity < 0.0f) return false;
+            const float fzy = cam.focal_y / p_view.z, ly = 1.3f * cam.tan_fovy;
+            const float fzx = cam.focal_x / p_view.z, lx = 1.3f * cam.tan_fovx;
+            // (|J row|^2 trace 1.02 + 0.3) * power <= |J row|^2 1.02 q + 0.3 kPowerMax
+            const float reach_y = 1.414214f * sqrtf(fzy * fzy * (1.0f + ly * ly) * 1.02f * q_or_opacity + 0.3f * kPowerMax) * 1.02f + 2.0f + (float)cam.block_y;
+            const float reach_x = 1.414214f * sqrtf(fzx * fzx * (1.0f + lx * lx) * 1.02f * q_or_opacity + 0.3f * kPowerMax) * 1.02f + 2.0f + (float)cam.block_x;
+            const float py = ndc_to_pix(hy * p_w, cam.H), px = ndc_to_pix(hx * p_w, cam.W);
+            const bool off_rows = py + reach_y < (float)(cam.row_begin * cam.block_y) || py - reach_y > (float)(cam.row_end * cam.block_y);
+            const bool off_cols = px + reach_x < 0.0f || px - reach_x > (float)(cam.grid_x * cam.block_x);
+            return !off_rows && !off_cols;
+        }
+        if (255.0f * q_or_opacity < 1.0f) return false;
+        return !misses_strip(cam, p_view.z, q_or_opacity, c3, hy * p_w) && !misses_columns(cam, p_view.z, q_or_opacity, c3, hx * p_w);
+    };
+
+    constexpr int BATCH = 4;   // records requested before the first is looked at
+    for (int c0 = 0; c0 < CULL_PER_BLOCK; c0 += BATCH * PRE_THREADS) {
+        float4 rec[BATCH];
+        if (BOUNDS) {
 #pragma unroll
-                for (int q = 0; q < 6; q++) c3[q] = __ldg(cov3ds + 6 * (size_t)i + q);
-                const float hx = pm[0] * p.x + pm[4] * p.y + pm[8] * p.z + pm[12];
-                const float projx = hx * (1.0f / (hw + 0.0000001f));
-                keep = !misses_strip(cam, p_view.z, opacity, c3, projy) && !misses_columns(cam, p_view.z, opacity, c3, projx);
+            for (int u = 0; u < BATCH; u++) {
+                const int i = block_first + c0 + u * PRE_THREADS + tid;
+                rec[u] = i < P ? __ldg(bounds + i) : make_float4(0.f, 0.f, 0.f, -1.f);
             }
         }
+#pragma unroll
+        for (int u = 0; u < BATCH; u++) {
+            const int i = block_first + c0 + u * PRE_THREADS + tid;
+            bool keep = false;
+            if (i < P) {
+                if (BOUNDS) {
+                    const f3 p = { rec[u].x, rec[u].y, rec[u].z };
+                    keep = reaches(p, rec[u].w, nullptr);
+                } else {
+                    const f3 p = { __ldg(positions + 3 * (size_t)i), __ldg(positions + 3 * (size_t)i + 1), __ldg(positions + 3 * (size_t)i + 2) };
+                    float c3[6];
+#pragma unroll
+                    for (int q = 0; q < 6; q++) c3[q] = __ldg(cov3ds + 6 * (size_t)i + q);
+                    keep = reaches(p, __ldg(opacities + i), c3);
+                }
+            }
+            const unsigned kept = __ballot_sync(FULL_MASK, keep);
+            if (keep && FGS_INDEX_OK(kept_here + __popc(kept & lt), CULL_PER_WARP)) s_keep[warp][kept_here + __popc(kept & lt)] = i;
+            kept_here += __popc(kept);
+        }
     }
-    const unsigned kept = __ballot_sync(FULL_MASK, keep);
-    if (lane == 0) s_count[warp] = __popc(kept);
+    if (lane == 0) s_count[warp] = kept_here;
     __syncthreads();
     if (tid == 0) {
         int total = 0;
@@ -336,11 +360,10 @@ strip_cull_kernel(int P, const float* __restrict__ positions, const float* __res
         s_base = total > 0 ? atomicAdd(list, total) : 0;   // one atomic per block
     }
     __syncthreads();
-    if (keep) {
-        int at = s_base + __popc(kept & lanemask_lt());
-        for (int w = 0; w < warp; w++) at += s_count[w];
-        if (FGS_INDEX_OK(at, P)) list[1 + at] = i;
-    }
+    int at = s_base;
+    for (int w = 0; w < warp; w++) at += s_count[w];
+    for (int j = lane; j < kept_here; j += 32)
+        if (FGS_INDEX_OK(at + j, P)) list[1 + at + j] = s_keep[warp][j];
 }
 
 // Optional per-phase cycle accounting (compile with -DFGS_PRE_TIMING): thread 0 of every block adds the SM
@@ -761,10 +784,11 @@ static int preprocess_impl(int P, const float* positions, const float* shs, cons
     if (events) cudaEventRecord(events[0], st);
     if (cull_scratch != nullptr) {
         if (cudaMemsetAsync(cull_scratch, 0, sizeof(int), st) != cudaSuccess) return FGS_ERR_CUDA;
+        const int cull_blocks = (P + CULL_PER_BLOCK - 1) / CULL_PER_BLOCK;
         if (scene_bounds != nullptr && aligned16(scene_bounds))
-            strip_cull_kernel<true><<<groups, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, reinterpret_cast<const float4*>(scene_bounds), cam, cull_scratch);
+            strip_cull_kernel<true><<<cull_blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, reinterpret_cast<const float4*>(scene_bounds), cam, cull_scratch);
         else
-            strip_cull_kernel<false><<<groups, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, nullptr, cam, cull_scratch);
+            strip_cull_kernel<false><<<cull_blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, nullptr, cam, cull_scratch);
         list = cull_scratch;
     }
     if (events) cudaEventRecord(events[1], st);

@@ -640,7 +640,11 @@ __global__ void segments_kernel(const uint64_t* __restrict__ keys, int n, const 
 #define FGS_MS_LATE_VALUES 1   // 1: read a partition's values after the ranking instead of with its keys
 #endif
 
-constexpr int MS_THREADS = 256;                       // thread d owns digit value d (at most 8 bits per pass)
+#ifndef FGS_MS_THREADS
+#define FGS_MS_THREADS 256
+#endif
+constexpr int MS_THREADS = FGS_MS_THREADS;            // thread d < MS_DIGITS owns digit value d (at most 8 bits per pass)
+constexpr int MS_DIGITS = MAX_BUCKETS;
 constexpr int MS_ITEMS = FGS_MS_ITEMS;
 constexpr int MS_PART = MS_THREADS * MS_ITEMS;        // pairs per partition
 constexpr int MS_SMEM_BYTES = MS_PART * 12;           // the partition reordered by digit: keys, then values
@@ -648,7 +652,7 @@ constexpr int MS_BLOCKS_PER_SM = FGS_MS_BLOCKS_PER_SM;
 constexpr int TILE_HIST_THREADS = 1024;
 constexpr int TILE_HIST_SMEM_VALUES = 49152;          // tile values whose counters fit one block's shared memory
 constexpr int TILE_SCAN_THREADS = 1024;
-static_assert(MS_THREADS == MAX_BUCKETS, "a pass has at most as many digit values as the block has threads");
+static_assert(MS_THREADS >= MS_DIGITS && MS_THREADS % 32 == 0, "a pass has at most as many digit values as the block has threads");
 
 // Pairs per tile value, added to tile_count[] (zero on entry). With `in_smem` a block counts into shared memory
 // (tile_values * 4 bytes of dynamic shared memory) and adds its non-zero counters to the global ones at the end;
@@ -828,10 +832,10 @@ multisplit_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restri
                   const uint32_t* bucket_tables, uint32_t* cursors)
 {
     extern __shared__ __align__(16) unsigned char s_ms[];      // reordered partition: keys [MS_PART], values [MS_PART]
-    __shared__ uint32_t s_cnt[MS_THREADS];                      // pairs per digit value in this partition
-    __shared__ uint32_t s_lstart[MS_THREADS];                   // where a digit's run starts in the reordered partition
-    __shared__ uint32_t s_delta[MS_THREADS];                    // destination index minus index in the reordered partition
-    __shared__ uint32_t s_wsum[MS_THREADS / 32];
+    __shared__ uint32_t s_cnt[MS_DIGITS];                       // pairs per digit value in this partition
+    __shared__ uint32_t s_lstart[MS_DIGITS];                    // where a digit's run starts in the reordered partition
+    __shared__ uint32_t s_delta[MS_DIGITS];                     // destination index minus index in the reordered partition
+    __shared__ uint32_t s_wsum[MS_DIGITS / 32];
     __shared__ uint32_t s_units[SECOND ? MAX_BUCKETS + 1 : 1];
     uint64_t* st_keys = reinterpret_cast<uint64_t*>(s_ms);
     uint32_t* st_vals = reinterpret_cast<uint32_t*>(s_ms + MS_PART * 8);
@@ -869,7 +873,7 @@ multisplit_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restri
         return SECOND ? (t & lo_mask) : (t >> lo_bits);
     };
 
-    s_cnt[tid] = 0;
+    if (tid < MS_DIGITS) s_cnt[tid] = 0;
     uint64_t key[MS_ITEMS];
 #pragma unroll
     for (int i = 0; i < MS_ITEMS; i++) {
@@ -897,22 +901,23 @@ multisplit_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restri
     __syncthreads();
     // thread d: exclusive scan of the counts (start of digit d's run in the reordered partition), and the
     // reservation of the run's place at its destination
-    const uint32_t c = s_cnt[tid];
+    const bool owner = tid < MS_DIGITS;   // whole warps
+    const uint32_t c = owner ? s_cnt[tid] : 0u;
     uint32_t inc = c;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         const uint32_t a = __shfl_up_sync(FULL_MASK, inc, o);
         if (lane >= o) inc += a;
     }
-    if (lane == 31) s_wsum[warp] = inc;
+    if (owner && lane == 31) s_wsum[warp] = inc;
     __syncthreads();
     uint32_t off = 0;
 #pragma unroll
-    for (int w = 0; w < MS_THREADS / 32; w++) off += (w < warp) ? s_wsum[w] : 0;
+    for (int w = 0; w < MS_DIGITS / 32; w++) off += (w < warp) ? s_wsum[w] : 0;
     const uint32_t lstart = off + inc - c;
-    s_lstart[tid] = lstart;
+    if (owner) s_lstart[tid] = lstart;
     uint32_t gstart = 0;
-    if (c && FGS_INDEX_OK(cursor_base + tid, SECOND ? MAX_TILE_VALUES : MAX_BUCKETS))
+    if (owner && c && FGS_INDEX_OK(cursor_base + tid, SECOND ? MAX_TILE_VALUES : MAX_BUCKETS))
         gstart = atomicAdd(cursors + cursor_base + tid, c);   // its round trip overlaps the reordering below
 #if FGS_MS_LATE_VALUES
     // the values are not needed before this point: fetched now, they do not hold registers during the ranking
@@ -935,7 +940,7 @@ multisplit_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restri
             }
         }
     }
-    s_delta[tid] = gstart - lstart;
+    if (owner) s_delta[tid] = gstart - lstart;
     __syncthreads();
     for (int j = tid; j < count; j += MS_THREADS) {
         const uint64_t k = st_keys[j];
