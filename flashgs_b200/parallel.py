@@ -132,6 +132,11 @@ class HostFrames:
             dist.broadcast_object_list(names, src=dst, group=group)
         if self.rank != dst:
             self.shm = shared_memory.SharedMemory(name=names[0])
+            try:   # the creating rank removes the segment; attaching ranks must not try to at exit
+                from multiprocessing import resource_tracker
+                resource_tracker.unregister(self.shm._name, "shared_memory")
+            except Exception:
+                pass
         buf = np.ndarray((total,), dtype=np.uint8, buffer=self.shm.buf)
         self._np = buf
         self.images = [torch.from_numpy(buf[i * image_bytes:(i + 1) * image_bytes].reshape(height, width, 3)).view(torch.int8)
