@@ -51,10 +51,12 @@ SM_COUNT, FP32_LANES_PER_SM, MUFU_LANES_PER_SM = 148, 128, 16
 # 1.5 M-Gaussian case of the same distribution (profiles/*_C4dist_1p5M_4K.txt); traffic grows in proportion
 # to the unit, so the full-size figure is this times the launch's units. None: no capture of that kernel.
 NCU_DRAM_BYTES_PER_UNIT = {
-    "preprocess_kernel": (287.9e6 / 1.5e6, "P"),      # per Gaussian of the scene (kernel on the index list)
-    "strip_cull_kernel": (60.2e6 / 1.5e6, "P"),
-    "blend_kernel": (117.3e6 / 7.161e6, "S"),         # per blended pair
-    "local_sort_kernel": (133.3e6 / 7.349e6, "R"),    # per pair
+    "preprocess_kernel": (290.5e6 / 1.5e6, "P"),      # per Gaussian of the scene (kernel on the index list)
+    "strip_cull_kernel": (24.0e6 / 1.5e6, "P"),       # the prepared 16-byte records
+    "blend_kernel": (115.0e6 / 7.161e6, "S"),         # per blended pair
+    "local_sort_kernel": (132.3e6 / 7.349e6, "R"),    # per pair
+    "multisplit_kernel": (127.9e6 / 7.349e6, "R"),    # per pair and pass; the small case's output partly stays in L2 (a lower bound)
+    "tile_hist_kernel": (59.0e6 / 7.349e6, "R"),
 }
 
 
