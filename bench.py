@@ -21,6 +21,8 @@ One JSON line is printed by rank 0:
             everything else: HBM); `roofline_hbm` the longest HBM-bound kernel; `kernels` every
             kernel of the frame with its fraction of the measured copy bandwidth and of 8 TB/s;
             `roofline_frame` the sum of the stages' minimum times over the measured step;
+  positional_frame  the same frame with preprocess and sort_gaussian given the reference's positional arguments only
+            (`config.preprocess_call` names the extension keywords the timed frame uses);
   cpu_baseline  the OpenMP restatement of the same pipeline on the host cores (N = 1 only);
   view_batch    the 64-view workload (C5) dealt out to the GPUs, views/s and per-view latency.
 
@@ -538,6 +540,20 @@ def main():
         except Exception as exc:
             fused["graph_error"] = repr(exc)[:200]
 
+    # ---- the same frame through the reference's positional arguments only (no extension keyword at all) ----
+    positional = None
+    if ours and (use_scratch or use_counts):
+        def positional_frame():
+            stage_pre(rows, scratch=False)
+            n = read_count()
+            ops.sort_gaussian(n, W, H, 16, 16, ras.list_sorting_space, ras.gaussian_keys_unsorted, ras.gaussian_values_unsorted,
+                              ras.gaussian_keys_sorted, ras.gaussian_values_sorted)
+            stage_render(n, rows)
+        pos_ms = timed(positional_frame)
+        positional = {"ms_per_step": pos_ms, "value": 1000.0 / pos_ms, "unit": "frames/s",
+                      "note": "preprocess and sort_gaussian called with the reference's positional arguments only"
+                              + ("" if rows is None else " (plus the strip's tile rows)")}
+
     # ---- per-kernel times (CUDA events around every launch, through the library's measurement entry points) ----
     peak, peak_src = measured_peaks()
     f_sm = (clocks.get("sm_mhz") or 1965.0) * 1e6
@@ -828,6 +844,7 @@ def main():
             line["strip_balance"] = balance
         if ours:
             line["fused_frame"] = fused
+            line["positional_frame"] = positional
             line["roofline"] = roofline
             line["roofline_hbm"] = roofline_hbm
             line["roofline_frame"] = roofline_frame
