@@ -1,28 +1,30 @@
-// Onesweep least-significant-digit radix sort of (64-bit key, 32-bit value) pairs, sm_100a.
+// Sort of (64-bit key, 32-bit value) pairs on the live key bits, sm_100a.
 //
-// Replaces the library radix sort the reference calls (csrc/cuda_rasterizer/sort.cu:28-44):
-// a STABLE sort on key bits [0, end_bit), end_bit = 32 + bit_length(#tiles)
-// (csrc/cuda_rasterizer/sort.cu:9-24,39), inputs preserved, outputs in separate buffers.
+// Replaces the library radix sort the reference calls (csrc/cuda_rasterizer/sort.cu:28-44): a sort on key bits
+// [0, end_bit), end_bit = 32 + bit_length(#tiles) (csrc/cuda_rasterizer/sort.cu:9-24,39), inputs preserved, outputs in
+// separate buffers. Two variants share the in-block tile sorts:
 //
-// Structure:
-//   * one histogram kernel reads the keys once and counts every 8-bit digit of the live
-//     bits (ceil(end_bit / 8) digits; bits at or above end_bit are never looked at);
-//   * one "onesweep" kernel per digit: a block (256 sorting threads and 64 look-back threads) takes the next
-//     partition of 4096 pairs from a ticket counter, ranks its keys by digit (lanes with equal digits meet
-//     through bit masks in shared memory; per-warp counters keep the sort stable), publishes its per-digit
-//     counts and obtains the counts of all earlier partitions by decoupled look-back, then moves keys and
-//     values through shared memory so that every digit's run leaves as contiguous global stores;
-//   * when the tile id fits 16 bits only the tile digits go through such passes; the pairs of every tile are
-//     then put in depth order by an in-block sort in shared memory (a block-wide radix sort in global memory
-//     for lists longer than 4096).
-//   Each pass reads 12 bytes and writes 12 bytes per pair once; passes ping-pong between the
-//   output buffers and an alternate pair buffer inside the caller's scratch.
+//   * fgs_sort_pairs (the default): the pairs are first GROUPED BY TILE, in any order inside a tile, by two passes in
+//     which no block waits for another (per-tile counts -> cursors; a block reserves room for each of its runs with
+//     one atomicAdd): tile_hist_kernel (unless the caller hands the counts over), tile_scan_kernel,
+//     multisplit_kernel; then every tile is ordered in shared memory by (depth bits, value): local_sort_kernel,
+//     long_list_kernel for lists longer than 4096. Pairs with identical keys come out in ascending order of their
+//     values, so the result depends on the set of pairs only, not on their input order.
+//   * fgs_sort_pairs_stable: the library sort's contract (identical keys in input order): one histogram kernel over
+//     the tile digits, one "onesweep" kernel per tile digit -- a block (256 sorting threads and 64 look-back
+//     threads) takes the next partition of 4096 pairs from a ticket counter, ranks its keys by digit (lanes with
+//     equal digits meet through bit masks in shared memory; per-warp counters keep the order), publishes its
+//     per-digit counts and obtains the counts of all earlier partitions by decoupled look-back, then moves keys and
+//     values through shared memory so that every digit's run leaves as contiguous global stores -- segments_kernel,
+//     and the tile sorts by (depth bits, position). Images with more than 65 535 tiles go through such passes for
+//     all their digits (no tile sorts).
+//   Each pass reads 12 bytes and writes 12 bytes per pair once; passes ping-pong between the output buffers and an
+//   alternate pair buffer inside the caller's scratch.
 //
-// Every wait on another block is bounded: the look-back gives up after a fixed poll budget,
-// raises FGS_ERR_LOOKBACK_TIMEOUT in the device status word, still publishes its own
-// (then meaningless) prefix so that later partitions do not wait on it, and the block ends
-// without scattering. Tickets are handed out in launch order, so a block only ever waits on
-// partitions whose blocks are already running.
+// Every wait on another block (the stable variant has them, the default none) is bounded: the look-back gives up
+// after a fixed poll budget, raises FGS_ERR_LOOKBACK_TIMEOUT in the device status word, still publishes its own
+// (then meaningless) prefix so that later partitions do not wait on it, and the block ends without scattering.
+// Tickets are handed out in launch order, so a block only ever waits on partitions whose blocks are already running.
 
 #include "fgs_common.cuh"
 
