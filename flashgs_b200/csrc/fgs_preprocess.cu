@@ -277,7 +277,10 @@ scene_bounds_kernel(int P, const float* __restrict__ positions, const float* __r
 // BOUNDS: the Gaussians come as the prepared 16-byte records (scene_bounds_kernel) instead of as position, opacity
 // and covariance rows; the reach bound is the same expression with ln(256 * opacity) replaced by its maximum in the
 // low-pass term, so it is never smaller and the list is a superset of the other variant's.
-constexpr int CULL_PER_BLOCK = 4096;                      // Gaussians a block of the index-list kernel looks at
+#ifndef FGS_CULL_PER_BLOCK
+#define FGS_CULL_PER_BLOCK 4096
+#endif
+constexpr int CULL_PER_BLOCK = FGS_CULL_PER_BLOCK;           // Gaussians a block of the index-list kernel looks at
 constexpr int CULL_PER_WARP = CULL_PER_BLOCK / PRE_WARPS;    // ... of which a warp can keep at most this many
 
 template <bool BOUNDS>
