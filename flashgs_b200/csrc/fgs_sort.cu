@@ -1188,7 +1188,15 @@ long_list_kernel(uint64_t* keys_grouped, uint32_t* vals_grouped, uint64_t* keys_
 #endif
 constexpr int LOCAL_BUCKET_LIMIT = FGS_LOCAL_BUCKET_LIMIT;
 __host__ __device__ constexpr int local_buckets(int cap) { return FGS_LOCAL_BUCKETS_PER_CAP_LOG2 >= 0 ? cap << (FGS_LOCAL_BUCKETS_PER_CAP_LOG2 >= 0 ? FGS_LOCAL_BUCKETS_PER_CAP_LOG2 : 0) : cap >> (FGS_LOCAL_BUCKETS_PER_CAP_LOG2 < 0 ? -(FGS_LOCAL_BUCKETS_PER_CAP_LOG2) : 0); }
-template <int CAP> constexpr int local_smem_bytes() { return CAP * 8 + CAP * 8 + (local_buckets(CAP) + 1) * 4 + local_buckets(CAP) * 4; }
+// The bucket tables (counts, starts) are read by threads that own CONSECUTIVE buckets during the scan: thread t reads
+// words t*PER ... t*PER + PER - 1, i.e. a warp reads with a stride of PER words and, unpadded, hits each bank PER
+// times (the scan then makes up almost half of the kernel's shared-memory traffic). One spare word per 32 spreads
+// such a warp over all banks.
+#ifndef FGS_LOCAL_PAD
+#define FGS_LOCAL_PAD 1
+#endif
+__host__ __device__ constexpr int bucket_slot(int i) { return FGS_LOCAL_PAD ? i + (i >> 5) : i; }
+template <int CAP> constexpr int local_smem_bytes() { return CAP * 8 + CAP * 8 + (bucket_slot(local_buckets(CAP)) + 1) * 4 + (bucket_slot(local_buckets(CAP)) + 1) * 4; }
 
 #ifdef FGS_SORT_TIMING
 __device__ unsigned long long g_local_cycles[8];
@@ -1210,8 +1218,8 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     extern __shared__ __align__(16) unsigned char s_local[];
     uint64_t* a = reinterpret_cast<uint64_t*>(s_local);                         // [CAP] depth << 32 | low word, sorted
     uint64_t* bk = reinterpret_cast<uint64_t*>(s_local + CAP * 8);              // [CAP] the same entries, bucket by bucket
-    uint32_t* start = reinterpret_cast<uint32_t*>(s_local + CAP * 16);          // [NB + 1]
-    uint32_t* cursor = start + NB + 1;                                          // [NB]
+    uint32_t* start = reinterpret_cast<uint32_t*>(s_local + CAP * 16);          // [NB + 1], at bucket_slot()
+    uint32_t* cursor = start + bucket_slot(NB) + 1;                             // [NB], at bucket_slot()
     __shared__ uint32_t s_min, s_max, s_tile_word, s_wsum[THREADS / 32];
     __shared__ int s_piled;
     __shared__ int2 s_seg;   // the list the block sorts next; y < x: none
@@ -1245,7 +1253,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
     __syncthreads();   // the previous list's shared memory, and s_seg, are no longer read
     int next_ticket = 0;
     if (tid == 0) { s_min = 0xFFFFFFFFu; s_max = 0u; s_piled = 0; s_tile_word = (uint32_t)(kk[0] >> 32); next_ticket = atomicAdd(work_ticket, 1); }
-    for (int i = tid; i < NB; i += THREADS) cursor[i] = 0;
+    for (int i = tid; i <= bucket_slot(NB); i += THREADS) cursor[i] = 0;
     FGS_LT(0);
     // The depths stay in registers until they are placed. The high words of a list's keys all hold the tile,
     // unless the caller left bits above the sorted width in them; "mixed" records that, and the write-out then
@@ -1299,7 +1307,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
             const int i = tid + q * THREADS;
             if (i < n) {
                 const int b = bucket_of(d[q]);
-                if (FGS_INDEX_OK(b, NB)) where[q] = (uint32_t)b | (atomicAdd(&cursor[b], 1u) << 16);
+                if (FGS_INDEX_OK(b, NB)) where[q] = (uint32_t)b | (atomicAdd(&cursor[bucket_slot(b)], 1u) << 16);
             }
         }
         int2 next_seg = make_int2(0, -1);
@@ -1310,7 +1318,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
         constexpr int PER = NB / THREADS;
         uint32_t sum = 0, biggest = 0;
 #pragma unroll
-        for (int q = 0; q < PER; q++) { const uint32_t c = cursor[tid * PER + q]; sum += c; biggest = max(biggest, c); }
+        for (int q = 0; q < PER; q++) { const uint32_t c = cursor[bucket_slot(tid * PER + q)]; sum += c; biggest = max(biggest, c); }
         if (biggest > LOCAL_BUCKET_LIMIT) s_piled = 1;
         uint32_t inc = sum;
 #pragma unroll
@@ -1323,8 +1331,8 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
         uint32_t off = inc - sum;
         for (int ww = 0; ww < warp; ww++) off += s_wsum[ww];
 #pragma unroll
-        for (int q = 0; q < PER; q++) { start[tid * PER + q] = off; off += cursor[tid * PER + q]; }
-        if (tid == THREADS - 1) start[NB] = off;
+        for (int q = 0; q < PER; q++) { start[bucket_slot(tid * PER + q)] = off; off += cursor[bucket_slot(tid * PER + q)]; }
+        if (tid == THREADS - 1) start[bucket_slot(NB)] = off;
         if (tid == 0) s_seg = next_seg;
         __syncthreads();
         FGS_LT(3);
@@ -1332,8 +1340,10 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
 #pragma unroll
             for (int q = 0; q < ITEMS; q++) {
                 const int i = tid + q * THREADS;
-                if (i < n && FGS_INDEX_OK(start[where[q] & 0xFFFFu] + (where[q] >> 16), n))
-                    bk[start[where[q] & 0xFFFFu] + (where[q] >> 16)] = ((uint64_t)d[q] << 32) | low[q];
+                if (i < n) {
+                    const uint32_t at = start[bucket_slot((int)(where[q] & 0xFFFFu))] + (where[q] >> 16);
+                    if (FGS_INDEX_OK(at, n)) bk[at] = ((uint64_t)d[q] << 32) | low[q];
+                }
             }
             fetch(s_seg);   // the registers are free again: request the next list's keys
             fetched = true;
@@ -1348,7 +1358,7 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
             for (int x = tid; x < n; x += THREADS) {
                 const uint64_t kc = bk[x];
                 const int bkt = bucket_of((uint32_t)(kc >> 32));
-                const int s0 = (int)start[bkt], s1 = (int)start[bkt + 1];
+                const int s0 = (int)start[bucket_slot(bkt)], s1 = (int)start[bucket_slot(bkt + 1)];
                 int rank = 0;
                 for (int y = s0; y < s1; y++) {
                     const uint64_t other = bk[y];
