@@ -230,6 +230,8 @@ def main():
                     help="only the view batch: all views of the workload (C5: 64), dealt out to the ranks")
     ap.add_argument("--view-passes", type=int, default=2)
     ap.add_argument("--view-gaussians", type=int, default=None, help="override the view batch's Gaussian count")
+    ap.add_argument("--no-tile-order", action="store_true",
+                    help="the blend takes the tiles up in row-major order instead of heaviest first")
     ap.add_argument("--no-tile-counts", action="store_true",
                     help="the sort counts the pairs per tile itself (one more pass over the keys) instead of taking preprocess's table")
     ap.add_argument("--no-scene-bounds", action="store_true",
@@ -321,6 +323,9 @@ def main():
     use_scratch = ours and ras.cull_scratch is not None
     use_bounds = use_scratch and ras.scene_bounds is not None
     use_counts = ours and ras.tile_counts is not None
+    if args.no_tile_order or not ours:
+        ras.order_refresh = 0
+    use_order = ours and ras.order_refresh > 0
     config["preprocess_call"] = ("the reference's positional arguments plus cull_scratch= (the idle head of the sort's "
                                  "scratch, for the index list of the Gaussians that reach the image)"
                                  + (" and scene_bounds= (16-byte records prepared once per scene, outside the timed region, "
@@ -329,6 +334,10 @@ def main():
                                     "given the table and does not count them again)" if use_counts else "")
                                  + "; stages.preprocess.preprocess_plain_call_ms is the call without them") if use_scratch else \
         "the reference's positional arguments only"
+    if use_order:
+        config["render_call"] = ("the reference's positional arguments plus consumed= and tile_order=: the blend records what it "
+                                 "consumed per tile, and every %d frames that record becomes the order in which the tiles are taken "
+                                 "up, heaviest first (the refresh, a sort of the tile counts, is inside the timed region)" % ras.order_refresh)
     H, W = cam.height, cam.width
     PAD = 32   # spare rows: the reference writes past ragged images
     out_img = torch.zeros((H + PAD, W, 3), device=dev, dtype=torch.int8)
@@ -356,14 +365,15 @@ def main():
         ops.sort_gaussian(n, W, H, 16, 16, ras.list_sorting_space, ras.gaussian_keys_unsorted, ras.gaussian_values_unsorted,
                           ras.gaussian_keys_sorted, ras.gaussian_values_sorted, **extra)
 
-    def stage_render(n, rows=None, img=None):
+    def stage_render(n, rows=None, img=None, plain=False):
         img = out_img if img is None else img
+        extra = ras._tile_order_arguments(tc, rows) if use_order and not plain else {}
         if rows is None:
             ops.render_16x16(n, W, H, ras.points_xy, ras.rgb_depth, ras.conic_opacity, ras.gaussian_keys_sorted,
-                             ras.gaussian_values_sorted, ras.ranges, bg, img)
+                             ras.gaussian_values_sorted, ras.ranges, bg, img, **extra)
         else:
             ops.render_ex(16, 16, n, W, H, ras.points_xy, ras.rgb_depth, ras.conic_opacity, ras.gaussian_keys_sorted,
-                          ras.gaussian_values_sorted, ras.ranges, bg, out_color=img, tile_row_begin=rows[0], tile_row_end=rows[1])
+                          ras.gaussian_values_sorted, ras.ranges, bg, out_color=img, tile_row_begin=rows[0], tile_row_end=rows[1], **extra)
 
     # the pair count comes back through pinned memory (what `.cpu()` does in example.py:79, without its allocation)
     count_host = torch.zeros(1, dtype=torch.int32).pin_memory()
@@ -542,16 +552,16 @@ def main():
 
     # ---- the same frame through the reference's positional arguments only (no extension keyword at all) ----
     positional = None
-    if ours and (use_scratch or use_counts):
+    if ours and (use_scratch or use_counts or use_order):
         def positional_frame():
             stage_pre(rows, scratch=False)
             n = read_count()
             ops.sort_gaussian(n, W, H, 16, 16, ras.list_sorting_space, ras.gaussian_keys_unsorted, ras.gaussian_values_unsorted,
                               ras.gaussian_keys_sorted, ras.gaussian_values_sorted)
-            stage_render(n, rows)
+            stage_render(n, rows, plain=True)
         pos_ms = timed(positional_frame)
         positional = {"ms_per_step": pos_ms, "value": 1000.0 / pos_ms, "unit": "frames/s",
-                      "note": "preprocess and sort_gaussian called with the reference's positional arguments only"
+                      "note": "preprocess, sort_gaussian and render_16x16 called with the reference's positional arguments only"
                               + ("" if rows is None else " (plus the strip's tile rows)")}
 
     # ---- per-kernel times (CUDA events around every launch, through the library's measurement entry points) ----

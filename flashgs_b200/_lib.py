@@ -46,7 +46,7 @@ SIGNATURES = {
     "fgs_render_16x16": (_i, [_i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]),
     "fgs_render_32x16": (_i, [_i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]),
     "fgs_render_32x32": (_i, [_i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]),
-    "fgs_render_ex": (_i, [_i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _p, _p, _p, _p, _p]),
+    "fgs_render_ex": (_i, [_i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _p, _p, _p, _p, _p, _p]),
     "fgs_render_frame": (_i, [_i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _f, _f, _f, _f, _p, _p, _p, _p, _p, _p, _p, _p, _i64,
                               _p, C.c_size_t, _p, _p, _i, _i, _p, _p]),
     "fgs_tile_ranges": (_i, [_i, _i, _p, _p, _p]),

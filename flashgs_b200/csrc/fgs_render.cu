@@ -111,7 +111,7 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
              const float4* __restrict__ conic_opacity,
              float bg_r, float bg_g, float bg_b, int vector_store, int list_len, const int* __restrict__ list_len_dev,
              uint8_t* __restrict__ out_color, float* __restrict__ out_rgb, float* __restrict__ out_alpha,
-             float* __restrict__ out_depth, int* __restrict__ consumed)
+             float* __restrict__ out_depth, int* __restrict__ consumed, const int* __restrict__ tile_order, int row_end)
 {
     constexpr int TX = BX / 8, TY = BY / 4;
     __shared__ __align__(16) BlendStage s_stage[BLEND_WARPS][STAGES];
@@ -120,8 +120,16 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int strip_tile = blockIdx.x * BLEND_WARPS + warp;
     if (strip_tile >= num_strip_tiles) return;          // whole warp leaves; no block-wide barrier is used
-    const int tile_y = row_begin + strip_tile / grid_x;
-    const int tile_x = strip_tile - (strip_tile / grid_x) * grid_x;
+    // The warp's tile: the strip's tiles in row-major order, or in the order the caller asks for (heaviest first keeps
+    // the launch's tail short). An entry that is not a tile of the strip is ignored.
+    int tile_y = row_begin + strip_tile / grid_x;
+    int tile_x = strip_tile - (strip_tile / grid_x) * grid_x;
+    if (tile_order != nullptr) {
+        const int t = tile_order[strip_tile];
+        tile_y = t / grid_x;
+        tile_x = t - tile_y * grid_x;
+        if (t < 0 || tile_y < row_begin || tile_y >= row_end) return;
+    }
     const int tile = tile_y * grid_x + tile_x;
     int2 range = ranges[tile];
 #ifdef FGS_DEBUG_BOUNDS
@@ -242,7 +250,7 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
         if (!stop) used = n;
         cp_async_wait<0>();
     }
-    if (EXTRA && consumed && lane == 0) consumed[tile] = used;
+    if (consumed && lane == 0) consumed[tile] = used;
 
     // ---- write-out (render.cu:59-73; background-only tiles: render.cu:530-546, here bounds-checked) ----
     float T[TY][TX], Cr[TY][TX], Cg[TY][TX], Cb[TY][TX], D[TY][TX];
@@ -306,7 +314,7 @@ int launch_render(int num_rendered, int width, int height,
                   const uint64_t* keys_sorted, const uint32_t* values_sorted, int* ranges, const float* bg,
                   int row_begin, int row_end,
                   uint8_t* out_color, float* out_rgb, float* out_alpha, float* out_depth, int* consumed, cudaStream_t st,
-                  const int* n_dev = nullptr)
+                  const int* n_dev = nullptr, const int* tile_order = nullptr)
 {
     const int grid_x = (width + BX - 1) / BX, grid_y = (height + BY - 1) / BY;
     const int num_tiles = grid_x * grid_y;
@@ -318,19 +326,19 @@ int launch_render(int num_rendered, int width, int height,
     const int strip_tiles = (row_end - row_begin) * grid_x;
     const int blocks = (strip_tiles + BLEND_WARPS - 1) / BLEND_WARPS;
     const int vec = (out_color != nullptr) && (width % BX == 0) && aligned16(out_color);
-    const bool extra = out_rgb || out_alpha || out_depth || consumed;
+    const bool extra = out_rgb || out_alpha || out_depth;
     if (extra)
         blend_kernel<BX, BY, true><<<blocks, BLEND_WARPS * 32, 0, st>>>(
             reinterpret_cast<const int2*>(ranges), values_sorted, width, height, grid_x, row_begin, strip_tiles,
             reinterpret_cast<const float2*>(points_xy), reinterpret_cast<const float4*>(rgb_depth),
             reinterpret_cast<const float4*>(conic_opacity), bg[0], bg[1], bg[2], vec, num_rendered, n_dev,
-            out_color, out_rgb, out_alpha, out_depth, consumed);
+            out_color, out_rgb, out_alpha, out_depth, consumed, tile_order, row_end);
     else
         blend_kernel<BX, BY, false><<<blocks, BLEND_WARPS * 32, 0, st>>>(
             reinterpret_cast<const int2*>(ranges), values_sorted, width, height, grid_x, row_begin, strip_tiles,
             reinterpret_cast<const float2*>(points_xy), reinterpret_cast<const float4*>(rgb_depth),
             reinterpret_cast<const float4*>(conic_opacity), bg[0], bg[1], bg[2], vec, num_rendered, n_dev,
-            out_color, nullptr, nullptr, nullptr, nullptr);
+            out_color, nullptr, nullptr, nullptr, consumed, tile_order, row_end);
     return launch_status();
 }
 
@@ -435,7 +443,7 @@ extern "C" int fgs_render_ex(int block_x, int block_y, int num_rendered, int wid
                              int* ranges, const float* bg_color,
                              int tile_row_begin, int tile_row_end,
                              uint8_t* out_color, float* out_rgb, float* out_alpha, float* out_depth, int* consumed,
-                             void* stream)
+                             const int* tile_order, void* stream)
 {
     using namespace fgs;
     if (num_rendered < 0 || width <= 0 || height <= 0 || !ranges || !bg_color) return FGS_ERR_BAD_ARG;
@@ -446,7 +454,7 @@ extern "C" int fgs_render_ex(int block_x, int block_y, int num_rendered, int wid
     if (block_x == BX && block_y == BY)                                                                                \
         return launch_render<BX, BY>(num_rendered, width, height, points_xy, rgb_depth, conic_opacity, keys_sorted,     \
                                      values_sorted, ranges, bg_color, tile_row_begin, tile_row_end, out_color, out_rgb, \
-                                     out_alpha, out_depth, consumed, st);
+                                     out_alpha, out_depth, consumed, st, nullptr, tile_order);
     FGS_RENDER_CASE(16, 16)
     FGS_RENDER_CASE(32, 16)
     FGS_RENDER_CASE(32, 32)
@@ -462,7 +470,7 @@ extern "C" int fgs_render_ex(int block_x, int block_y, int num_rendered, int wid
         if (!out_color) return FGS_ERR_BAD_ARG;                                                                      \
         return fgs_render_ex(BX, BY, num_rendered, width, height, points_xy, rgb_depth, conic_opacity, keys_sorted,  \
                              values_sorted, ranges, bg_color, 0, -1, out_color, nullptr, nullptr, nullptr, nullptr,  \
-                             stream);                                                                                \
+                             nullptr, stream);                                                                       \
     }
 FGS_RENDER_ENTRY(fgs_render_16x16, 16, 16)
 FGS_RENDER_ENTRY(fgs_render_32x16, 32, 16)

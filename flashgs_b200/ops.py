@@ -198,7 +198,11 @@ def _check_frame_buffers(block_x, block_y, width, height, ranges, out_color, num
 
 
 def _render(fn_name, block_x, block_y, num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
-            gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color):
+            gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color, tile_order=None, consumed=None):
+    if tile_order is not None or consumed is not None:   # the keyword extensions live in the general entry point
+        return render_ex(block_x, block_y, num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
+                         gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color=out_color,
+                         consumed=consumed, tile_order=tile_order)
     f32 = torch.float32
     xy = _in(points_xy, "points_xy", f32)
     rd = _in(rgb_depth, "rgb_depth", f32)
@@ -219,31 +223,38 @@ def _render(fn_name, block_x, block_y, num_rendered, width, height, points_xy, r
 
 
 def render_16x16(num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
-                 gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color) -> None:
-    """csrc/pybind.cpp:170-188."""
+                 gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color,
+                 tile_order=None, consumed=None) -> None:
+    """csrc/pybind.cpp:170-188. Keyword extensions: see ``render_ex``."""
     _render("fgs_render_16x16", 16, 16, num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
-            gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color)
+            gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color, tile_order, consumed)
 
 
 def render_32x16(num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
-                 gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color) -> None:
-    """csrc/pybind.cpp:190-208."""
+                 gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color,
+                 tile_order=None, consumed=None) -> None:
+    """csrc/pybind.cpp:190-208. Keyword extensions: see ``render_ex``."""
     _render("fgs_render_32x16", 32, 16, num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
-            gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color)
+            gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color, tile_order, consumed)
 
 
 def render_32x32(num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
-                 gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color) -> None:
-    """csrc/pybind.cpp:210-228."""
+                 gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color,
+                 tile_order=None, consumed=None) -> None:
+    """csrc/pybind.cpp:210-228. Keyword extensions: see ``render_ex``."""
     _render("fgs_render_32x32", 32, 32, num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
-            gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color)
+            gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color, out_color, tile_order, consumed)
 
 
 def render_ex(block_x, block_y, num_rendered, width, height, points_xy, rgb_depth, conic_opacity,
               gaussian_keys_sorted, gaussian_values_sorted, ranges, bg_color,
               out_color=None, out_rgb=None, out_alpha=None, out_depth=None, consumed=None,
-              tile_row_begin: int = 0, tile_row_end: int = -1) -> None:
-    """General render call (no reference counterpart): strips of tile rows and optional float outputs."""
+              tile_row_begin: int = 0, tile_row_end: int = -1, tile_order=None) -> None:
+    """General render call (no reference counterpart): strips of tile rows, optional float outputs, the number of
+    splats blended per tile (``consumed``, int32 per tile of the frame) and the order in which the tiles are taken up
+    (``tile_order``, int32 whole-frame tile ids, every tile of the rendered rows once). The image does not depend on
+    the order, the time does: a launch ends with its slowest tiles, so ``tile_order_from(consumed, ...)`` of the
+    previous frame of the same view -- heaviest tiles first -- shortens its tail."""
     f32 = torch.float32
     bg = _host(bg_color, "bg_color", 3)
     ptr = lambda t: 0 if t is None else t.data_ptr()  # noqa: E731
@@ -261,12 +272,33 @@ def render_ex(block_x, block_y, num_rendered, width, height, points_xy, rgb_dept
             _out(t, nm, dt)
             if t.numel() < need:
                 raise RuntimeError("%s needs %d elements, has %d" % (nm, need, t.numel()))
+    order = None
+    if tile_order is not None:
+        order = _in(tile_order, "tile_order", torch.int32)
+        gx = (int(width) + int(block_x) - 1) // int(block_x)
+        gy = (int(height) + int(block_y) - 1) // int(block_y)
+        r0 = max(0, int(tile_row_begin))
+        r1 = gy if int(tile_row_end) < 0 or int(tile_row_end) > gy else int(tile_row_end)
+        if not tile_order.is_contiguous() or order.numel() < max(0, r1 - r0) * gx:
+            raise RuntimeError("tile_order needs one contiguous entry per tile of the rendered rows (%d)" % (max(0, r1 - r0) * gx))
     st = _L.fgs_render_ex(int(block_x), int(block_y), int(num_rendered), int(width), int(height),
                           xy.data_ptr(), rd.data_ptr(), co.data_ptr(), ks.data_ptr(), vs.data_ptr(),
                           rg.data_ptr(), bg.data_ptr(),
                           int(tile_row_begin), int(tile_row_end),
-                          ptr(out_color), ptr(out_rgb), ptr(out_alpha), ptr(out_depth), ptr(consumed), _stream())
+                          ptr(out_color), ptr(out_rgb), ptr(out_alpha), ptr(out_depth), ptr(consumed),
+                          None if order is None else order.data_ptr(), _stream())
     _lib.check("render_ex", st)
+
+
+def tile_order_from(consumed, width, height, block_x: int = 16, block_y: int = 16, tile_row_begin: int = 0, tile_row_end: int = -1):
+    """The tiles of the rendered rows in descending order of ``consumed`` (what ``render_ex(..., consumed=)`` wrote for
+    an earlier frame of the same view), as the int32 tensor ``render_ex(..., tile_order=)`` takes."""
+    gx = (int(width) + block_x - 1) // block_x
+    gy = (int(height) + block_y - 1) // block_y
+    r0 = max(0, int(tile_row_begin))
+    r1 = gy if int(tile_row_end) < 0 or int(tile_row_end) > gy else int(tile_row_end)
+    part = consumed[r0 * gx: r1 * gx]
+    return (torch.argsort(part, descending=True, stable=True) + r0 * gx).to(torch.int32)
 
 
 def render_frame(orig_points, shs, opacities, cov3Ds, width, height, block_x, block_y,

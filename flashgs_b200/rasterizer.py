@@ -80,6 +80,11 @@ class Rasterizer:
                              if self.cull_scratch is not None and hasattr(ops, "prepare_scene") else None)
         # preprocess knows every pair's tile when it emits it: it counts the pairs per tile for the sort that follows
         self.tile_counts = z(65536, torch.int32) if ours else None
+        # Tiles are taken up heaviest first (by what the blend consumed per tile a few frames ago): a launch ends with its
+        # slowest tiles. The order is refreshed every `order_refresh` frames; 0 turns it off.
+        self.order_refresh = 16 if ours and hasattr(ops, "tile_order_from") else 0
+        self.tile_consumed = z(MAX_NUM_TILES, torch.int32) if self.order_refresh else None
+        self._order, self._order_key, self._frames = None, None, 0
         self._render = {(16, 16): "render_16x16", (32, 16): "render_32x16", (32, 32): "render_32x32"}[tuple(block)]
 
     def forward(self, scene: DeviceScene, camera, bg_color, out_color=None, rows=None):
@@ -112,18 +117,40 @@ class Rasterizer:
                           self.gaussian_keys_sorted, self.gaussian_values_sorted, **sort_extra)
         if out_color is None:
             out_color = torch.zeros((camera.height, camera.width, 3), device=scene.device, dtype=torch.int8)
+        order_extra = self._tile_order_arguments(camera, rows)
         if rows is None:
             getattr(ops, self._render)(num_rendered, camera.width, camera.height,
                                        self.points_xy, self.rgb_depth, self.conic_opacity,
                                        self.gaussian_keys_sorted, self.gaussian_values_sorted,
-                                       self.ranges, bg_color, out_color)
+                                       self.ranges, bg_color, out_color, **order_extra)
         else:
             ops.render_ex(bx, by, num_rendered, camera.width, camera.height,
                           self.points_xy, self.rgb_depth, self.conic_opacity,
                           self.gaussian_keys_sorted, self.gaussian_values_sorted,
                           self.ranges, bg_color, out_color=out_color,
-                          tile_row_begin=rows[0], tile_row_end=rows[1])
+                          tile_row_begin=rows[0], tile_row_end=rows[1], **order_extra)
         return out_color
+
+    def _tile_order_arguments(self, camera, rows):
+        """Keyword arguments of the render call that concern the order of the tiles: every frame the blend records what
+        it consumed per tile; every ``order_refresh`` frames of one (image size, strip) that record becomes the order."""
+        if not self.order_refresh:
+            return {}
+        bx, by = self.block
+        tiles = ((camera.width + bx - 1) // bx) * ((camera.height + by - 1) // by)
+        if tiles > self.tile_consumed.numel():
+            return {}
+        key = (camera.width, camera.height, rows)
+        if key != self._order_key:
+            self._order, self._order_key, self._frames = None, key, 0
+        elif self._frames % self.order_refresh == 1:      # the previous frame of this view has left its counts
+            r = rows or (0, -1)
+            self._order = self.ops.tile_order_from(self.tile_consumed[:tiles], camera.width, camera.height, bx, by, r[0], r[1])
+        self._frames += 1
+        extra = {"consumed": self.tile_consumed[:tiles]}
+        if self._order is not None:
+            extra["tile_order"] = self._order
+        return extra
 
 
     def forward_fused(self, scene: DeviceScene, camera, bg_color, out_color=None, rows=None):

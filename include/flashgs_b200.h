@@ -278,6 +278,11 @@ int fgs_render_32x32(int num_rendered, int width, int height,
  *   consumed [tiles] = number of splats blended per tile (the reference's stop rule,
  *                      csrc/cuda_rasterizer/render.cu:315,394-407)
  * out_color may be NULL when only float outputs are wanted.
+ *   tile_order [tiles of the rendered rows]  (may be NULL) the order in which the tiles are taken up, as whole-frame
+ *                      tile ids; every tile of the rendered rows must appear once (an entry outside them is ignored,
+ *                      a tile that is missing is not rendered). The image does not depend on the order; the time
+ *                      does: the launch ends with its slowest tiles, so handing over the tiles in descending order of
+ *                      the `consumed` counts of the previous frame of the same view shortens its tail.
  */
 int fgs_render_ex(int block_x, int block_y, int num_rendered, int width, int height,
                   const float* points_xy, const float* rgb_depth, const float* conic_opacity,
@@ -285,7 +290,7 @@ int fgs_render_ex(int block_x, int block_y, int num_rendered, int width, int hei
                   int* ranges, const float* bg_color,
                   int tile_row_begin, int tile_row_end,
                   uint8_t* out_color, float* out_rgb, float* out_alpha, float* out_depth, int* consumed,
-                  void* stream);
+                  const int* tile_order, void* stream);
 
 /*
  * One whole frame in a single call that never waits for the GPU: zero the pair counter, preprocess (optionally a

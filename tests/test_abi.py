@@ -69,7 +69,7 @@ def test_argument_checks_need_no_gpu():
     assert lib.fgs_sort_pairs(0, 64, 64, 16, 16, None, 0, None, None, None, None, None) == _lib.OK
     assert lib.fgs_sort_pairs(5, 64, 64, 16, 16, None, 0, None, None, None, None, None) == _lib.ERR_BAD_ARG
     assert lib.fgs_render_ex(8, 8, 0, 64, 64, None, None, None, None, None, None, None, 0, -1,
-                             None, None, None, None, None, None) == _lib.ERR_BAD_ARG
+                             None, None, None, None, None, None, None) == _lib.ERR_BAD_ARG
     assert lib.fgs_preprocess(-1, *([None] * 4), 64, 64, 16, 16, None, None, 1.0, 1.0, 100.0, 0.01,
                               *([None] * 5), 0, None, None) == _lib.ERR_BAD_ARG
     assert lib.fgs_tile_ranges(0, 0, None, None, None) == _lib.ERR_BAD_ARG

@@ -743,3 +743,74 @@ def test_sort_from_preprocess_tile_counts(ops, oracle_lib):
     assert ops.device_status() & _lib.ERR_BAD_ARG
     assert (guard_k[a.R:] == -7).all() and (guard_v[a.R:] == -7).all()
     assert ops.device_status() == 0
+
+
+def test_tile_order_changes_nothing_but_the_time(ops, oracle_lib):
+    """The blend may be told in which order to take the tiles up (heaviest first shortens a launch's tail). Whatever the
+    order, the image is the same bytes, the per-tile consumed counts are the oracle's, and an entry that is not a tile
+    of the rendered rows is ignored."""
+    w, sc, cams = scenes.make_workload("C1", 40000)
+    cam = cams[0]
+    f = Frame(ops, sc, cam)                       # float outputs and consumed counts through the general kernel
+    o = oracle_lib.render_frame(sc, cam)
+    gx, gy = scenes.tile_grid(cam.width, cam.height)
+    T = gx * gy
+    bg = torch.zeros(3)
+    rng = np.random.default_rng(4)
+
+    def render(order=None, rows=(0, -1), consumed=None):
+        img = torch.full((cam.height, cam.width, 3), 0x33, device=DEV, dtype=torch.uint8)
+        ops.render_16x16(f.R, cam.width, cam.height, f.xy, f.rd, f.co, f.ks, f.vs, f.ranges, bg, img,
+                         tile_order=order, consumed=consumed) if rows == (0, -1) else \
+            ops.render_ex(16, 16, f.R, cam.width, cam.height, f.xy, f.rd, f.co, f.ks, f.vs, f.ranges, bg, out_color=img,
+                          tile_row_begin=rows[0], tile_row_end=rows[1], tile_order=order, consumed=consumed)
+        torch.cuda.synchronize()
+        return img.cpu().numpy()
+
+    natural = render()
+    d = np.abs(natural.astype(int) - f.np("img").astype(int))      # the kernel with float outputs beside it
+    assert d.max() <= 1 and (d > 0).mean() <= 1e-5
+    consumed = torch.full((T,), -1, device=DEV, dtype=torch.int32)
+    shuffled = render(order=_t(rng.permutation(T).astype(np.int32)), consumed=consumed)
+    assert (shuffled == natural).all()
+    assert (consumed.cpu().numpy() == f.np("consumed")).all()
+    assert (consumed.cpu().numpy() == o["consumed"]).mean() >= 0.999
+    # heaviest first, as the frame loop uses it
+    order = ops.tile_order_from(consumed, cam.width, cam.height)
+    assert order.dtype == torch.int32 and sorted(order.tolist()) == list(range(T))
+    c = consumed.cpu().numpy()[order.cpu().numpy()]
+    assert (c[1:] <= c[:-1]).all()
+    assert (render(order=order) == natural).all()
+    # a strip with its own order; entries outside the strip (and negative ones) are ignored, their slots render nothing
+    rows = (gy // 4, gy // 2)
+    strip_order = ops.tile_order_from(consumed, cam.width, cam.height, 16, 16, rows[0], rows[1])
+    assert strip_order.numel() == (rows[1] - rows[0]) * gx
+    strip = render(order=strip_order, rows=rows)
+    y0, y1 = rows[0] * 16, rows[1] * 16
+    assert (strip[y0:y1] == natural[y0:y1]).all() and (strip[:y0] == 0x33).all() and (strip[y1:] == 0x33).all()
+    bad = strip_order.clone()
+    bad[0], bad[1], bad[2] = 0, T + 5, -3          # a tile of another strip, a tile beyond the grid, a negative entry
+    part = render(order=bad, rows=rows)
+    assert (part[:y0] == 0x33).all() and (part[y1:] == 0x33).all()
+    skipped = strip_order[:3].cpu().numpy()
+    for t in range(T):
+        ty, tx = divmod(t, gx)
+        if not (rows[0] <= ty < rows[1]):
+            continue
+        tile = part[ty * 16:(ty + 1) * 16, tx * 16:(tx + 1) * 16]
+        if t in skipped:
+            assert (tile == 0x33).all()
+        else:
+            assert (tile == natural[ty * 16:(ty + 1) * 16, tx * 16:(tx + 1) * 16]).all()
+    with pytest.raises(RuntimeError):
+        render(order=strip_order[:5], rows=rows)          # too short for the rendered rows
+    # the frame loop: the order appears after a few frames of one view and leaves the image alone
+    from flashgs_b200.rasterizer import DeviceScene, Rasterizer, TorchCamera
+    ds = DeviceScene(sc, DEV)
+    ras = Rasterizer(ds, 1 << 21, 1 << 12)
+    ras.order_refresh = 2
+    imgs = [ras.forward(ds, TorchCamera(cam), bg).cpu().numpy().view(np.uint8) for _ in range(5)]
+    assert ras._order is not None
+    for im in imgs:
+        assert (im == natural).all()
+    assert ops.device_status() == 0
