@@ -542,8 +542,12 @@ def main():
                 ras.forward_fused(ds, tc, bg, out_color=out_img, rows=rows)
             torch.cuda.current_stream().wait_stream(side)
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                ras.forward_fused(ds, tc, bg, out_color=out_img, rows=rows)
+            refresh, ras.order_refresh = ras.order_refresh, (1 << 30 if use_order else 0)   # the captured frame keeps the
+            try:                                                                           # tile order it has, no refresh inside
+                with torch.cuda.graph(graph):
+                    ras.forward_fused(ds, tc, bg, out_color=out_img, rows=rows)
+            finally:
+                ras.order_refresh = refresh
             graph_ms = timed(graph.replay)
             fused["graph_ms_per_step"] = graph_ms
             fused["graph_value"] = 1000.0 / graph_ms

@@ -389,7 +389,8 @@ extern "C" int fgs_render_frame(int P, const float* positions, const float* shs,
                                 uint64_t* keys_unsorted, uint32_t* values_unsorted,
                                 uint64_t* keys_sorted, uint32_t* values_sorted, int64_t pair_capacity,
                                 void* sort_temp, size_t sort_temp_bytes, int* ranges, int* curr_offset,
-                                int tile_row_begin, int tile_row_end, uint8_t* out_color, void* stream)
+                                int tile_row_begin, int tile_row_end, uint8_t* out_color,
+                                int* consumed, const int* tile_order, void* stream)
 {
     using namespace fgs;
     if (pair_capacity <= 0 || pair_capacity >= (1 << 30) || !curr_offset || !out_color || !bg_color || !ranges) return FGS_ERR_BAD_ARG;
@@ -421,7 +422,7 @@ extern "C" int fgs_render_frame(int P, const float* positions, const float* shs,
     if (block_x == BX && block_y == BY)                                                                                 \
         return launch_render<BX, BY>((int)pair_capacity, width, height, points_xy, rgb_depth, conic_opacity, keys_sorted, \
                                      values_sorted, ranges, bg_color, tile_row_begin, tile_row_end, out_color, nullptr,  \
-                                     nullptr, nullptr, nullptr, st, curr_offset);
+                                     nullptr, nullptr, consumed, st, curr_offset, tile_order);
     FGS_FRAME_CASE(16, 16)
     FGS_FRAME_CASE(32, 16)
     FGS_FRAME_CASE(32, 32)

@@ -306,7 +306,7 @@ def render_frame(orig_points, shs, opacities, cov3Ds, width, height, block_x, bl
                  points_xy, rgb_depth, conic_opacity,
                  gaussian_keys_unsorted, gaussian_values_unsorted, gaussian_keys_sorted, gaussian_values_sorted,
                  list_sorting_space, ranges, curr_offset, out_color,
-                 tile_row_begin: int = 0, tile_row_end: int = -1) -> None:
+                 tile_row_begin: int = 0, tile_row_end: int = -1, consumed=None, tile_order=None) -> None:
     """One frame in one call with no host round trip (no reference counterpart): what ``preprocess``,
     ``sort_gaussian`` and ``render_*`` do in sequence, the pair count staying in ``curr_offset`` on the device.
     Read ``curr_offset`` afterwards if the count is wanted; an overflow of the pair buffers shows in ``device_status``."""
@@ -328,7 +328,15 @@ def render_frame(orig_points, shs, opacities, cov3Ds, width, height, block_x, bl
     P = int(op.size(0))
     xy, rd, co = _out(points_xy, "points_xy", f32), _out(rgb_depth, "rgb_depth", f32), _out(conic_opacity, "conic_opacity", f32)
     rg = _out(ranges, "ranges", torch.int32)
-    _check_frame_buffers(int(block_x), int(block_y), width, height, rg, out_color)
+    tiles = _check_frame_buffers(int(block_x), int(block_y), width, height, rg, out_color)
+    if (consumed is not None and consumed.numel() < tiles) or (tile_order is not None and not tile_order.is_contiguous()):
+        raise RuntimeError("consumed needs one element per tile (%d); tile_order must be contiguous" % tiles)
+    if tile_order is not None:
+        gx = (int(width) + int(block_x) - 1) // int(block_x)
+        gy = (int(height) + int(block_y) - 1) // int(block_y)
+        r1 = gy if int(tile_row_end) < 0 or int(tile_row_end) > gy else int(tile_row_end)
+        if tile_order.numel() < max(0, r1 - max(0, int(tile_row_begin))) * gx:
+            raise RuntimeError("tile_order needs one entry per tile of the rendered rows")
     if xy.numel() < 2 * P or rd.numel() < 4 * P or co.numel() < 4 * P:
         raise RuntimeError("points_xy, rgb_depth and conic_opacity need one record per Gaussian (%d)" % P)
     st = _L.fgs_render_frame(P, _in(orig_points, "orig_points", f32).data_ptr(), _in(shs, "shs", f32).data_ptr(),
@@ -339,7 +347,9 @@ def render_frame(orig_points, shs, opacities, cov3Ds, width, height, block_x, bl
                              ku.data_ptr(), vu.data_ptr(), ks.data_ptr(), vs.data_ptr(), cap,
                              tmp.data_ptr(), tmp.numel() * tmp.element_size(),
                              rg.data_ptr(), _out(curr_offset, "curr_offset", torch.int32).data_ptr(),
-                             int(tile_row_begin), int(tile_row_end), out_color.data_ptr(), _stream())
+                             int(tile_row_begin), int(tile_row_end), out_color.data_ptr(),
+                             None if consumed is None else _out(consumed, "consumed", torch.int32).data_ptr(),
+                             None if tile_order is None else _in(tile_order, "tile_order", torch.int32).data_ptr(), _stream())
     _lib.check("render_frame", st)
 
 

@@ -624,6 +624,15 @@ def test_fused_frame_equals_stage_calls(ops, oracle_lib):
                                         ras.gaussian_values_sorted[:R].cpu().numpy().view(np.uint32))).all()
         d = np.abs(a.astype(int) - b.astype(int))
         assert d.max() <= 1 and (d > 0).mean() <= 1e-5
+        # that call took the tiles up heaviest first (the order comes from the first frame's consumed counts) and left
+        # its own counts; further frames, whatever order they use, are the same bytes
+        gxy = scenes.tile_grid(cam.width, cam.height, *block)
+        T = gxy[0] * gxy[1]
+        assert ras._order is not None and ras._order.numel() == T
+        consumed = ras.tile_consumed[:T].clone()
+        for _ in range(2):
+            assert (ras.forward_fused(ds, tc, bg).cpu().numpy().view(np.uint8) == b).all()
+            assert (ras.tile_consumed[:T] == consumed).all()
         # a strip through the fused call
         gy = scenes.tile_grid(cam.width, cam.height, *block)[1]
         rows = (gy // 3, 2 * gy // 3)
