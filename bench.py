@@ -230,6 +230,8 @@ def main():
                     help="only the view batch: all views of the workload (C5: 64), dealt out to the ranks")
     ap.add_argument("--view-passes", type=int, default=2)
     ap.add_argument("--view-gaussians", type=int, default=None, help="override the view batch's Gaussian count")
+    ap.add_argument("--no-chained-launches", action="store_true",
+                    help="plain kernel launches instead of programmatic dependent launches")
     ap.add_argument("--no-tile-order", action="store_true",
                     help="the blend takes the tiles up in row-major order instead of heaviest first")
     ap.add_argument("--no-tile-counts", action="store_true",
@@ -326,6 +328,11 @@ def main():
     if args.no_tile_order or not ours:
         ras.order_refresh = 0
     use_order = ours and ras.order_refresh > 0
+    if ours:
+        from flashgs_b200 import _lib as _fgs_lib
+        _fgs_lib.load().fgs_debug_chained_launches(0 if args.no_chained_launches else 1)
+        config["launches"] = ("plain" if args.no_chained_launches else
+                              "programmatic dependent launch: a kernel's blocks are resident and waiting when the kernel before it ends")
     config["preprocess_call"] = ("the reference's positional arguments plus cull_scratch= (the idle head of the sort's "
                                  "scratch, for the index list of the Gaussians that reach the image)"
                                  + (" and scene_bounds= (16-byte records prepared once per scene, outside the timed region, "

@@ -54,7 +54,8 @@ SIGNATURES = {
     "fgs_ply_load": (_i, [C.c_char_p, C.c_longlong, _p, _p, _p, _p]),
 }
 
-TEST_HOOKS = ("fgs_debug_preprocess_no_column_cull", "fgs_debug_sort_plain", "fgs_debug_sort_skip_publish")
+TEST_HOOKS = ("fgs_debug_preprocess_no_column_cull", "fgs_debug_sort_plain", "fgs_debug_sort_skip_publish",
+              "fgs_debug_chained_launches")
 CHECKED_HOOKS = ("fgs_debug_bounds_report", "fgs_debug_bounds_selftest")   # exported by the checked flavour only
 LIB_CHECKED_PATH = os.path.join(HERE, "libflashgs_b200_checked.so")
 ERR_BOUNDS = 32

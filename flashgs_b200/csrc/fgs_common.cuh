@@ -43,6 +43,40 @@ __device__ __forceinline__ unsigned lanemask_lt()
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---- chained launches (programmatic dependent launch) ----
+// The kernels of a frame follow one another on one stream, each needing the one before it complete. Launched with the
+// programmatic-serialization attribute, a kernel's blocks may become resident while the kernel before it is still
+// draining -- once every block of that kernel has started and executed chain_release() -- and stop at chain_wait()
+// until it has completed and its writes are visible. What overlaps is launch latency and ramp-up, nothing else:
+// chain_wait() is the first statement of every kernel launched this way, so no kernel touches memory before all
+// earlier work on the stream is complete (a kernel's completion implies that of everything before it, because it
+// waited itself). Under stream capture, and when switched off (test hook), the launch is a plain one and
+// chain_wait() returns at once.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int g_chained_launches;   // fgs_host.cu; fgs_debug_chained_launches()
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t chain_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 0;
+    if (g_chained_launches) {
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &capturing) == cudaSuccess && capturing == cudaStreamCaptureStatusNone) cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- checked build (-DFGS_DEBUG_BOUNDS) ----
 // Every global store, every index computed from data (a Gaussian index read from a list, a destination derived
 // from counters) and every computed shared-memory index is compared with the extent of what it addresses before the

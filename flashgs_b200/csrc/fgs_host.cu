@@ -69,6 +69,11 @@ void host_view_proj(int width, int height, const float* pos, const float* rot, f
 
 } // namespace fgs
 
+namespace fgs { int g_chained_launches = 1; }
+
+// Test hook: zero makes every kernel launch a plain one (no programmatic dependent launch).
+extern "C" void fgs_debug_chained_launches(int on) { fgs::g_chained_launches = on; }
+
 extern "C" int fgs_abi_version(void) { return FGS_ABI_VERSION; }
 
 extern "C" const char* fgs_status_string(int status)

@@ -289,6 +289,8 @@ strip_cull_kernel(int P, const float* __restrict__ positions, const float* __res
                   const float* __restrict__ cov3ds, const float4* __restrict__ bounds,
                   const __grid_constant__ PreCam cam, int* __restrict__ list)
 {
+    chain_release();
+    chain_wait();   // nothing is read or written before the kernels ahead on the stream are complete
     // A block looks at CULL_PER_BLOCK consecutive Gaussians, 256 at a time; every warp collects the indices it keeps
     // in its own shared-memory region, and the block appends all of them to the list with ONE atomicAdd at the end
     // (every block adds to the same counter: one add per 256 Gaussians made the kernel wait on that word).
@@ -394,6 +396,8 @@ preprocess_kernel(int P,
                   int* __restrict__ curr_offset, int* __restrict__ status, const int* __restrict__ list,
                   unsigned* __restrict__ tile_count)
 {
+    chain_release();
+    chain_wait();   // nothing is read or written before the kernels ahead on the stream are complete
     __shared__ __align__(16) float s_pos[PRE_THREADS * 3];
     __shared__ __align__(16) float s_cov[PRE_THREADS * 6];
     __shared__ __align__(16) float s_opa[PRE_THREADS];
@@ -794,18 +798,18 @@ static int preprocess_impl(int P, const float* positions, const float* shs, cons
         if (cudaMemsetAsync(cull_scratch, 0, sizeof(int), st) != cudaSuccess) return FGS_ERR_CUDA;
         const int cull_blocks = (P + CULL_PER_BLOCK - 1) / CULL_PER_BLOCK;
         if (scene_bounds != nullptr && aligned16(scene_bounds))
-            strip_cull_kernel<true><<<cull_blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, reinterpret_cast<const float4*>(scene_bounds), cam, cull_scratch);
+            chain_launch(strip_cull_kernel<true>, dim3(cull_blocks), dim3(PRE_THREADS), 0, st, P, positions, opacities, cov3ds, reinterpret_cast<const float4*>(scene_bounds), cam, cull_scratch);
         else
-            strip_cull_kernel<false><<<cull_blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, nullptr, cam, cull_scratch);
+            chain_launch(strip_cull_kernel<false>, dim3(cull_blocks), dim3(PRE_THREADS), 0, st, P, positions, opacities, cov3ds, nullptr, cam, cull_scratch);
         list = cull_scratch;
     }
     if (events) cudaEventRecord(events[1], st);
     if (vec)
-        preprocess_kernel<true><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,
+        chain_launch(preprocess_kernel<true>, dim3(blocks), dim3(PRE_THREADS), 0, st, P, positions, opacities, cov3ds, shs, cam,
             reinterpret_cast<float2*>(points_xy), reinterpret_cast<float4*>(rgb_depth), reinterpret_cast<float4*>(conic_opacity),
             keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status, list, tile_counts);
     else
-        preprocess_kernel<false><<<blocks, PRE_THREADS, 0, st>>>(P, positions, opacities, cov3ds, shs, cam,
+        chain_launch(preprocess_kernel<false>, dim3(blocks), dim3(PRE_THREADS), 0, st, P, positions, opacities, cov3ds, shs, cam,
             reinterpret_cast<float2*>(points_xy), reinterpret_cast<float4*>(rgb_depth), reinterpret_cast<float4*>(conic_opacity),
             keys_unsorted, values_unsorted, (long long)pair_capacity, curr_offset, status, list, tile_counts);
     if (events) cudaEventRecord(events[2], st);

@@ -42,6 +42,8 @@ constexpr int RANGE_TILES = 256, RANGE_THREADS = RANGE_TILES + 32;
 __global__ void tile_ranges_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict__ n_dev, int num_tiles,
                                    int2* __restrict__ ranges)
 {
+    chain_release();
+    chain_wait();   // nothing is read or written before the kernels ahead on the stream are complete
     const int tile = blockIdx.x * RANGE_TILES + threadIdx.x;
     if (n_dev != nullptr) {   // count produced on the device by the same frame (bounded by the buffers' capacity n)
         const int v = *n_dev;
@@ -113,6 +115,8 @@ blend_kernel(const int2* __restrict__ ranges, const uint32_t* __restrict__ point
              uint8_t* __restrict__ out_color, float* __restrict__ out_rgb, float* __restrict__ out_alpha,
              float* __restrict__ out_depth, int* __restrict__ consumed, const int* __restrict__ tile_order, int row_end)
 {
+    chain_release();
+    chain_wait();   // nothing is read or written before the kernels ahead on the stream are complete
     constexpr int TX = BX / 8, TY = BY / 4;
     __shared__ __align__(16) BlendStage s_stage[BLEND_WARPS][STAGES];
     __shared__ __align__(16) uint8_t s_out[BLEND_WARPS][BY][BX * 3];
@@ -320,7 +324,7 @@ int launch_render(int num_rendered, int width, int height,
     const int num_tiles = grid_x * grid_y;
     if (row_begin < 0) row_begin = 0;
     if (row_end < 0 || row_end > grid_y) row_end = grid_y;
-    tile_ranges_kernel<<<(num_tiles + RANGE_TILES - 1) / RANGE_TILES, RANGE_THREADS, 0, st>>>(keys_sorted, num_rendered, n_dev, num_tiles,
+    chain_launch(tile_ranges_kernel, dim3((num_tiles + RANGE_TILES - 1) / RANGE_TILES), dim3(RANGE_THREADS), 0, st, keys_sorted, num_rendered, n_dev, num_tiles,
                                                                reinterpret_cast<int2*>(ranges));
     if (row_end <= row_begin) return launch_status();
     const int strip_tiles = (row_end - row_begin) * grid_x;
@@ -328,13 +332,13 @@ int launch_render(int num_rendered, int width, int height,
     const int vec = (out_color != nullptr) && (width % BX == 0) && aligned16(out_color);
     const bool extra = out_rgb || out_alpha || out_depth;
     if (extra)
-        blend_kernel<BX, BY, true><<<blocks, BLEND_WARPS * 32, 0, st>>>(
+        chain_launch(blend_kernel<BX, BY, true>, dim3(blocks), dim3(BLEND_WARPS * 32), 0, st, 
             reinterpret_cast<const int2*>(ranges), values_sorted, width, height, grid_x, row_begin, strip_tiles,
             reinterpret_cast<const float2*>(points_xy), reinterpret_cast<const float4*>(rgb_depth),
             reinterpret_cast<const float4*>(conic_opacity), bg[0], bg[1], bg[2], vec, num_rendered, n_dev,
             out_color, out_rgb, out_alpha, out_depth, consumed, tile_order, row_end);
     else
-        blend_kernel<BX, BY, false><<<blocks, BLEND_WARPS * 32, 0, st>>>(
+        chain_launch(blend_kernel<BX, BY, false>, dim3(blocks), dim3(BLEND_WARPS * 32), 0, st, 
             reinterpret_cast<const int2*>(ranges), values_sorted, width, height, grid_x, row_begin, strip_tiles,
             reinterpret_cast<const float2*>(points_xy), reinterpret_cast<const float4*>(rgb_depth),
             reinterpret_cast<const float4*>(conic_opacity), bg[0], bg[1], bg[2], vec, num_rendered, n_dev,
@@ -433,7 +437,7 @@ extern "C" int fgs_render_frame(int P, const float* positions, const float* shs,
 extern "C" int fgs_tile_ranges(int num_rendered, int num_tiles, const uint64_t* keys_sorted, int* ranges, void* stream)
 {
     if (num_rendered < 0 || num_tiles <= 0 || !ranges || (num_rendered > 0 && !keys_sorted)) return FGS_ERR_BAD_ARG;
-    fgs::tile_ranges_kernel<<<(num_tiles + fgs::RANGE_TILES - 1) / fgs::RANGE_TILES, fgs::RANGE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+    fgs::chain_launch(fgs::tile_ranges_kernel, dim3((num_tiles + fgs::RANGE_TILES - 1) / fgs::RANGE_TILES), dim3(fgs::RANGE_THREADS), 0, static_cast<cudaStream_t>(stream), 
         keys_sorted, num_rendered, nullptr, num_tiles, reinterpret_cast<int2*>(ranges));
     return fgs::launch_status();
 }

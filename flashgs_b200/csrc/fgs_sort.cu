@@ -144,6 +144,8 @@ __global__ void clear_bookkeeping_kernel(uint32_t* __restrict__ base_words, size
                                          int slots, int parts_stride, int n, const int* __restrict__ n_dev,
                                          size_t keep_begin, size_t keep_end)
 {
+    chain_release();
+    chain_wait();   // nothing is read or written before the kernels ahead on the stream are complete
     n = device_count(n, n_dev);
     const int parts = (n + SORT_PART - 1) / SORT_PART;
     const size_t per_slot = (size_t)parts * RADIX;
@@ -663,6 +665,8 @@ __global__ void __launch_bounds__(TILE_HIST_THREADS, 1)
 tile_hist_kernel(const uint64_t* __restrict__ keys, int n, const int* __restrict__ n_dev, uint32_t tile_mask, int tile_values,
                  int in_smem, uint32_t* __restrict__ tile_count)
 {
+    chain_release();
+    chain_wait();   // nothing is read or written before the kernels ahead on the stream are complete
     extern __shared__ __align__(16) uint32_t s_tiles[];
     n = device_count(n, n_dev);
     if (in_smem) {
@@ -711,6 +715,8 @@ tile_scan_kernel(const uint32_t* __restrict__ tile_count, int tile_values, int l
                  int* class_count, uint32_t* __restrict__ class_tiles,
                  int n_pairs, const int* __restrict__ n_dev, int* __restrict__ dev_status, uint32_t* done_ticket)
 {
+    chain_release();
+    chain_wait();   // nothing is read or written before the kernels ahead on the stream are complete
     constexpr int WARPS = TILE_SCAN_THREADS / 32;
     __shared__ uint32_t s_wsum[2][WARPS];
     __shared__ uint32_t s_units[MAX_BUCKETS];
@@ -833,6 +839,8 @@ multisplit_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restri
                   int n, const int* __restrict__ n_dev, uint32_t tile_mask, int lo_bits, int buckets,
                   const uint32_t* bucket_tables, uint32_t* cursors)
 {
+    chain_release();
+    chain_wait();   // nothing is read or written before the kernels ahead on the stream are complete
     extern __shared__ __align__(16) unsigned char s_ms[];      // reordered partition: keys [MS_PART], values [MS_PART]
     __shared__ uint32_t s_cnt[MS_DIGITS];                       // pairs per digit value in this partition
     __shared__ uint32_t s_lstart[MS_DIGITS];                    // where a digit's run starts in the reordered partition
@@ -1144,6 +1152,8 @@ long_list_kernel(uint64_t* keys_grouped, uint32_t* vals_grouped, uint64_t* keys_
                  const int2* __restrict__ seg, const int* __restrict__ work_count, const uint32_t* __restrict__ work_tiles,
                  int* __restrict__ work_ticket)
 {
+    chain_release();
+    chain_wait();   // nothing is read or written before the kernels ahead on the stream are complete
     extern __shared__ __align__(16) unsigned char s_long[];   // LONG_SMEM_BYTES
     __shared__ int s_w;
     const int work = *work_count;
@@ -1213,6 +1223,8 @@ local_sort_kernel(const uint64_t* __restrict__ keys_grouped, const uint32_t* __r
                   const int2* __restrict__ seg,
                   const int* __restrict__ work_count, const uint32_t* __restrict__ work_tiles, int* __restrict__ work_ticket)
 {
+    chain_release();
+    chain_wait();   // nothing is read or written before the kernels ahead on the stream are complete
     constexpr int NB = local_buckets(CAP);   // depth buckets
     constexpr int ITEMS = CAP / THREADS;     // elements per thread: positions tid + q * THREADS of the list
     extern __shared__ __align__(16) unsigned char s_local[];
@@ -1570,7 +1582,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         if (cudaMemsetAsync(base, 0, clear_bytes, st) != cudaSuccess) return FGS_ERR_CUDA;
     } else {
         const bool keep = have_counts && counts_in_scratch;
-        clear_bookkeeping_kernel<<<sms * 8, 256, 0, st>>>(reinterpret_cast<uint32_t*>(base), L.status_off / 4, status_words,
+        chain_launch(clear_bookkeeping_kernel, dim3(sms * 8), dim3(256), 0, st, reinterpret_cast<uint32_t*>(base), L.status_off / 4, status_words,
                                                           slots, L.parts, n, n_dev,
                                                           keep ? L.tilecnt_off / 4 : 0, keep ? L.status_off / 4 : 0);
     }
@@ -1618,14 +1630,14 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
             const int in_smem = tile_values <= TILE_HIST_SMEM_VALUES && n >= 4 * tile_values;
             int hist_blocks = (int)(((int64_t)n + 65535) / 65536);
             hist_blocks = hist_blocks < 1 ? 1 : (hist_blocks > sms ? sms : hist_blocks);
-            tile_hist_kernel<<<hist_blocks, TILE_HIST_THREADS, in_smem ? (size_t)tile_values * 4 : 0, st>>>(
+            chain_launch(tile_hist_kernel, dim3(hist_blocks), dim3(TILE_HIST_THREADS), in_smem ? (size_t)tile_values * 4 : 0, st, 
                 keys_unsorted, n, n_dev, (uint32_t)tile_values - 1u, tile_values, in_smem, tile_count);
             mark(LAUNCH_HISTOGRAM);
         }
         // lower and upper halves of the tile bits: at most 8 bits each
         const int lo_bits = tile_bits <= RADIX_BITS ? tile_bits : tile_bits / 2;
         const int buckets = tile_values >> lo_bits;
-        tile_scan_kernel<<<(tile_values + SCAN_CHUNK - 1) / SCAN_CHUNK, TILE_SCAN_THREADS, 0, st>>>(
+        chain_launch(tile_scan_kernel, dim3((tile_values + SCAN_CHUNK - 1) / SCAN_CHUNK), dim3(TILE_SCAN_THREADS), 0, st, 
             counts, tile_values, lo_bits, seg, tile_cursor, bucket_tables, class_count, class_tiles, n, n_dev, dev_status,
             tickets /* the first ticket word: cleared above, not used by any pass of this path */);
         mark(LAUNCH_SEGMENTS);
@@ -1633,7 +1645,7 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         const uint64_t* src_k = keys_unsorted;
         const uint32_t* src_v = values_unsorted;
         if (buckets > 1) {
-            multisplit_kernel<false><<<ms_parts, MS_THREADS, MS_SMEM_BYTES, st>>>(
+            chain_launch(multisplit_kernel<false>, dim3(ms_parts), dim3(MS_THREADS), MS_SMEM_BYTES, st, 
                 src_k, src_v, keys_sorted, values_sorted, n, n_dev, (uint32_t)tile_values - 1u, lo_bits, buckets,
                 bucket_tables, bucket_tables /* the coarse buckets' cursors lead the tables */);
             mark(LAUNCH_DIGIT_PASS);
@@ -1641,19 +1653,19 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
             src_v = values_sorted;
         }
         // every coarse bucket is cut into partitions of its own: at most one ragged partition more per bucket
-        multisplit_kernel<true><<<ms_parts + buckets, MS_THREADS, MS_SMEM_BYTES, st>>>(
+        chain_launch(multisplit_kernel<true>, dim3(ms_parts + buckets), dim3(MS_THREADS), MS_SMEM_BYTES, st, 
             src_k, src_v, alt_keys, alt_vals, n, n_dev, (uint32_t)tile_values - 1u, lo_bits, buckets, bucket_tables, tile_cursor);
         mark(LAUNCH_DIGIT_PASS);
-        local_sort_kernel<1024, 128, 8, true><<<grid_for(12), 128, local_smem_bytes<1024>(), st>>>(
+        chain_launch(local_sort_kernel<1024, 128, 8, true>, dim3(grid_for(12)), dim3(128), local_smem_bytes<1024>(), st, 
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 0, class_tiles, class_count + LOCAL_CLASSES + 0);
         mark(LAUNCH_LOCAL_SORT);
-        local_sort_kernel<2048, 256, 4, true><<<grid_for(6), 256, local_smem_bytes<2048>(), st>>>(
+        chain_launch(local_sort_kernel<2048, 256, 4, true>, dim3(grid_for(6)), dim3(256), local_smem_bytes<2048>(), st, 
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 1, class_tiles + MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 1);
         mark(LAUNCH_LOCAL_SORT);
-        local_sort_kernel<LOCAL_CAP, 256, 2, true><<<grid_for(3), 256, local_smem_bytes<LOCAL_CAP>(), st>>>(
+        chain_launch(local_sort_kernel<LOCAL_CAP, 256, 2, true>, dim3(grid_for(3)), dim3(256), local_smem_bytes<LOCAL_CAP>(), st, 
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 2, class_tiles + 2 * MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 2);
         mark(LAUNCH_LOCAL_SORT);
-        long_list_kernel<true><<<grid_for(2), LONG_THREADS, LONG_SMEM_BYTES, st>>>(
+        chain_launch(long_list_kernel<true>, dim3(grid_for(2)), dim3(LONG_THREADS), LONG_SMEM_BYTES, st, 
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 3, class_tiles + 3 * MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 3);
         mark(LAUNCH_LOCAL_SORT);
         if (num_launches) *num_launches = launches;
@@ -1681,16 +1693,16 @@ static int sort_pairs_impl(int num_rendered, int width, int height, int block_x,
         segments_kernel<<<(tile_values + SEG_TILES - 1) / SEG_TILES, SEG_THREADS, 0, st>>>(alt_keys, n, n_dev, tile_values, (uint32_t)tile_values - 1u, seg,
                                                                   class_count, class_tiles);
         mark(LAUNCH_SEGMENTS);
-        local_sort_kernel<1024, 128, 9, false><<<grid_for(12), 128, local_smem_bytes<1024>(), st>>>(
+        chain_launch(local_sort_kernel<1024, 128, 9, false>, dim3(grid_for(12)), dim3(128), local_smem_bytes<1024>(), st, 
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 0, class_tiles, class_count + LOCAL_CLASSES + 0);
         mark(LAUNCH_LOCAL_SORT);
-        local_sort_kernel<2048, 256, 4, false><<<grid_for(6), 256, local_smem_bytes<2048>(), st>>>(
+        chain_launch(local_sort_kernel<2048, 256, 4, false>, dim3(grid_for(6)), dim3(256), local_smem_bytes<2048>(), st, 
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 1, class_tiles + MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 1);
         mark(LAUNCH_LOCAL_SORT);
-        local_sort_kernel<LOCAL_CAP, 256, 2, false><<<grid_for(3), 256, local_smem_bytes<LOCAL_CAP>(), st>>>(
+        chain_launch(local_sort_kernel<LOCAL_CAP, 256, 2, false>, dim3(grid_for(3)), dim3(256), local_smem_bytes<LOCAL_CAP>(), st, 
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 2, class_tiles + 2 * MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 2);
         mark(LAUNCH_LOCAL_SORT);
-        long_list_kernel<false><<<grid_for(2), LONG_THREADS, LONG_SMEM_BYTES, st>>>(
+        chain_launch(long_list_kernel<false>, dim3(grid_for(2)), dim3(LONG_THREADS), LONG_SMEM_BYTES, st, 
             alt_keys, alt_vals, keys_sorted, values_sorted, seg, class_count + 3, class_tiles + 3 * MAX_TILE_VALUES, class_count + LOCAL_CLASSES + 3);
         mark(LAUNCH_LOCAL_SORT);
     }

@@ -29,6 +29,13 @@ void fgs_debug_preprocess_no_column_cull(int on);
 void fgs_debug_sort_plain(int on);
 
 /*
+ * 0: every kernel is launched plainly; non-zero (the default): the kernels of a frame are launched with the
+ * programmatic-serialization attribute, so that a kernel's blocks are resident and waiting when the kernel before it
+ * ends. Results are the same either way; the tests compare the two.
+ */
+void fgs_debug_chained_launches(int on);
+
+/*
  * part >= 0: in the next look-back digit passes (fgs_sort_pairs_stable, or any sort of an image with more than
  * 65536 tiles) the partition with this index does not publish its look-back words, so later partitions run out of
  * their poll budget: the sort returns, FGS_ERR_LOOKBACK_TIMEOUT is raised in the device status word and the output

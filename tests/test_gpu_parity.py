@@ -823,3 +823,41 @@ def test_tile_order_changes_nothing_but_the_time(ops, oracle_lib):
     for im in imgs:
         assert (im == natural).all()
     assert ops.device_status() == 0
+
+
+def test_chained_launches_change_nothing(ops):
+    """The kernels of a frame are launched so that each one's blocks are resident and waiting when the one before it ends
+    (programmatic dependent launch). Two views are rendered alternately, so every frame overwrites the other view's
+    buffers: each frame's sorted lists and image must be the bytes of that view's first frame, and the bytes of the same
+    frames rendered with plain launches, through the operator calls and through the single-call frame."""
+    from flashgs_b200 import _lib
+    from flashgs_b200.rasterizer import DeviceScene, Rasterizer, TorchCamera
+    w = scenes.WORKLOADS["C4"]
+    sc = scenes.make_scene(250000, w.clusters, w.log_scale, seed=11)
+    cams = [scenes.look_at_camera(1280, 720, w.radius, w.hfov_deg, w.azimuth_deg + a, w.elevation_deg) for a in (0.0, 25.0)]
+    ds = DeviceScene(sc, DEV)
+    bg = torch.tensor([0.0, 0.1, 0.2])
+    L = _lib.load()
+    seen = {}
+    try:
+        for chained in (1, 0, 1):
+            L.fgs_debug_chained_launches(chained)
+            ras = Rasterizer(ds, 1 << 23, 1 << 14)
+            for frame in range(24):
+                v = frame & 1
+                fused = (frame >> 1) & 1
+                img = (ras.forward_fused if fused else ras.forward)(ds, TorchCamera(cams[v]), bg)
+                R = int(ras.curr_offset.cpu()[0])
+                got = (R, ras.gaussian_keys_sorted[:R].clone(), ras.gaussian_values_sorted[:R].clone(), img.clone())
+                if v not in seen:
+                    seen[v] = got
+                    assert R > 100000
+                    continue
+                want = seen[v]
+                assert got[0] == want[0], (chained, frame)
+                for a, b in zip(got[1:], want[1:]):
+                    assert bool((a == b).all()), (chained, frame, fused)
+            del ras
+        assert ops.device_status() == 0
+    finally:
+        L.fgs_debug_chained_launches(1)
