@@ -21,7 +21,8 @@ REF_SO = os.path.join(REF_DIR, "flash_gaussian_splatting.so")
 # Tool and source locations; each can be overridden from the environment.
 CXX = os.environ.get("FLASHGS_CXX", "/usr/bin/g++")   # the system compiler; a wrapped compiler produced a reference module that crashed in loadPly
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
-REFERENCE_ROOT = os.environ.get("FLASHGS_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: by default a directory named "reference" beside this repository
+REFERENCE_ROOT = os.environ.get("FLASHGS_REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 REF_EXAMPLE = os.path.join(REF_DIR, "example.py")   # the reference's example script, beside its build (untracked like it)
 
 
