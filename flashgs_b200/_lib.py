@@ -48,7 +48,7 @@ SIGNATURES = {
     "fgs_render_32x32": (_i, [_i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]),
     "fgs_render_ex": (_i, [_i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _p, _p, _p, _p, _p, _p]),
     "fgs_render_frame": (_i, [_i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _f, _f, _f, _f, _p, _p, _p, _p, _p, _p, _p, _p, _i64,
-                              _p, C.c_size_t, _p, _p, _i, _i, _p, _p, _p, _p]),
+                              _p, C.c_size_t, _p, _p, _i, _i, _p, _p, _p, _p, _p]),
     "fgs_tile_ranges": (_i, [_i, _i, _p, _p, _p]),
     "fgs_ply_vertex_count": (C.c_longlong, [C.c_char_p]),
     "fgs_ply_load": (_i, [C.c_char_p, C.c_longlong, _p, _p, _p, _p]),

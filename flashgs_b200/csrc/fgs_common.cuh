@@ -6,7 +6,7 @@
 
 #include "../../include/flashgs_b200.h"
 
-#define FGS_ABI_VERSION 2
+#define FGS_ABI_VERSION 3
 
 namespace fgs {
 

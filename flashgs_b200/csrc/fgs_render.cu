@@ -399,9 +399,10 @@ extern "C" int fgs_render_frame(int P, const float* positions, const float* shs,
                                 uint64_t* keys_sorted, uint32_t* values_sorted, int64_t pair_capacity,
                                 void* sort_temp, size_t sort_temp_bytes, int* ranges, int* curr_offset,
                                 int tile_row_begin, int tile_row_end, uint8_t* out_color,
-                                int* consumed, const int* tile_order, void* stream)
+                                int* consumed, const int* tile_order, const float* scene_bounds, void* stream)
 {
     using namespace fgs;
+    if (scene_bounds != nullptr && !aligned16(scene_bounds)) return FGS_ERR_BAD_ARG;
     if (pair_capacity <= 0 || pair_capacity >= (1 << 30) || !curr_offset || !out_color || !bg_color || !ranges) return FGS_ERR_BAD_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (cudaMemsetAsync(curr_offset, 0, sizeof(int), st) != cudaSuccess) return FGS_ERR_CUDA;
@@ -422,7 +423,7 @@ extern "C" int fgs_render_frame(int P, const float* positions, const float* shs,
     int rc = fgs_preprocess_prepared(P, positions, shs, opacities, cov3ds, width, height, block_x, block_y, cam_position,
                                      cam_rotation, focal_x, focal_y, zFar, zNear, tile_row_begin, tile_row_end, points_xy,
                                      rgb_depth, conic_opacity, keys_unsorted, values_unsorted, pair_capacity, curr_offset,
-                                     cull_list, cull_list ? (int64_t)P + 1 : 0, nullptr, tile_counts, stream);
+                                     cull_list, cull_list ? (int64_t)P + 1 : 0, cull_list ? scene_bounds : nullptr, tile_counts, stream);
     if (rc != FGS_OK) return rc;
     rc = sort_pairs_device_count((int)pair_capacity, curr_offset, width, height, block_x, block_y, sort_temp, sort_temp_bytes,
                                  keys_unsorted, values_unsorted, keys_sorted, values_sorted, stream, tile_counts != nullptr);

@@ -306,7 +306,7 @@ def render_frame(orig_points, shs, opacities, cov3Ds, width, height, block_x, bl
                  points_xy, rgb_depth, conic_opacity,
                  gaussian_keys_unsorted, gaussian_values_unsorted, gaussian_keys_sorted, gaussian_values_sorted,
                  list_sorting_space, ranges, curr_offset, out_color,
-                 tile_row_begin: int = 0, tile_row_end: int = -1, consumed=None, tile_order=None) -> None:
+                 tile_row_begin: int = 0, tile_row_end: int = -1, consumed=None, tile_order=None, scene_bounds=None) -> None:
     """One frame in one call with no host round trip (no reference counterpart): what ``preprocess``,
     ``sort_gaussian`` and ``render_*`` do in sequence, the pair count staying in ``curr_offset`` on the device.
     Read ``curr_offset`` afterwards if the count is wanted; an overflow of the pair buffers shows in ``device_status``."""
@@ -339,6 +339,11 @@ def render_frame(orig_points, shs, opacities, cov3Ds, width, height, block_x, bl
             raise RuntimeError("tile_order needs one entry per tile of the rendered rows")
     if xy.numel() < 2 * P or rd.numel() < 4 * P or co.numel() < 4 * P:
         raise RuntimeError("points_xy, rgb_depth and conic_opacity need one record per Gaussian (%d)" % P)
+    bounds = None
+    if scene_bounds is not None:
+        bounds = _in(scene_bounds, "scene_bounds", f32)
+        if bounds.numel() != 4 * P or not scene_bounds.is_contiguous():
+            raise RuntimeError("scene_bounds needs one contiguous [4] record per Gaussian")
     st = _L.fgs_render_frame(P, _in(orig_points, "orig_points", f32).data_ptr(), _in(shs, "shs", f32).data_ptr(),
                              op.data_ptr(), _in(cov3Ds, "cov3Ds", f32).data_ptr(),
                              int(width), int(height), int(block_x), int(block_y), pos.data_ptr(), rot.data_ptr(),
@@ -349,7 +354,8 @@ def render_frame(orig_points, shs, opacities, cov3Ds, width, height, block_x, bl
                              rg.data_ptr(), _out(curr_offset, "curr_offset", torch.int32).data_ptr(),
                              int(tile_row_begin), int(tile_row_end), out_color.data_ptr(),
                              None if consumed is None else _out(consumed, "consumed", torch.int32).data_ptr(),
-                             None if tile_order is None else _in(tile_order, "tile_order", torch.int32).data_ptr(), _stream())
+                             None if tile_order is None else _in(tile_order, "tile_order", torch.int32).data_ptr(),
+                             None if bounds is None else bounds.data_ptr(), _stream())
     _lib.check("render_frame", st)
 
 

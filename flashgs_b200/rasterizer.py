@@ -166,7 +166,8 @@ class Rasterizer:
                               self.gaussian_keys_unsorted, self.gaussian_values_unsorted,
                               self.gaussian_keys_sorted, self.gaussian_values_sorted,
                               self.list_sorting_space, self.ranges, self.curr_offset, out_color,
-                              tile_row_begin=r[0], tile_row_end=r[1], **self._tile_order_arguments(camera, rows))
+                              tile_row_begin=r[0], tile_row_end=r[1], scene_bounds=self.scene_bounds,
+                              **self._tile_order_arguments(camera, rows))
         return out_color
 
 

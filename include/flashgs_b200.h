@@ -303,7 +303,7 @@ int fgs_render_ex(int block_x, int block_y, int num_rendered, int width, int hei
  * fgs_preprocess_strip_culled: the sort does not need its scratch until preprocess is done). If the frame produces more
  * pairs than pair_capacity the surplus is dropped, the image is built from the pairs that fit and
  * FGS_ERR_PAIR_OVERFLOW is raised in the device status word. `consumed` and `tile_order` (both may be NULL) are
- * fgs_render_ex's. No counterpart in the reference.
+ * fgs_render_ex's, `scene_bounds` (may be NULL) is fgs_preprocess_prepared's. No counterpart in the reference.
  */
 int fgs_render_frame(int P, const float* positions, const float* shs, const float* opacities, const float* cov3ds,
                      int width, int height, int block_x, int block_y,
@@ -314,7 +314,7 @@ int fgs_render_frame(int P, const float* positions, const float* shs, const floa
                      uint64_t* keys_sorted, uint32_t* values_sorted, int64_t pair_capacity,
                      void* sort_temp, size_t sort_temp_bytes, int* ranges, int* curr_offset,
                      int tile_row_begin, int tile_row_end, uint8_t* out_color,
-                     int* consumed, const int* tile_order, void* stream);
+                     int* consumed, const int* tile_order, const float* scene_bounds, void* stream);
 
 /*
  * Tile ranges only (the first half of the render entry points). Replaces

@@ -35,7 +35,7 @@ def test_library_exports_every_declared_symbol():
         checked = C.CDLL(_lib.LIB_CHECKED_PATH)
         for n in names + list(_lib.TEST_HOOKS + _lib.CHECKED_HOOKS):
             assert hasattr(checked, n), "checked flavour: missing export " + n
-    assert lib.fgs_abi_version() == 2
+    assert lib.fgs_abi_version() == 3
     assert _lib.status_string(0) == "ok"
     assert "overflow" in _lib.status_string(_lib.ERR_PAIR_OVERFLOW)
 
