@@ -85,10 +85,18 @@ class Rasterizer:
         self.order_refresh = 16 if ours and hasattr(ops, "tile_order_from") else 0
         self.tile_consumed = z(MAX_NUM_TILES, torch.int32) if self.order_refresh else None
         self._order, self._order_key, self._frames = None, None, 0
+        self._count_host, self._count_ready = None, None
         self._render = {(16, 16): "render_16x16", (32, 16): "render_32x16", (32, 32): "render_32x32"}[tuple(block)]
 
     def forward(self, scene: DeviceScene, camera, bg_color, out_color=None, rows=None):
         """One frame (example.py:67-94). Returns the int8 [H,W,3] image tensor."""
+        self.begin(scene, camera, rows=rows)
+        return self.finish(scene, camera, bg_color, out_color=out_color, rows=rows)
+
+    def begin(self, scene: DeviceScene, camera, rows=None):
+        """First half of a frame, nothing waited for: preprocess on the current stream (example.py:67-78). A caller
+        that keeps two rasterizers on two streams calls ``begin`` of the next frame before ``finish`` of this one, so
+        that the GPU has work while the host waits for this frame's pair count."""
         ops, (bx, by) = self.ops, self.block
         self.curr_offset.fill_(0)
         extra = {} if rows is None else dict(tile_row_begin=rows[0], tile_row_end=rows[1])
@@ -96,10 +104,8 @@ class Rasterizer:
             extra["cull_scratch"] = self.cull_scratch
             if self.scene_bounds is not None:
                 extra["scene_bounds"] = self.scene_bounds
-        sort_extra = {}
         if self.tile_counts is not None:
             extra["tile_counts"] = self.tile_counts
-            sort_extra["tile_counts"] = self.tile_counts
         ops.preprocess(scene.position, scene.shs, scene.opacity, scene.cov3d,
                        camera.width, camera.height, bx, by,
                        camera.position, camera.rotation,
@@ -107,10 +113,22 @@ class Rasterizer:
                        self.points_xy, self.rgb_depth, self.conic_opacity,
                        self.gaussian_keys_unsorted, self.gaussian_values_unsorted,
                        self.curr_offset, **extra)
-        num_rendered = int(self.curr_offset.cpu()[0])
+        if self._count_host is None:
+            self._count_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._count_ready = torch.cuda.Event()
+        self._count_host.copy_(self.curr_offset, non_blocking=True)   # example.py:79, through pinned memory
+        self._count_ready.record()
+
+    def finish(self, scene: DeviceScene, camera, bg_color, out_color=None, rows=None):
+        """Second half: wait for the pair count (the one host synchronisation the operator signatures impose), sort,
+        render (example.py:79-94). Runs on the current stream, which must be the one ``begin`` ran on."""
+        ops, (bx, by) = self.ops, self.block
+        self._count_ready.synchronize()
+        num_rendered = int(self._count_host[0])
         if num_rendered >= self.MAX_NUM_RENDERED:
             raise RuntimeError("Too many k-v pairs! (%d >= %d)" % (num_rendered, self.MAX_NUM_RENDERED))
         self.num_rendered = num_rendered
+        sort_extra = {"tile_counts": self.tile_counts} if self.tile_counts is not None else {}
         ops.sort_gaussian(num_rendered, camera.width, camera.height, bx, by,
                           self.list_sorting_space,
                           self.gaussian_keys_unsorted, self.gaussian_values_unsorted,

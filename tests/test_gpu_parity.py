@@ -861,3 +861,39 @@ def test_chained_launches_change_nothing(ops):
         assert ops.device_status() == 0
     finally:
         L.fgs_debug_chained_launches(1)
+
+
+def test_two_frames_in_flight(ops):
+    """Two rasterizers on two streams, the next frame's ``begin`` queued before this frame's ``finish``: every frame
+    is the bytes of the same view rendered alone."""
+    from flashgs_b200.rasterizer import DeviceScene, Rasterizer, TorchCamera
+    w = scenes.WORKLOADS["C4"]
+    sc = scenes.make_scene(200000, w.clusters, w.log_scale, seed=3)
+    cams = [TorchCamera(scenes.look_at_camera(1280, 720, w.radius, w.hfov_deg, w.azimuth_deg + 20.0 * i, w.elevation_deg)) for i in range(5)]
+    ds = DeviceScene(sc, DEV)
+    bg = torch.tensor([0.3, 0.2, 0.1])
+    alone = Rasterizer(ds, 1 << 23, 1 << 14)
+    want = [alone.forward(ds, c, bg).clone() for c in cams]
+    counts = []
+    for c in cams:
+        alone.forward(ds, c, bg)
+        counts.append(alone.num_rendered)
+    slots = [(Rasterizer(ds, 1 << 23, 1 << 14), torch.cuda.Stream()), (Rasterizer(ds, 1 << 23, 1 << 14), torch.cuda.Stream())]
+    torch.cuda.synchronize()
+    frames = [k % len(cams) for k in range(12)]
+    got = []
+    with torch.cuda.stream(slots[0][1]):
+        slots[0][0].begin(ds, cams[frames[0]])
+    for k, v in enumerate(frames):
+        r, s = slots[k & 1]
+        if k + 1 < len(frames):
+            rn, sn = slots[(k + 1) & 1]
+            with torch.cuda.stream(sn):
+                rn.begin(ds, cams[frames[k + 1]])
+        with torch.cuda.stream(s):
+            got.append((v, r.finish(ds, cams[v], bg), r.num_rendered))
+    torch.cuda.synchronize()
+    for v, img, n in got:
+        assert n == counts[v]
+        assert bool((img == want[v]).all()), v
+    assert ops.device_status() == 0
