@@ -495,6 +495,11 @@ def main():
 
     # ---- device-resident throughput ----
     sampler = ClockSampler(local_rank)
+    # No collector pauses inside timed regions (both arms): a frame is under two milliseconds, and the host reads the
+    # pair count back once per frame, so a pause of the interpreter is a pause of the GPU.
+    import gc
+    gc.collect()
+    gc.disable()
     sampler.start()   # before the warm-up: the tool needs a moment before its first sample
     t_warm = time.perf_counter()
     for _ in range(args.warmup):
